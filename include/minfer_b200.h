@@ -1,0 +1,134 @@
+/*
+ * minfer_b200.h - C ABI of the B200-native (sm_100a) quantized decode path.
+ *
+ * This is the boundary a host program binds to (C, C++, ctypes, cgo ...): plain
+ * pointers and sizes, no C++ or framework types.  The reference engine
+ * (123-code/nano-inference, "minfer") has no plugin API; its seam between host
+ * driver and CUDA kernels is the set of kernel launches in src/cuda_infer.cu
+ * and the device functions of src/mega.cu.  Each entry point below names the
+ * reference code it stands in for (paths relative to the reference root).
+ *
+ * Conventions
+ *  - Every function returns an int status (MI_OK == 0).  Nothing here calls
+ *    exit() or traps; mi_last_error() gives a text for the last failure on a
+ *    context.  The reference's CK()/REQUIRE() print-and-exit behaviour
+ *    (src/cuda_infer.cu:20, src/mega.cu:46-47) stays in the driver programs.
+ *  - Pointers named *_dev are device pointers on the context's GPU; pointers
+ *    named *_host are ordinary host memory.  Work is enqueued on the context's
+ *    stream and is asynchronous unless stated otherwise.
+ *  - There is no CPU fallback: without a usable CUDA device every call fails.
+ *  - Device-side waits (bulk-copy barriers, grid barriers, peer flags) are
+ *    bounded; when one gives up the kernel records MI_ERR_TIMEOUT in the
+ *    context's device error word, which mi_ctx_sync() reports.
+ */
+#ifndef MINFER_B200_H
+#define MINFER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define MI_API __attribute__((visibility("default")))
+#else
+#define MI_API
+#endif
+
+enum {
+    MI_OK = 0,
+    MI_ERR_INVALID = 1,      /* bad argument (null pointer, shape not a multiple of 32, ...) */
+    MI_ERR_CUDA = 2,         /* a CUDA runtime call failed; see mi_last_error */
+    MI_ERR_NOMEM = 3,        /* device or host allocation failed */
+    MI_ERR_TIMEOUT = 4,      /* a bounded device-side wait gave up */
+    MI_ERR_IO = 5,           /* file could not be opened / read */
+    MI_ERR_FORMAT = 6,       /* GGUF file malformed or missing a tensor / key */
+    MI_ERR_UNSUPPORTED = 7,  /* tensor type or shape outside what this path implements */
+    MI_ERR_LIMIT = 8         /* request exceeds a fixed capacity stated by the entry point */
+};
+
+typedef struct mi_ctx mi_ctx;        /* one GPU: stream, error word, scratch */
+typedef struct mi_weight mi_weight;  /* q4_0 matrix (or stack of equal matrices) in the tiled device layout */
+
+/* ---- context ------------------------------------------------------------- */
+
+/* Library version string. */
+MI_API const char* mi_version(void);
+/* Text for a status code. */
+MI_API const char* mi_strerror(int status);
+
+/* Create a context on CUDA device `device` with its own non-blocking stream.
+ * Stands in for the reference's implicit process-wide state (one device, one
+ * stream: src/cuda_infer.cu:1089, src/mega.cu:1149). */
+MI_API int mi_ctx_create(int device, mi_ctx** out);
+MI_API int mi_ctx_destroy(mi_ctx* ctx);
+/* Use a caller-owned cudaStream_t (passed as void*) for all later work; NULL
+ * restores the context's own stream. */
+MI_API int mi_ctx_set_stream(mi_ctx* ctx, void* cuda_stream);
+/* Wait for the stream, then report the device error word (MI_ERR_TIMEOUT if a
+ * bounded wait gave up) and clear it. */
+MI_API int mi_ctx_sync(mi_ctx* ctx);
+MI_API const char* mi_last_error(const mi_ctx* ctx);
+/* Number of SMs the context sizes its grids for. */
+MI_API int mi_ctx_sm_count(const mi_ctx* ctx);
+
+/* ---- weights: GGUF q4_0 -> tiled device layout --------------------------- */
+
+/* Upload `count` consecutive row-major q4_0 matrices of rows x cols (18-byte
+ * blocks exactly as stored in a GGUF file: src/gguf.h:29,94-102) from host
+ * memory and repack them ON THE DEVICE into the tiled layout the kernels
+ * stream (32-row groups x kb-block tiles, nibbles then fp16 scales, each tile
+ * one contiguous 16-byte-multiple run so a single bulk copy fetches it).
+ * Replaces the host-side repack loops dt_q4r (src/cuda_infer.cu:761-777) and
+ * pack_q4 (src/mega.cu:966-984).  cols must be a multiple of 32. Synchronous. */
+MI_API int mi_weight_upload_q4_0(mi_ctx* ctx, const void* raw_host, int64_t rows, int64_t cols,
+                                 int64_t count, mi_weight** out);
+/* Same, the raw blocks already being in device memory (2-byte aligned). */
+MI_API int mi_weight_repack_q4_0_dev(mi_ctx* ctx, const void* raw_dev, int64_t rows, int64_t cols,
+                                     int64_t count, mi_weight** out);
+/* Inverse of the repack: tiled layout back to GGUF block order in host memory
+ * (count*rows*(cols/32)*18 bytes).  For round-trip checks. Synchronous. */
+MI_API int mi_weight_download_q4_0(mi_ctx* ctx, const mi_weight* w, void* raw_host);
+MI_API int mi_weight_free(mi_ctx* ctx, mi_weight* w);
+/* Shape queries: rows, cols, count, bytes held on the device. */
+MI_API int mi_weight_info(const mi_weight* w, int64_t* rows, int64_t* cols, int64_t* count, int64_t* device_bytes);
+
+/* ---- activation quantizer ------------------------------------------------ */
+
+/* q8_0 quantizer for M vectors of n floats (n a multiple of 32), each block of
+ * 32: a = max|x|, xq = rint(x * 127/a) as int8, xd = fp16(a/127); a == 0 gives
+ * zeros.  x_dev is [M][n], xq_dev [M][n], xd_dev [M][n/32] (fp16 bits).
+ * Replaces quant_x_q8 / quant_x_q8_batch (src/cuda_infer.cu:80-89, 168-178). */
+MI_API int mi_quant_q8(mi_ctx* ctx, const float* x_dev, int64_t n, int M, int8_t* xq_dev, uint16_t* xd_dev);
+
+/* ---- q4_0 x q8_0 GEMV ---------------------------------------------------- */
+
+/* y[c][r] = sum_b dw[c][r][b] * dx[b] * (sum_k n_k*xq_k - 8*sum_k xq_k) + bias[r]
+ * for every matrix c of the stack; the integer part is exact, the fp32 part is
+ * fma(dw*dx, float(isum), acc) in block order within a K-split, splits added in
+ * split order.  xq_dev [cols], xd_dev [cols/32] fp16 bits, bias_dev [rows] or
+ * NULL, y_dev [count][rows] fp32.  One launch covers the whole stack.
+ * Replaces gemv_dp4a (src/cuda_infer.cu:94-127) and row_dot (src/mega.cu:178-196). */
+MI_API int mi_gemv_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
+                         const float* bias_dev, float* y_dev);
+/* Same with explicit tuning: ksplit (0 = automatic) is the number of K-splits
+ * per 32-row group, variant (0 = default) selects a warps/stages instantiation. */
+MI_API int mi_gemv_q4_q8_ex(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
+                            const float* bias_dev, float* y_dev, int ksplit, int variant);
+/* The exact integer block sums isum[r][b] = sum n*xq - 8*sum xq (int32,
+ * [rows][cols/32]) of matrix 0 of the stack, produced by the same unpack + dp4a
+ * code as the GEMV.  For bit-exact parity checks. */
+MI_API int mi_block_isums_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, int32_t* isum_dev);
+
+/* Host-buffer convenience: quantize x_host [cols] on the device, run the GEMV on
+ * matrix stack w, and copy y back to y_host [count][rows].  Host-to-device and
+ * device-to-host copies are inside the call; it returns when y_host is valid. */
+MI_API int mi_gemv_q4_f32_host(mi_ctx* ctx, const mi_weight* w, const float* x_host, const float* bias_dev,
+                               float* y_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MINFER_B200_H */

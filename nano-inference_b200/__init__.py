@@ -1,0 +1,176 @@
+"""ctypes binding of libminfer_b200.so, the B200-native (sm_100a) quantized decode path.
+
+The product is the CUDA library behind the C ABI of include/minfer_b200.h; this
+module only loads it and passes device pointers.  PyTorch is used by callers for
+device memory and streams, never for the arithmetic.  There is no CPU fallback:
+if the library has not been built, or no GPU is present, calls fail loudly.
+
+The directory name contains a hyphen, so load it with importlib (the repository's
+__graft_entry__.load_package() does this) under the module name nano_inference_b200.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "lib" / "libminfer_b200.so"
+BIN_DIR = PKG_DIR / "bin"
+
+MI_OK = 0
+STATUS_NAMES = {0: "MI_OK", 1: "MI_ERR_INVALID", 2: "MI_ERR_CUDA", 3: "MI_ERR_NOMEM", 4: "MI_ERR_TIMEOUT",
+                5: "MI_ERR_IO", 6: "MI_ERR_FORMAT", 7: "MI_ERR_UNSUPPORTED", 8: "MI_ERR_LIMIT"}
+
+
+class MinferError(RuntimeError):
+    def __init__(self, status, where, detail=""):
+        self.status = status
+        super().__init__(f"{where}: {STATUS_NAMES.get(status, status)} {detail}".strip())
+
+
+_lib = None
+
+_vp, _i32, _i64 = C.c_void_p, C.c_int, C.c_int64
+# name -> (restype, argtypes); every symbol include/minfer_b200.h declares
+SIGNATURES = {
+    "mi_version": (C.c_char_p, []),
+    "mi_strerror": (C.c_char_p, [_i32]),
+    "mi_ctx_create": (_i32, [_i32, C.POINTER(_vp)]),
+    "mi_ctx_destroy": (_i32, [_vp]),
+    "mi_ctx_set_stream": (_i32, [_vp, _vp]),
+    "mi_ctx_sync": (_i32, [_vp]),
+    "mi_last_error": (C.c_char_p, [_vp]),
+    "mi_ctx_sm_count": (_i32, [_vp]),
+    "mi_weight_upload_q4_0": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
+    "mi_weight_repack_q4_0_dev": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
+    "mi_weight_download_q4_0": (_i32, [_vp, _vp, _vp]),
+    "mi_weight_free": (_i32, [_vp, _vp]),
+    "mi_weight_info": (_i32, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
+    "mi_quant_q8": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
+    "mi_gemv_q4_q8": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mi_gemv_q4_q8_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32]),
+    "mi_block_isums_q4_q8": (_i32, [_vp, _vp, _vp, _vp]),
+    "mi_gemv_q4_f32_host": (_i32, [_vp, _vp, _vp, _vp, _vp]),
+}
+
+
+def load_library(path=None):
+    """Load libminfer_b200.so and attach argument types.  Raises if it is missing."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = Path(path) if path else LIB_PATH
+    if not p.exists():
+        raise FileNotFoundError(f"{p} not built: run `python nano-inference_b200/build.py` (needs nvcc); there is no fallback path")
+    lib = C.CDLL(str(p))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError if the library does not export a declared symbol
+        fn.restype, fn.argtypes = res, args
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def _ptr(t):
+    """Device (or host) address of a torch tensor / numpy array / int / None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    if hasattr(t, "ctypes"):
+        return t.ctypes.data
+    raise TypeError(f"cannot take the address of {type(t)}")
+
+
+class Context:
+    """One GPU: wraps mi_ctx."""
+
+    def __init__(self, device=0):
+        self.lib = load_library()
+        h = _vp()
+        st = self.lib.mi_ctx_create(device, C.byref(h))
+        if st != MI_OK:
+            raise MinferError(st, "mi_ctx_create", "(no usable sm_100 CUDA device?)")
+        self.h = h
+        self.device = device
+
+    def check(self, st, where):
+        if st != MI_OK:
+            raise MinferError(st, where, self.lib.mi_last_error(self.h).decode())
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.mi_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def sm_count(self):
+        return self.lib.mi_ctx_sm_count(self.h)
+
+    def set_stream(self, cuda_stream_ptr):
+        self.check(self.lib.mi_ctx_set_stream(self.h, cuda_stream_ptr), "mi_ctx_set_stream")
+
+    def use_torch_stream(self):
+        import torch
+        self.set_stream(torch.cuda.current_stream().cuda_stream)
+
+    def sync(self):
+        self.check(self.lib.mi_ctx_sync(self.h), "mi_ctx_sync")
+
+    # ---- weights
+    def upload_q4_0(self, raw_host, rows, cols, count=1):
+        """raw_host: numpy uint8 array of count*rows*(cols/32)*18 bytes in GGUF block order."""
+        h = _vp()
+        self.check(self.lib.mi_weight_upload_q4_0(self.h, _ptr(raw_host), rows, cols, count, C.byref(h)), "mi_weight_upload_q4_0")
+        return Weight(self, h)
+
+    def repack_q4_0_dev(self, raw_dev, rows, cols, count=1):
+        h = _vp()
+        self.check(self.lib.mi_weight_repack_q4_0_dev(self.h, _ptr(raw_dev), rows, cols, count, C.byref(h)), "mi_weight_repack_q4_0_dev")
+        return Weight(self, h)
+
+    # ---- kernels (device pointers: torch CUDA tensors)
+    def quant_q8(self, x, xq, xd, n=None, M=1):
+        n = x.shape[-1] if n is None else n
+        self.check(self.lib.mi_quant_q8(self.h, _ptr(x), n, M, _ptr(xq), _ptr(xd)), "mi_quant_q8")
+
+    def gemv_q4_q8(self, w, xq, xd, y, bias=None, ksplit=0, variant=0):
+        self.check(self.lib.mi_gemv_q4_q8_ex(self.h, w.h, _ptr(xq), _ptr(xd), _ptr(bias), _ptr(y), ksplit, variant), "mi_gemv_q4_q8")
+
+    def block_isums(self, w, xq, isum):
+        self.check(self.lib.mi_block_isums_q4_q8(self.h, w.h, _ptr(xq), _ptr(isum)), "mi_block_isums_q4_q8")
+
+    def gemv_q4_f32_host(self, w, x_host, y_host, bias=None):
+        self.check(self.lib.mi_gemv_q4_f32_host(self.h, w.h, _ptr(x_host), _ptr(bias), _ptr(y_host)), "mi_gemv_q4_f32_host")
+
+
+class Weight:
+    """A q4_0 matrix stack in the tiled device layout: wraps mi_weight."""
+
+    def __init__(self, ctx, h):
+        self.ctx, self.h = ctx, h
+        r, c, n, b = _i64(), _i64(), _i64(), _i64()
+        ctx.lib.mi_weight_info(h, C.byref(r), C.byref(c), C.byref(n), C.byref(b))
+        self.rows, self.cols, self.count, self.device_bytes = r.value, c.value, n.value, b.value
+
+    def download(self, out_host):
+        self.ctx.check(self.ctx.lib.mi_weight_download_q4_0(self.ctx.h, self.h, _ptr(out_host)), "mi_weight_download_q4_0")
+
+    def free(self):
+        if self.h and self.ctx.h:
+            self.ctx.lib.mi_weight_free(self.ctx.h, self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
