@@ -65,7 +65,8 @@ MI_API const char* mi_strerror(int status);
 MI_API int mi_ctx_create(int device, mi_ctx** out);
 MI_API int mi_ctx_destroy(mi_ctx* ctx);
 /* Use a caller-owned cudaStream_t (passed as void*) for all later work; NULL
- * restores the context's own stream. */
+ * restores the context's own stream.  The legacy default stream, whose handle is
+ * 0, is selected with its alias cudaStreamLegacy ((void*)1). */
 MI_API int mi_ctx_set_stream(mi_ctx* ctx, void* cuda_stream);
 /* Wait for the stream, then report the device error word (MI_ERR_TIMEOUT if a
  * bounded wait gave up) and clear it. */

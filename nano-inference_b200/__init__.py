@@ -120,7 +120,8 @@ class Context:
 
     def use_torch_stream(self):
         import torch
-        self.set_stream(torch.cuda.current_stream().cuda_stream)
+        h = torch.cuda.current_stream().cuda_stream
+        self.set_stream(h if h else 1)          # handle 0 is the legacy default stream: pass its alias
 
     def sync(self):
         self.check(self.lib.mi_ctx_sync(self.h), "mi_ctx_sync")

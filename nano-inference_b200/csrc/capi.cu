@@ -120,7 +120,7 @@ extern "C" int mi_ctx_destroy(mi_ctx* ctx) {
 
 extern "C" int mi_ctx_set_stream(mi_ctx* ctx, void* cuda_stream) {
     if (!ctx) return MI_ERR_INVALID;
-    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;
+    ctx->stream = cuda_stream ? (cudaStream_t)cuda_stream : ctx->own_stream;   // cudaStreamLegacy is (void*)1
     return MI_OK;
 }
 

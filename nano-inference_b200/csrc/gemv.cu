@@ -46,7 +46,11 @@ static int launch_one(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksp
     if (smem > (size_t)ctx->smem_optin)
         return set_error(ctx, MI_ERR_UNSUPPORTED, "gemv: %zu bytes of shared memory needed, %d available", smem, ctx->smem_optin);
     auto kern = gemv_q4_q8_kernel<KB, NW, S, DUMP>;
-    MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    static size_t smem_set[16] = {0};                  // per device: largest size already opted in
+    if (smem > smem_set[ctx->device & 15]) {
+        MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        smem_set[ctx->device & 15] = smem;
+    }
     const long long base_units = (long long)w->count * w->groups;
     const long long total_warps = (long long)ctx->sm_count * NW;
     int ks = ksplit;
@@ -76,13 +80,13 @@ template <int KB, bool DUMP>
 static int launch_kb(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksplit, int variant) {
     if (DUMP) return launch_one<KB, 8, 2, true>(ctx, w, io, 1);
     switch (variant) {
-        case 0: return launch_one<KB, 8, 4, false>(ctx, w, io, ksplit);
-        case 1: return launch_one<KB, 8, 3, false>(ctx, w, io, ksplit);
+        case 0: return launch_one<KB, 8, 3, false>(ctx, w, io, ksplit);
+        case 1: return launch_one<KB, 8, 4, false>(ctx, w, io, ksplit);
         case 2: return launch_one<KB, 8, 2, false>(ctx, w, io, ksplit);
         case 3: return launch_one<KB, 16, 2, false>(ctx, w, io, ksplit);
         case 4: return launch_one<KB, 4, 8, false>(ctx, w, io, ksplit);
         case 5: return launch_one<KB, 12, 3, false>(ctx, w, io, ksplit);
-        case 6: return launch_one<KB, 16, 3, false>(ctx, w, io, ksplit);
+        case 6: return launch_one<KB, 6, 4, false>(ctx, w, io, ksplit);
         case 7: return launch_one<KB, 4, 4, false>(ctx, w, io, ksplit);
         default: return set_error(ctx, MI_ERR_INVALID, "gemv: variant %d out of range [0,%d)", variant, kNumVariants);
     }
