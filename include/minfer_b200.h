@@ -107,9 +107,9 @@ MI_API int mi_quant_q8(mi_ctx* ctx, const float* x_dev, int64_t n, int M, int8_t
 /* ---- q4_0 x q8_0 GEMV ---------------------------------------------------- */
 
 /* y[c][r] = sum_b dw[c][r][b] * dx[b] * (sum_k n_k*xq_k - 8*sum_k xq_k) + bias[r]
- * for every matrix c of the stack; the integer part is exact, the fp32 part is
- * fma(dw*dx, float(isum), acc) in block order within a K-split, splits added in
- * split order.  xq_dev [cols], xd_dev [cols/32] fp16 bits, bias_dev [rows] or
+ * for every matrix c of the stack; the integer part is exact, every block product
+ * dw*dx*isum is exact in double, the sum is carried in double and rounded to fp32
+ * once, so the result does not depend on how the blocks are split or ordered.  xq_dev [cols], xd_dev [cols/32] fp16 bits, bias_dev [rows] or
  * NULL, y_dev [count][rows] fp32.  One launch covers the whole stack.
  * Replaces gemv_dp4a (src/cuda_infer.cu:94-127) and row_dot (src/mega.cu:178-196). */
 MI_API int mi_gemv_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
@@ -128,6 +128,53 @@ MI_API int mi_block_isums_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* x
  * device-to-host copies are inside the call; it returns when y_host is valid. */
 MI_API int mi_gemv_q4_f32_host(mi_ctx* ctx, const mi_weight* w, const float* x_host, const float* bias_dev,
                                float* y_host);
+
+/* ---- model and decode loop -------------------------------------------------- */
+
+typedef struct mi_model mi_model;    /* weights (tiled), fp16 KV cache and decode state of one Qwen2-architecture model */
+
+typedef struct mi_model_config {
+    int32_t n_layer, n_embd, n_ff, n_head, n_head_kv, head_dim, n_vocab, max_seq, tied_lm_head, grid_ctas;
+    float rope_base, rms_eps;
+    int64_t q4_weight_bytes_per_token;   /* q4_0 bytes every decoded token streams (18 bytes per 32 weights) */
+    int64_t kv_bytes_per_position;       /* fp16 K+V bytes per cached position over all layers */
+} mi_model_config;
+
+enum { MI_DECODE_PERSISTENT = 0,   /* one cooperative launch: all phases, layers and steps in one persistent kernel */
+       MI_DECODE_PER_PHASE = 1 };  /* the same kernel launched once per phase (plain stream order, no grid barrier) */
+
+enum { MI_STATE_H = 0, MI_STATE_Q = 1, MI_STATE_ATT = 2, MI_STATE_KCACHE = 3, MI_STATE_VCACHE = 4,
+       MI_STATE_ACT_Q = 5, MI_STATE_ACT_D = 6 };
+
+/* Load an all-q4_0 Qwen2-architecture GGUF file (metadata keys and tensor names
+ * exactly as the reference drivers read them: src/cpu_infer.cpp:71-98), repack
+ * every matrix on the device (q/k/v fused, rows of q and k made pair-adjacent for
+ * RoPE; gate and up interleaved by 32-row group), allocate an fp16 KV cache for
+ * max_seq positions and plan the per-phase work split.  output.weight may be
+ * absent or byte-identical to token_embd.weight (tied lm_head, stored once).
+ * Replaces the load / upload / buffer set-up of src/cuda_infer.cu:846-955 and
+ * src/mega.cu:1067-1139.  Tensor types other than Q4_0 (matrices) and F32 (norms,
+ * biases) give MI_ERR_UNSUPPORTED. */
+MI_API int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi_model** out);
+MI_API int mi_model_free(mi_ctx* ctx, mi_model* model);
+MI_API int mi_model_info(const mi_model* model, mi_model_config* out);
+/* Device address (and size) of one state buffer, for inspection by tests. */
+MI_API int mi_model_state_ptr(const mi_model* model, int which, void** ptr, int64_t* bytes);
+
+/* Run n_steps decode steps at positions pos0 .. pos0+n_steps-1.  Step s takes
+ * in_tokens_host[s] while s < n_forced (prompt / teacher forcing), afterwards the
+ * previous step's greedy token; out_tokens_host[s] receives the greedy token after
+ * step s (lowest index on ties, as src/cpu_infer.cpp:153-154).  logits_dev, if not
+ * NULL, receives [n_steps][n_vocab] fp32 logits.  elapsed_ms, if not NULL, receives
+ * the device time of the steps (CUDA events on the context's stream).  Returns
+ * after the steps have finished.  Replaces the record() step graph + decode loop of
+ * src/cuda_infer.cu:1031-1201 and the mega kernel of src/mega.cu:597-903. */
+MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
+                     int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms);
+/* Run phases [phase_begin, phase_end) of one step (5 per layer: QKV, attention, O,
+ * gate/up, down; then the lm_head) one launch each, leaving the state buffers for
+ * inspection.  For per-phase parity checks. */
+MI_API int mi_decode_phases(mi_ctx* ctx, mi_model* model, int32_t token, int pos, int phase_begin, int phase_end);
 
 #ifdef __cplusplus
 }

@@ -51,7 +51,23 @@ SIGNATURES = {
     "mi_gemv_q4_q8_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32]),
     "mi_block_isums_q4_q8": (_i32, [_vp, _vp, _vp, _vp]),
     "mi_gemv_q4_f32_host": (_i32, [_vp, _vp, _vp, _vp, _vp]),
+    "mi_model_load_gguf": (_i32, [_vp, C.c_char_p, _i32, C.POINTER(_vp)]),
+    "mi_model_free": (_i32, [_vp, _vp]),
+    "mi_model_info": (_i32, [_vp, _vp]),
+    "mi_model_state_ptr": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
+    "mi_decode": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, C.POINTER(C.c_float)]),
+    "mi_decode_phases": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32]),
 }
+
+DECODE_PERSISTENT, DECODE_PER_PHASE = 0, 1
+STATE = {"h": 0, "q": 1, "att": 2, "kcache": 3, "vcache": 4, "act_q": 5, "act_d": 6}
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "n_ff", "n_head", "n_head_kv", "head_dim", "n_vocab",
+                                          "max_seq", "tied_lm_head", "grid_ctas")] + \
+               [("rope_base", C.c_float), ("rms_eps", C.c_float),
+                ("q4_weight_bytes_per_token", C.c_int64), ("kv_bytes_per_position", C.c_int64)]
 
 
 def load_library(path=None):
@@ -175,3 +191,62 @@ class Weight:
             self.free()
         except Exception:
             pass
+
+
+class Model:
+    """A loaded GGUF model with its KV cache and decode state: wraps mi_model."""
+
+    def __init__(self, ctx, path, max_seq):
+        self.ctx = ctx
+        h = _vp()
+        ctx.check(ctx.lib.mi_model_load_gguf(ctx.h, str(path).encode(), max_seq, C.byref(h)), "mi_model_load_gguf")
+        self.h = h
+        self.config = ModelConfig()
+        ctx.check(ctx.lib.mi_model_info(h, C.byref(self.config)), "mi_model_info")
+
+    def decode(self, in_tokens, n_steps, pos0=0, logits=None, mode=DECODE_PERSISTENT):
+        """Returns (greedy tokens after each step, device milliseconds)."""
+        import numpy as np
+        toks = np.ascontiguousarray(in_tokens, dtype=np.int32)
+        out = np.empty(max(n_steps, 1), dtype=np.int32)
+        ms = C.c_float(0)
+        self.ctx.check(self.ctx.lib.mi_decode(self.ctx.h, self.h, _ptr(toks) if toks.size else None, toks.size, n_steps, pos0,
+                                              _ptr(out), _ptr(logits), mode, C.byref(ms)), "mi_decode")
+        return out[:n_steps].tolist(), ms.value
+
+    def generate(self, prompt, n_gen, mode=DECODE_PERSISTENT):
+        """The reference CLI's output: n_gen greedy ids, the first predicted after the last prompt token."""
+        out, ms = self.decode(prompt, len(prompt) + n_gen - 1, 0, None, mode)
+        return out[len(prompt) - 1:], ms
+
+    def run_phases(self, token, pos, ph0, ph1):
+        self.ctx.check(self.ctx.lib.mi_decode_phases(self.ctx.h, self.h, token, pos, ph0, ph1), "mi_decode_phases")
+
+    def state(self, name, dtype, count):
+        """Copy of a state buffer as a numpy array."""
+        import numpy as np
+        p, n = _vp(), _i64()
+        self.ctx.check(self.ctx.lib.mi_model_state_ptr(self.h, STATE[name], C.byref(p), C.byref(n)), "mi_model_state_ptr")
+        self.ctx.sync()
+        nbytes = min(n.value, count * np.dtype(dtype).itemsize)
+        return _as_cuda_tensor(p.value, nbytes).cpu().numpy().view(dtype).copy()
+
+    def free(self):
+        if self.h and self.ctx.h:
+            self.ctx.lib.mi_model_free(self.ctx.h, self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _as_cuda_tensor(ptr, nbytes):
+    """A torch uint8 CUDA tensor aliasing raw device memory (no copy)."""
+    import torch
+
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None}
+    return torch.as_tensor(_Holder(), device="cuda")

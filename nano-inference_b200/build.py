@@ -57,12 +57,26 @@ def cuda_sources():
 
 
 def build_library(force=False, verbose=False, extra_flags=()):
+    """Each .cu becomes an object under build/ (recompiled only when it or a header
+    changed, several at a time), then one shared library is linked."""
+    from concurrent.futures import ThreadPoolExecutor
     srcs = cuda_sources()
-    deps = srcs + sorted(CSRC.glob("*.cuh")) + sorted(HOST.glob("*.hpp")) + [ROOT / "include" / "minfer_b200.h"]
-    if force or _newer(LIB, deps):
-        LIB.parent.mkdir(parents=True, exist_ok=True)
-        env_ccbin = ["-ccbin", GXX]
-        _run([_nvcc(), *NVCC_FLAGS, *env_ccbin, *extra_flags, "-I", ROOT / "include", "-I", HOST, "-o", LIB, *srcs], verbose)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(HOST.glob("*.hpp")) + [ROOT / "include" / "minfer_b200.h"]
+    objdir = PKG / "build"
+    objdir.mkdir(parents=True, exist_ok=True)
+    LIB.parent.mkdir(parents=True, exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f != "--shared"]
+    jobs = []
+    for s in srcs:
+        o = objdir / (s.stem + ".o")
+        if force or _newer(o, [s] + headers):
+            jobs.append([_nvcc(), *flags, "-ccbin", GXX, *extra_flags, "-I", ROOT / "include", "-I", HOST, "-c", "-o", o, s])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 1)) as ex:
+            list(ex.map(lambda c: _run(c, verbose), jobs))
+    objs = [objdir / (s.stem + ".o") for s in srcs]
+    if force or jobs or _newer(LIB, objs):
+        _run([_nvcc(), "--shared", "-ccbin", GXX, "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs], verbose)
     return LIB
 
 

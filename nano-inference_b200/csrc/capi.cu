@@ -14,16 +14,16 @@ int set_error(mi_ctx* ctx, int status, const char* fmt, ...) {
     return status;
 }
 
-int ensure_scratch(mi_ctx* ctx, size_t part_floats, size_t n_counters) {
-    if (part_floats > ctx->part_floats) {
+int ensure_scratch(mi_ctx* ctx, size_t part_count, size_t n_counters) {
+    if (part_count > ctx->part_count) {
         // the stream may still be using the old buffer
         MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         if (ctx->part) cudaFree(ctx->part);
-        ctx->part = nullptr; ctx->part_floats = 0;
-        size_t want = part_floats * 2;
-        cudaError_t e = cudaMalloc(&ctx->part, want * sizeof(float));
-        if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "scratch: cudaMalloc(%zu) failed: %s", want * sizeof(float), cudaGetErrorString(e));
-        ctx->part_floats = want;
+        ctx->part = nullptr; ctx->part_count = 0;
+        size_t want = part_count * 2;
+        cudaError_t e = cudaMalloc(&ctx->part, want * sizeof(double));
+        if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "scratch: cudaMalloc(%zu) failed: %s", want * sizeof(double), cudaGetErrorString(e));
+        ctx->part_count = want;
     }
     if (n_counters > ctx->n_counters) {
         MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));

@@ -1,0 +1,418 @@
+// Model loading (GGUF -> tiled device layout), job planning and launching of the
+// fused decode kernel; the model / decode part of the C ABI.
+#include "decode_kernel.cuh"
+#include "gguf_file.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <new>
+#include <string>
+#include <vector>
+
+using namespace mi;
+
+struct mi_model {
+    int device = 0;
+    int L = 0, E = 0, FF = 0, NH = 0, NKV = 0, HD = 0, KVD = 0, V = 0, G = 0;
+    float eps = 1e-6f, rope_base = 1e6f;
+    int max_seq = 0, grid = 0, max_chunks = 0;
+    bool tied = false;
+    int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)
+    std::vector<void*> allocs;            // everything cudaMalloc'ed for this model
+    std::vector<Job> jobs;
+    DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
+    int* d_in_tokens = nullptr; int in_capacity = 0;
+    int* d_out_tokens = nullptr; int out_capacity = 0;
+    size_t smem = 0;
+    size_t part_count = 0, n_counters = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+};
+
+namespace {
+
+template <typename T>
+int dev_alloc(mi_ctx* ctx, mi_model* m, T** p, size_t n, bool zero = true) {
+    *p = nullptr;
+    if (n == 0) n = 1;
+    cudaError_t e = cudaMalloc((void**)p, n * sizeof(T));
+    if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: cudaMalloc(%zu) failed: %s", n * sizeof(T), cudaGetErrorString(e));
+    m->allocs.push_back(*p);
+    if (zero) { e = cudaMemset(*p, 0, n * sizeof(T)); if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "model: cudaMemset failed"); }
+    return MI_OK;
+}
+
+struct Staging {       // one reusable device buffer for raw GGUF bytes
+    void* d = nullptr; size_t cap = 0;
+    ~Staging() { if (d) cudaFree(d); }
+    int put(mi_ctx* ctx, const void* src, size_t n) {
+        if (n > cap) {
+            if (d) { cudaStreamSynchronize(ctx->stream); cudaFree(d); d = nullptr; cap = 0; }
+            cudaError_t e = cudaMalloc(&d, n);
+            if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: staging cudaMalloc(%zu) failed", n);
+            cap = n;
+        }
+        // the previous repack (same stream) must be done with the buffer before it is overwritten
+        MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        MI_CUDA(ctx, cudaMemcpy(d, src, n, cudaMemcpyHostToDevice));
+        return MI_OK;
+    }
+};
+
+const mib200::GgufTensor* need(mi_ctx* ctx, const mib200::GgufFile& g, const std::string& name, uint32_t type,
+                               int64_t cols, int64_t rows, int* st) {
+    const mib200::GgufTensor* t = g.find(name);
+    if (!t) { *st = set_error(ctx, MI_ERR_FORMAT, "model: tensor not found: %s", name.c_str()); return nullptr; }
+    if (t->type != type) {
+        *st = set_error(ctx, MI_ERR_UNSUPPORTED, "model: tensor %s has ggml type %u, this path takes %s only", name.c_str(), t->type,
+                        type == mib200::GGML_Q4_0 ? "Q4_0" : "F32");
+        return nullptr;
+    }
+    if (t->cols() != cols || t->rows() != rows) {
+        *st = set_error(ctx, MI_ERR_FORMAT, "model: tensor %s is %lld x %lld, expected %lld x %lld", name.c_str(),
+                        (long long)t->rows(), (long long)t->cols(), (long long)rows, (long long)cols);
+        return nullptr;
+    }
+    return t;
+}
+
+// Tiled buffer for `rows` packed rows of `cols` columns, zero-filled.
+int alloc_tiled(mi_ctx* ctx, mi_model* m, int64_t rows, int64_t cols, uint8_t** out, int* kb_out, int* nt_out) {
+    const int nb = (int)(cols / 32), kb = choose_kb(nb), nt = nb / kb;
+    const size_t groups = (size_t)((rows + 31) / 32);
+    *kb_out = kb; *nt_out = nt;
+    return dev_alloc(ctx, m, out, groups * nt * tile_bytes(kb), true);
+}
+
+// Cost model for the K-split of one job (smaller is better): the slowest warp's tile
+// count against the busiest SM's share of the stream, plus a charge for the fold.
+int plan_ks(int groups, int nt, int nacc, int rot, int grid) {
+    const int W = grid * DNW;
+    double best_cost = 1e30; int best = 1;
+    std::vector<int> warp_tiles(W), cta_tiles(grid);
+    for (int ks = 1; ks <= std::min(nt, 40); ks++) {
+        std::fill(warp_tiles.begin(), warp_tiles.end(), 0);
+        std::fill(cta_tiles.begin(), cta_tiles.end(), 0);
+        const long long n_units = (long long)groups * ks;
+        for (long long u = 0; u < n_units; u++) {
+            const int sp = (int)(u % ks), t0 = (int)((long long)sp * nt / ks), t1 = (int)((long long)(sp + 1) * nt / ks);
+            const int slot = (int)((u + rot) % W);
+            warp_tiles[slot] += nacc * (t1 - t0);
+            cta_tiles[slot % grid] += nacc * (t1 - t0);
+        }
+        const int mw = *std::max_element(warp_tiles.begin(), warp_tiles.end());
+        const int mc = *std::max_element(cta_tiles.begin(), cta_tiles.end());
+        double cost = std::max(0.20 * mw, 0.105 * mc) + (ks > 1 ? 0.25 + 0.03 * ks : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
+    }
+    return best;
+}
+
+int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
+    void (*kern)(DecodeParams, int, int, int, int) = nullptr;
+    #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
+    MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
+    #undef MI_PICK
+    if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: head_dim %d with %d query heads per kv head is not instantiated", m->HD, m->G);
+    static const void* attr_done[16] = {nullptr};
+    if (attr_done[ctx->device & 15] != (const void*)kern) {
+        MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem));
+        attr_done[ctx->device & 15] = (const void*)kern;
+    }
+    if (coop) {
+        void* args[] = {(void*)&P, &step0, &step1, &ph0, &ph1};
+        MI_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)kern, dim3(m->grid), dim3(DNT), args, m->smem, ctx->stream));
+    } else {
+        kern<<<m->grid, DNT, m->smem, ctx->stream>>>(P, step0, step1, ph0, ph1);
+        MI_CUDA(ctx, cudaGetLastError());
+    }
+    return MI_OK;
+}
+
+}  // namespace
+
+extern "C" int mi_model_free(mi_ctx* ctx, mi_model* m) {
+    (void)ctx;
+    if (!m) return MI_OK;
+    cudaSetDevice(m->device);
+    cudaDeviceSynchronize();
+    for (void* p : m->allocs) cudaFree(p);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    delete m;
+    return MI_OK;
+}
+
+extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi_model** out) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!out || !path) return set_error(ctx, MI_ERR_INVALID, "model: null argument");
+    *out = nullptr;
+    if (max_seq <= 0) return set_error(ctx, MI_ERR_INVALID, "model: max_seq must be positive");
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    mib200::GgufFile g;
+    std::string err = g.open(path);
+    if (!err.empty()) {
+        const bool io = err.rfind("cannot", 0) == 0 || err.rfind("mmap", 0) == 0;
+        return set_error(ctx, io ? MI_ERR_IO : MI_ERR_FORMAT, "model: %s", err.c_str());
+    }
+    mi_model* m = new (std::nothrow) mi_model();
+    if (!m) return set_error(ctx, MI_ERR_NOMEM, "model: host allocation failed");
+    struct Guard { mi_ctx* c; mi_model* m; bool keep = false; ~Guard() { if (!keep) mi_model_free(c, m); } } guard{ctx, m};
+    m->device = ctx->device;
+    // hyper-parameters: the keys the reference drivers read (src/cpu_infer.cpp:71-79)
+    m->L = (int)g.num("qwen2.block_count", 0);
+    m->E = (int)g.num("qwen2.embedding_length", 0);
+    m->FF = (int)g.num("qwen2.feed_forward_length", 0);
+    m->NH = (int)g.num("qwen2.attention.head_count", 0);
+    m->NKV = (int)g.num("qwen2.attention.head_count_kv", 0);
+    m->rope_base = (float)g.num("qwen2.rope.freq_base", 1e6);
+    m->eps = (float)g.num("qwen2.attention.layer_norm_rms_epsilon", 1e-6);
+    m->V = (int)g.n_tokens();
+    if (m->L <= 0 || m->E <= 0 || m->FF <= 0 || m->NH <= 0 || m->NKV <= 0 || m->V <= 0)
+        return set_error(ctx, MI_ERR_FORMAT, "model: missing qwen2.* metadata or tokenizer.ggml.tokens");
+    if (m->E % m->NH || m->NH % m->NKV) return set_error(ctx, MI_ERR_FORMAT, "model: head counts do not divide");
+    m->HD = m->E / m->NH; m->KVD = m->NKV * m->HD; m->G = m->NH / m->NKV;
+    if (m->E % 32 || m->FF % 32 || m->HD % 32 || m->G > DNW || m->L > 64 || m->E > 16384 || m->FF > 32768)
+        return set_error(ctx, MI_ERR_UNSUPPORTED, "model: shape outside this path (E, FF, head_dim multiples of 32; <= 8 query heads per kv head)");
+    m->max_seq = max_seq;
+    m->grid = ctx->sm_count;
+    if (const char* gs = getenv("MINFER_GRID")) { int v = atoi(gs); if (v > 0 && v <= ctx->sm_count) m->grid = v; }
+    m->max_chunks = std::max(1, m->grid / m->NKV);
+
+    const int E = m->E, FF = m->FF, HD = m->HD, KVD = m->KVD, L = m->L, V = m->V, NQ = m->NH * m->HD;
+    int st = MI_OK;
+    Staging stg;
+    DecodeParams& P = m->P;
+    P.L = L; P.E = E; P.FF = FF; P.NH = m->NH; P.NKV = m->NKV; P.HD = HD; P.KVD = KVD; P.V = V; P.eps = m->eps;
+
+    // ---- row maps (device): q/k rows pair-adjacent for RoPE, gate/up groups interleaved
+    auto rope_map = [&](int nheads, int offset) {
+        std::vector<int> mp((size_t)nheads * HD);
+        for (int h = 0; h < nheads; h++)
+            for (int i = 0; i < HD / 2; i++) {
+                mp[(size_t)h * HD + i] = offset + h * HD + 2 * i;                 // source row (h, i)        -> even slot
+                mp[(size_t)h * HD + i + HD / 2] = offset + h * HD + 2 * i + 1;   // source row (h, i + HD/2) -> odd slot
+            }
+        return mp;
+    };
+    std::vector<int> mq = rope_map(m->NH, 0), mk = rope_map(m->NKV, NQ), mg((size_t)FF), mu((size_t)FF);
+    for (int r = 0; r < FF; r++) { mg[r] = (r / 32) * 64 + r % 32; mu[r] = (r / 32) * 64 + 32 + r % 32; }
+    int *d_mq, *d_mk, *d_mg, *d_mu;
+    if ((st = dev_alloc(ctx, m, &d_mq, mq.size())) || (st = dev_alloc(ctx, m, &d_mk, mk.size())) ||
+        (st = dev_alloc(ctx, m, &d_mg, mg.size())) || (st = dev_alloc(ctx, m, &d_mu, mu.size()))) return st;
+    MI_CUDA(ctx, cudaMemcpy(d_mq, mq.data(), mq.size() * 4, cudaMemcpyHostToDevice));
+    MI_CUDA(ctx, cudaMemcpy(d_mk, mk.data(), mk.size() * 4, cudaMemcpyHostToDevice));
+    MI_CUDA(ctx, cudaMemcpy(d_mg, mg.data(), mg.size() * 4, cudaMemcpyHostToDevice));
+    MI_CUDA(ctx, cudaMemcpy(d_mu, mu.data(), mu.size() * 4, cudaMemcpyHostToDevice));
+
+    auto upload_f32 = [&](const mib200::GgufTensor* t, float** dst, size_t padded) -> int {
+        int s = dev_alloc(ctx, m, dst, padded, true);
+        if (s) return s;
+        MI_CUDA(ctx, cudaMemcpy(*dst, t->data, (size_t)t->cols() * 4, cudaMemcpyHostToDevice));
+        return MI_OK;
+    };
+    auto repack = [&](const mib200::GgufTensor* t, uint8_t* dst, const int* map, int offset) -> int {
+        int s = stg.put(ctx, t->data, t->nbytes());
+        if (s) return s;
+        return launch_repack_map(ctx, stg.d, t->rows(), (int)(t->cols() / 32), choose_kb((int)(t->cols() / 32)), dst, map, offset);
+    };
+
+    // ---- embedding / lm_head
+    const mib200::GgufTensor* te = need(ctx, g, "token_embd.weight", mib200::GGML_Q4_0, E, V, &st); if (!te) return st;
+    const mib200::GgufTensor* tl = g.find("output.weight");            // optional: tied to the embedding when absent
+    m->tied = !tl || (tl->type == te->type && tl->nbytes() == te->nbytes() && memcmp(tl->data, te->data, te->nbytes()) == 0);
+    if (tl && !m->tied) { tl = need(ctx, g, "output.weight", mib200::GGML_Q4_0, E, V, &st); if (!tl) return st; }
+    uint8_t *d_emb = nullptr, *d_lm = nullptr; int ekb, ent;
+    if ((st = alloc_tiled(ctx, m, V, E, &d_emb, &ekb, &ent))) return st;
+    if ((st = repack(te, d_emb, nullptr, 0))) return st;
+    d_lm = d_emb;
+    if (!m->tied) { if ((st = alloc_tiled(ctx, m, V, E, &d_lm, &ekb, &ent))) return st; if ((st = repack(tl, d_lm, nullptr, 0))) return st; }
+    P.emb_base = d_emb; P.emb_kb = ekb; P.emb_nt = ent;
+    const mib200::GgufTensor* tn = need(ctx, g, "output_norm.weight", mib200::GGML_F32, E, 1, &st); if (!tn) return st;
+    float* d_outnorm; if ((st = upload_f32(tn, &d_outnorm, E))) return st;
+    P.out_norm = d_outnorm;
+
+    // ---- layers
+    std::vector<LayerPtrs> lp(L);
+    const int qkv_rows = NQ + 2 * KVD, W = m->grid * DNW;
+    int rot = 0; size_t part_off = 0, cnt_off = 0;
+    auto add_job = [&](const uint8_t* base, int groups, int cols, int nacc, int kind, int layer) {
+        Job jb{}; jb.base = base; jb.groups = groups; jb.nb = cols / 32; jb.kb = choose_kb(jb.nb); jb.nt = jb.nb / jb.kb;
+        jb.nacc = nacc; jb.kind = kind; jb.layer = layer; jb.rot = rot;
+        const char* force = getenv("MINFER_KS");
+        jb.ks = force ? std::max(1, std::min(atoi(force), jb.nt)) : plan_ks(groups, jb.nt, nacc, rot, m->grid);
+        jb.n_units = groups * jb.ks;
+        jb.part_off = (int)part_off; jb.cnt_off = (int)cnt_off;
+        part_off += (size_t)groups * jb.ks * nacc * 32; cnt_off += (size_t)groups;
+        rot = (int)(((long long)rot + jb.n_units) % W);
+        m->jobs.push_back(jb);
+    };
+    for (int l = 0; l < L; l++) {
+        const std::string p = "blk." + std::to_string(l) + ".";
+        const mib200::GgufTensor *an, *fn, *wq, *wk, *wv, *wo, *wg, *wu, *wd, *bq, *bk, *bv;
+        if (!(an = need(ctx, g, p + "attn_norm.weight", mib200::GGML_F32, E, 1, &st))) return st;
+        if (!(fn = need(ctx, g, p + "ffn_norm.weight", mib200::GGML_F32, E, 1, &st))) return st;
+        if (!(wq = need(ctx, g, p + "attn_q.weight", mib200::GGML_Q4_0, E, NQ, &st))) return st;
+        if (!(wk = need(ctx, g, p + "attn_k.weight", mib200::GGML_Q4_0, E, KVD, &st))) return st;
+        if (!(wv = need(ctx, g, p + "attn_v.weight", mib200::GGML_Q4_0, E, KVD, &st))) return st;
+        if (!(wo = need(ctx, g, p + "attn_output.weight", mib200::GGML_Q4_0, NQ, E, &st))) return st;
+        if (!(wg = need(ctx, g, p + "ffn_gate.weight", mib200::GGML_Q4_0, E, FF, &st))) return st;
+        if (!(wu = need(ctx, g, p + "ffn_up.weight", mib200::GGML_Q4_0, E, FF, &st))) return st;
+        if (!(wd = need(ctx, g, p + "ffn_down.weight", mib200::GGML_Q4_0, FF, E, &st))) return st;
+        if (!(bq = need(ctx, g, p + "attn_q.bias", mib200::GGML_F32, NQ, 1, &st))) return st;
+        if (!(bk = need(ctx, g, p + "attn_k.bias", mib200::GGML_F32, KVD, 1, &st))) return st;
+        if (!(bv = need(ctx, g, p + "attn_v.bias", mib200::GGML_F32, KVD, 1, &st))) return st;
+        float *d_an, *d_fn, *d_b;
+        if ((st = upload_f32(an, &d_an, E)) || (st = upload_f32(fn, &d_fn, E))) return st;
+        // fused bias in packed row order
+        std::vector<float> hb((size_t)(qkv_rows + 31) / 32 * 32, 0.f);
+        const float *fq = (const float*)bq->data, *fk = (const float*)bk->data, *fv = (const float*)bv->data;
+        for (int r = 0; r < NQ; r++) hb[mq[r]] = fq[r];
+        for (int r = 0; r < KVD; r++) hb[mk[r]] = fk[r];
+        for (int r = 0; r < KVD; r++) hb[NQ + KVD + r] = fv[r];
+        if ((st = dev_alloc(ctx, m, &d_b, hb.size()))) return st;
+        MI_CUDA(ctx, cudaMemcpy(d_b, hb.data(), hb.size() * 4, cudaMemcpyHostToDevice));
+        lp[l] = LayerPtrs{d_an, d_fn, d_b};
+        uint8_t *d_qkv, *d_o, *d_gu, *d_dn; int kb, nt;
+        if ((st = alloc_tiled(ctx, m, qkv_rows, E, &d_qkv, &kb, &nt))) return st;
+        if ((st = repack(wq, d_qkv, d_mq, 0)) || (st = repack(wk, d_qkv, d_mk, 0)) || (st = repack(wv, d_qkv, nullptr, NQ + KVD))) return st;
+        if ((st = alloc_tiled(ctx, m, E, NQ, &d_o, &kb, &nt)) || (st = repack(wo, d_o, nullptr, 0))) return st;
+        if ((st = alloc_tiled(ctx, m, 2 * (int64_t)FF, E, &d_gu, &kb, &nt))) return st;
+        if ((st = repack(wg, d_gu, d_mg, 0)) || (st = repack(wu, d_gu, d_mu, 0))) return st;
+        if ((st = alloc_tiled(ctx, m, E, FF, &d_dn, &kb, &nt)) || (st = repack(wd, d_dn, nullptr, 0))) return st;
+        add_job(d_qkv, (qkv_rows + 31) / 32, E, 1, JOB_QKV, l);
+        add_job(d_o, (E + 31) / 32, NQ, 1, JOB_O, l);
+        add_job(d_gu, FF / 32, E, 2, JOB_GU, l);
+        add_job(d_dn, (E + 31) / 32, FF, 1, JOB_DOWN, l);
+        m->weight_bytes_q4 += ((int64_t)NQ * E + 2 * (int64_t)KVD * E + (int64_t)E * NQ + 3 * (int64_t)FF * E) / 32 * 18;
+    }
+    add_job(d_lm, (V + 31) / 32, E, 1, JOB_LM, L);
+    m->weight_bytes_q4 += (int64_t)V * E / 32 * 18;
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+
+    LayerPtrs* d_lp; Job* d_jobs;
+    if ((st = dev_alloc(ctx, m, &d_lp, lp.size())) || (st = dev_alloc(ctx, m, &d_jobs, m->jobs.size()))) return st;
+    MI_CUDA(ctx, cudaMemcpy(d_lp, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice));
+    MI_CUDA(ctx, cudaMemcpy(d_jobs, m->jobs.data(), m->jobs.size() * sizeof(Job), cudaMemcpyHostToDevice));
+    P.layers = d_lp; P.jobs = d_jobs;
+
+    // rope frequencies exactly as the reference computes them on the host: powf(base, -2i/hd) (src/cpu_infer.cpp:54)
+    std::vector<float> freq(HD / 2);
+    for (int i = 0; i < HD / 2; i++) freq[i] = std::pow(m->rope_base, -2.f * i / HD);
+    float* d_freq; if ((st = dev_alloc(ctx, m, &d_freq, freq.size()))) return st;
+    MI_CUDA(ctx, cudaMemcpy(d_freq, freq.data(), freq.size() * 4, cudaMemcpyHostToDevice));
+    P.rope_freq = d_freq;
+
+    // ---- state
+    m->part_count = part_off; m->n_counters = cnt_off;
+    if ((st = dev_alloc(ctx, m, &P.h, E)) || (st = dev_alloc(ctx, m, &P.q, NQ)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
+        (st = dev_alloc(ctx, m, &P.att_q, NQ)) || (st = dev_alloc(ctx, m, &P.att_d, NQ / 32)) ||
+        (st = dev_alloc(ctx, m, &P.act_q, FF)) || (st = dev_alloc(ctx, m, &P.act_d, FF / 32)) ||
+        (st = dev_alloc(ctx, m, &P.kc, (size_t)L * max_seq * KVD)) || (st = dev_alloc(ctx, m, &P.vc, (size_t)L * max_seq * KVD)) ||
+        (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NKV)) ||
+        (st = dev_alloc(ctx, m, &P.part, part_off)) || (st = dev_alloc(ctx, m, &P.counters, cnt_off)) ||
+        (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
+        (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 1)))
+        return st;
+    P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
+    m->smem = decode_smem_bytes((int)m->jobs.size(), E, FF, HD, m->G);
+    if (m->smem > (size_t)ctx->smem_optin)
+        return set_error(ctx, MI_ERR_UNSUPPORTED, "model: decode kernel needs %zu bytes of shared memory, %d available", m->smem, ctx->smem_optin);
+    MI_CUDA(ctx, cudaEventCreate(&m->ev0));
+    MI_CUDA(ctx, cudaEventCreate(&m->ev1));
+    guard.keep = true;
+    *out = m;
+    return MI_OK;
+}
+
+extern "C" int mi_model_info(const mi_model* m, mi_model_config* c) {
+    if (!m || !c) return MI_ERR_INVALID;
+    c->n_layer = m->L; c->n_embd = m->E; c->n_ff = m->FF; c->n_head = m->NH; c->n_head_kv = m->NKV; c->head_dim = m->HD;
+    c->n_vocab = m->V; c->max_seq = m->max_seq; c->tied_lm_head = m->tied ? 1 : 0; c->grid_ctas = m->grid;
+    c->rope_base = m->rope_base; c->rms_eps = m->eps;
+    c->q4_weight_bytes_per_token = m->weight_bytes_q4;
+    c->kv_bytes_per_position = (int64_t)2 * m->L * m->KVD * 2;
+    return MI_OK;
+}
+
+extern "C" int mi_model_state_ptr(const mi_model* m, int which, void** ptr, int64_t* bytes) {
+    if (!m || !ptr) return MI_ERR_INVALID;
+    const DecodeParams& P = m->P;
+    const int NQ = m->NH * m->HD;
+    switch (which) {
+        case MI_STATE_H: *ptr = P.h; if (bytes) *bytes = (int64_t)m->E * 4; break;
+        case MI_STATE_Q: *ptr = P.q; if (bytes) *bytes = (int64_t)NQ * 4; break;
+        case MI_STATE_ATT: *ptr = P.att; if (bytes) *bytes = (int64_t)NQ * 4; break;
+        case MI_STATE_KCACHE: *ptr = P.kc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
+        case MI_STATE_VCACHE: *ptr = P.vc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
+        case MI_STATE_ACT_Q: *ptr = P.act_q; if (bytes) *bytes = (int64_t)m->FF; break;
+        case MI_STATE_ACT_D: *ptr = P.act_d; if (bytes) *bytes = (int64_t)m->FF / 32 * 2; break;
+        default: return MI_ERR_INVALID;
+    }
+    return MI_OK;
+}
+
+static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
+                       int32_t* out_tokens_host, float* logits_dev, int mode, int ph0, int ph1, float* elapsed_ms) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "decode: null model");
+    if (n_steps < 0 || n_forced < 0 || pos0 < 0) return set_error(ctx, MI_ERR_INVALID, "decode: negative count");
+    if (n_steps == 0) { if (elapsed_ms) *elapsed_ms = 0.f; return MI_OK; }
+    if (n_forced > n_steps) n_forced = n_steps;
+    if (n_forced > 0 && !in_tokens_host) return set_error(ctx, MI_ERR_INVALID, "decode: null input tokens");
+    if (pos0 + n_steps > m->max_seq)
+        return set_error(ctx, MI_ERR_LIMIT, "decode: positions %d..%d exceed the KV cache of %d", pos0, pos0 + n_steps - 1, m->max_seq);
+    for (int i = 0; i < n_forced; i++)
+        if (in_tokens_host[i] < 0 || in_tokens_host[i] >= m->V) return set_error(ctx, MI_ERR_INVALID, "decode: token id %d out of range", in_tokens_host[i]);
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    int st;
+    if (n_forced > m->in_capacity) {
+        if ((st = dev_alloc(ctx, m, &m->d_in_tokens, (size_t)n_forced * 2))) return st;
+        m->in_capacity = n_forced * 2;
+    }
+    if (n_steps > m->out_capacity) {
+        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, (size_t)n_steps * 2))) return st;
+        m->out_capacity = n_steps * 2;
+    }
+    if (n_forced) MI_CUDA(ctx, cudaMemcpyAsync(m->d_in_tokens, in_tokens_host, (size_t)n_forced * 4, cudaMemcpyHostToDevice, ctx->stream));
+    DecodeParams P = m->P;
+    P.in_tokens = m->d_in_tokens; P.n_forced = n_forced; P.out_tokens = m->d_out_tokens; P.pos0 = pos0;
+    P.logits = logits_dev; P.logits_stride = m->V;
+    const int nph = 5 * m->L + 1;
+    MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    if (mode == MI_DECODE_PERSISTENT) {
+        MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, sizeof(unsigned), ctx->stream));
+        if ((st = dispatch_launch(ctx, m, P, 0, n_steps, 0, nph, true))) return st;
+    } else if (mode == MI_DECODE_PER_PHASE) {
+        for (int s = 0; s < n_steps; s++) {
+            DecodeParams Ps = P;
+            if (Ps.logits) Ps.logits += (long long)s * Ps.logits_stride;    // the kernel indexes logits from its first step
+            for (int ph = ph0; ph < ph1; ph++)
+                if ((st = dispatch_launch(ctx, m, Ps, s, s + 1, ph, ph + 1, false))) return st;
+        }
+    } else {
+        return set_error(ctx, MI_ERR_INVALID, "decode: unknown mode %d", mode);
+    }
+    MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    if (out_tokens_host)
+        MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, m->d_out_tokens, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    st = mi_ctx_sync(ctx);
+    if (st != MI_OK) return st;
+    if (elapsed_ms) MI_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, m->ev0, m->ev1));
+    return MI_OK;
+}
+
+extern "C" int mi_decode(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
+                         int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms) {
+    return decode_impl(ctx, m, in_tokens_host, n_forced, n_steps, pos0, out_tokens_host, logits_dev, mode, 0,
+                       m ? 5 * m->L + 1 : 0, elapsed_ms);
+}
+
+extern "C" int mi_decode_phases(mi_ctx* ctx, mi_model* m, int32_t token, int pos, int phase_begin, int phase_end) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "decode: null model");
+    const int nph = 5 * m->L + 1;
+    if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end) return set_error(ctx, MI_ERR_INVALID, "decode: bad phase range");
+    int32_t out;
+    return decode_impl(ctx, m, &token, 1, 1, pos, &out, nullptr, MI_DECODE_PER_PHASE, phase_begin, phase_end, nullptr);
+}

@@ -12,6 +12,8 @@
 // the nibbles, broadcast reads for the int8 activations.  No cross-lane
 // reduction is needed; K-splits meet in global scratch and the last split to
 // arrive adds them in split order, so the result does not depend on timing.
+// Sums are carried in double (see blk_acc): the fp32 result does not depend on
+// the split either.
 //
 // HBM traffic per weight byte is exactly one read; the tile stream is the only
 // traffic that scales with the matrix.
@@ -28,7 +30,7 @@ struct GemvShape {
 };
 
 struct GemvScratch {
-    float* part;              // [n_mats*groups][ks][32] partial sums (ks > 1 only)
+    double* part;             // [n_mats*groups][ks][32] partial sums (ks > 1 only)
     unsigned* counters;       // [n_mats*groups] arrivals, zero between launches
 };
 
@@ -93,8 +95,8 @@ __device__ __forceinline__ void load_tile_scales(const uint8_t* tile, int lane, 
 // DUMP writes the exact integer block values to isum_row[b] instead of relying
 // on the float result.
 template <int KB, bool DUMP>
-__device__ __forceinline__ float tile_dot_row(const uint8_t* tile, int lane, int b0, const int8_t* xq_s,
-                                              const float2* xs_s, float acc, int32_t* isum_row) {
+__device__ __forceinline__ double tile_dot_row(const uint8_t* tile, int lane, int b0, const int8_t* xq_s,
+                                               const float2* xs_s, double acc, int32_t* isum_row) {
     float dw[KB];
     load_tile_scales<KB>(tile, lane, dw);
     const uint4* wq = reinterpret_cast<const uint4*>(tile) + lane;
@@ -128,7 +130,7 @@ __device__ __forceinline__ void stage_x_q8(const int8_t* xq, const __half* xd, i
 // (gemv_init_barriers), weights prefetch started (gemv_prefetch) and the
 // activations staged in shared memory behind a __syncthreads().
 //   epi(c, g, lane, value) is called by all 32 lanes once per (matrix, group)
-//   with the complete fp32 sum of row g*32+lane.
+//   with the complete sum of row g*32+lane, rounded to fp32 once.
 // Returns false if a bounded wait gave up.
 template <int KB, int NW, int S>
 struct GemvWarp {
@@ -176,7 +178,7 @@ struct GemvWarp {
                                         const float2* xs_s, int lane, int32_t* isum_out, Epi epi) {
         bool ok = true;
         while (cc.u < n_units && ok) {
-            float acc = 0.f;
+            double acc = 0.0;
             int32_t* isum_row = (DUMP && cc.g * 32 + lane < sh.rows) ? isum_out + ((size_t)cc.g * 32 + lane) * sh.nb : nullptr;
             for (int t = cc.t; t < cc.t1; t++) {
                 const int slot = consumed % S;
@@ -189,9 +191,9 @@ struct GemvWarp {
             if (!ok) break;
             const int cg = cc.c * sh.groups + cc.g;
             if (sh.ks == 1) {
-                epi(cc.c, cc.g, lane, acc);
+                epi(cc.c, cc.g, lane, __double2float_rn(acc));
             } else {
-                float* part = sc.part + ((size_t)cg * sh.ks) * 32;
+                double* part = sc.part + ((size_t)cg * sh.ks) * 32;
                 __stcg(part + cc.sp * 32 + lane, acc);
                 __threadfence();
                 __syncwarp();
@@ -200,10 +202,10 @@ struct GemvWarp {
                 prev = __shfl_sync(0xffffffffu, prev, 0);
                 if (prev == (unsigned)sh.ks - 1) {          // last split to arrive folds all of them, in split order
                     __threadfence();
-                    float sum = __ldcg(part + lane);
-                    for (int s = 1; s < sh.ks; s++) sum = __fadd_rn(sum, __ldcg(part + s * 32 + lane));
+                    double sum = __ldcg(part + lane);
+                    for (int s = 1; s < sh.ks; s++) sum = __dadd_rn(sum, __ldcg(part + s * 32 + lane));
                     if (lane == 0) sc.counters[cg] = 0;   // ready for the next launch
-                    epi(cc.c, cc.g, lane, sum);
+                    epi(cc.c, cc.g, lane, __double2float_rn(sum));
                 }
             }
             cursor_set<KB>(cc, cc.u + stride, n_units, sh);

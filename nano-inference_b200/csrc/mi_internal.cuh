@@ -17,7 +17,7 @@ struct mi_ctx {
     int smem_optin = 0;
     int* d_err = nullptr;            // device error word (0 = none)
     // scratch of the split-K GEMV: partial sums and self-resetting arrival counters
-    float* part = nullptr; size_t part_floats = 0;
+    double* part = nullptr; size_t part_count = 0;
     unsigned* counters = nullptr; size_t n_counters = 0;
     // staging for the host-buffer convenience calls
     void* h_pinned = nullptr; size_t h_pinned_bytes = 0;
@@ -47,8 +47,10 @@ __host__ __device__ constexpr int tile_bytes(int kb) { return kb * kTileRowBytes
 inline int choose_kb(int nb) { return nb % 8 == 0 ? 8 : nb % 4 == 0 ? 4 : nb % 2 == 0 ? 2 : 1; }
 
 int set_error(mi_ctx* ctx, int status, const char* fmt, ...);
-int ensure_scratch(mi_ctx* ctx, size_t part_floats, size_t n_counters);
+int ensure_scratch(mi_ctx* ctx, size_t part_count, size_t n_counters);
 int ensure_staging(mi_ctx* ctx, size_t host_bytes, size_t dev_bytes);
+int launch_repack_map(mi_ctx* ctx, const void* raw_dev, long long src_rows, int nb, int kb, uint8_t* tiled,
+                      const int* dst_row_dev, int row_offset);
 
 #define MI_CUDA(ctx, call)                                                                    \
     do {                                                                                      \
@@ -132,12 +134,15 @@ __device__ __forceinline__ int sum_x_block(const int4 xa, const int4 xc) {
     s = __dp4a(0x01010101, xc.z, s); s = __dp4a(0x01010101, xc.w, s);
     return s;
 }
-// acc + (dw*dx) * float(isum - s8) with every rounding spelled out (reference
-// src/mega.cu:151-155).  s8f = float(8*sum x) is exact, and so is the fp32
-// difference (both magnitudes are far below 2^24), hence
-// float(isum) - s8f == float(isum - s8).
-__device__ __forceinline__ float blk_acc(float acc, float dw, float dx, int isum, float s8f) {
-    return __fmaf_rn(__fmul_rn(dw, dx), __fsub_rn(__int2float_rn(isum), s8f), acc);
+// acc + (dw*dx) * (isum - s8), carried in double.  dw and dx are fp16 values, so
+// their fp32 product is exact; isum and s8f = float(8*sum x) are integers far below
+// 2^24, so their fp32 difference is exact; the product of the two is exact in
+// double.  Only the running sum rounds (to 53 bits), which makes the fp32 value
+// of the final sum independent of the order in which blocks are added - K-splits,
+// multi-token steps and tensor-parallel shards all give the same bits.  The
+// formula is the reference's (src/cuda_infer.cu:122, src/mega.cu:151-155).
+__device__ __forceinline__ double blk_acc(double acc, float dw, float dx, int isum, float s8f) {
+    return __fma_rn((double)__fmul_rn(dw, dx), (double)__fsub_rn(__int2float_rn(isum), s8f), acc);
 }
 
 #endif  // __CUDACC__

@@ -28,6 +28,37 @@ __global__ void repack_q4_0_kernel(const uint16_t* __restrict__ raw, uint8_t* __
     *reinterpret_cast<uint16_t*>(tile + (size_t)kb * 512 + ((size_t)r * kb + k) * 2) = d;
 }
 
+// Same scatter with an explicit destination row per source row (dst_row[p], or
+// p + row_offset when dst_row is null): used to build fused matrices whose rows
+// are permuted or interleaved (Q/K rows pair-adjacent for RoPE, gate/up groups
+// alternating).  The destination must have been zero-filled (padding rows keep scale 0).
+__global__ void repack_q4_0_map_kernel(const uint16_t* __restrict__ raw, uint8_t* __restrict__ tiled, long long src_rows,
+                                       int nb, int kb, int nt, const int* __restrict__ dst_row, int row_offset) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= src_rows * nb) return;
+    const int b = (int)(idx % nb);
+    const long long p = idx / nb;
+    const long long P = dst_row ? dst_row[p] : p + row_offset;
+    const int g = (int)(P / 32), r = (int)(P % 32), t = b / kb, k = b % kb;
+    const uint16_t* src = raw + (p * nb + b) * 9;
+    uint32_t q[4];
+    #pragma unroll
+    for (int i = 0; i < 4; i++) q[i] = (uint32_t)src[1 + 2 * i] | ((uint32_t)src[2 + 2 * i] << 16);
+    uint8_t* tile = tiled + ((size_t)g * nt + t) * tile_bytes(kb);
+    *reinterpret_cast<uint4*>(tile + ((size_t)k * 32 + r) * 16) = make_uint4(q[0], q[1], q[2], q[3]);
+    *reinterpret_cast<uint16_t*>(tile + (size_t)kb * 512 + ((size_t)r * kb + k) * 2) = src[0];
+}
+
+int launch_repack_map(mi_ctx* ctx, const void* raw_dev, long long src_rows, int nb, int kb, uint8_t* tiled,
+                      const int* dst_row_dev, int row_offset) {
+    const long long n = src_rows * nb;
+    if (n == 0) return MI_OK;
+    repack_q4_0_map_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const uint16_t*>(raw_dev), tiled, src_rows, nb, kb, nb / kb, dst_row_dev, row_offset);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
 __global__ void unpack_q4_0_kernel(const uint8_t* __restrict__ tiled, uint16_t* __restrict__ raw, long long rows,
                                    int nb, int kb, int nt, long long mat_stride, long long count) {
     const long long per_mat = rows * nb;

@@ -14,6 +14,17 @@
  * kernels (src/cuda_infer.cu quant_x_q8 / gemv_dp4a, src/mega.cu blk_acc),
  * which has no CPU implementation in the reference.
  *
+ * Arithmetic of the q8_0 mode.  A q8_0 quantizer is discontinuous: an ulp-sized
+ * difference in its input (a different fp32 summation order, another libm's expf)
+ * can flip one int8, and two engines that differ that way drift apart to about
+ * 2e-3 on the logits.  The reference's own GPU engines each sum in their own
+ * order, so the reference defines the formulas but no canonical rounding.  The
+ * q8_0 mode therefore evaluates every reference formula in double precision
+ * (block products dw*dx*isum are exact in double; exp / cos / sin through the
+ * double libm) and rounds to fp32 once, where the reference stores an fp32
+ * tensor.  A result obtained this way does not depend on the order of the sum,
+ * so any engine that accumulates in double can match it bit for bit.
+ *
  * Plain C99 + OpenMP (optional).  No dependencies.
  */
 #include <math.h>
@@ -140,8 +151,9 @@ ORC_API void orc_block_isums(const uint8_t* W, int64_t rows, int64_t cols, const
             isum[r * nb + b] = block_isum(W + (r * nb + b) * 18, xq + b * 32);
 }
 
-/* y[r] = sum_b fma(dw*dx, float(isum), acc) in block order (+bias): the rounded
- * accumulate of src/mega.cu:151-155 applied to src/cuda_infer.cu:94-127's sum. */
+/* y[r] = fp32( sum_b (dw*dx) * isum ) + bias[r]: the sum of src/cuda_infer.cu:94-127
+ * (src/mega.cu:151-155) with the accumulation carried in double.  dw*dx is exact in
+ * fp32 (two fp16 values), its product with the integer is exact in double. */
 ORC_API void orc_gemv_q4_q8(const uint8_t* W, int64_t rows, int64_t cols, const int8_t* xq,
                             const uint16_t* xd, const float* bias, float* y) {
     const int64_t nb = cols / 32;
@@ -149,15 +161,15 @@ ORC_API void orc_gemv_q4_q8(const uint8_t* W, int64_t rows, int64_t cols, const 
     for (int64_t b = 0; b < nb; b++) dx[b] = orc_fp16_to_fp32(xd[b]);
     #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; r++) {
-        float acc = 0.f;
+        double acc = 0.0;
         for (int64_t b = 0; b < nb; b++) {
             const uint8_t* blk = W + (r * nb + b) * 18;
             uint16_t dh; memcpy(&dh, blk, 2);
-            float dw = orc_fp16_to_fp32(dh);
-            float s = dw * dx[b];                       /* rounded product, then one fma */
-            acc = fmaf(s, (float)block_isum(blk, xq + b * 32), acc);
+            const float s = orc_fp16_to_fp32(dh) * dx[b];
+            acc += (double)s * (double)block_isum(blk, xq + b * 32);
         }
-        y[r] = acc + (bias ? bias[r] : 0.f);
+        const float v = (float)acc;
+        y[r] = bias ? v + bias[r] : v;
     }
     free(dx);
 }
@@ -198,6 +210,52 @@ ORC_API void orc_rope(float* v, int n_head, int hd, int pos, float base) {
             p[i + half] = x0 * s + x1 * c;
         }
     }
+}
+
+/* q8_0 mode: the same rotation with cos/sin from the double libm and exact double
+ * products, rounded to fp32 once per output. */
+ORC_API void orc_rope_d(float* v, int n_head, int hd, int pos, float base) {
+    int half = hd / 2;
+    for (int h = 0; h < n_head; h++) {
+        float* p = v + (size_t)h * hd;
+        for (int i = 0; i < half; i++) {
+            const float theta = pos * powf(base, -2.f * i / hd);
+            const float c = (float)cos((double)theta), s = (float)sin((double)theta);
+            const double x0 = p[i], x1 = p[i + half];
+            p[i] = (float)(x0 * c - x1 * s);
+            p[i + half] = (float)(x0 * s + x1 * c);
+        }
+    }
+}
+
+/* q8_0 mode: softmax attention (src/cpu_infer.cpp:121-140) carried in double:
+ * score = fp32(q.k) * inv in fp32, weights exp(score - max) and both sums in double,
+ * output fp32(sum / denominator). */
+ORC_API void orc_attention_d(const float* q, const float* kc, const float* vc, int pos,
+                             int n_head, int n_head_kv, int hd, float* att) {
+    const int kv_dim = n_head_kv * hd, gqa = n_head / n_head_kv;
+    const float inv = 1.f / sqrtf((float)hd);
+    float* sc = (float*)malloc(sizeof(float) * (size_t)(pos + 1));
+    double* o = (double*)malloc(sizeof(double) * (size_t)hd);
+    for (int hh = 0; hh < n_head; hh++) {
+        const int kvh = hh / gqa; const float* qh = q + (size_t)hh * hd;
+        float mx = -INFINITY;
+        for (int t = 0; t <= pos; t++) {
+            const float* kt = kc + (size_t)t * kv_dim + (size_t)kvh * hd;
+            double d = 0; for (int i = 0; i < hd; i++) d += (double)qh[i] * (double)kt[i];
+            sc[t] = (float)d * inv; if (sc[t] > mx) mx = sc[t];
+        }
+        double sum = 0;
+        for (int i = 0; i < hd; i++) o[i] = 0;
+        for (int t = 0; t <= pos; t++) {
+            const float* vt = vc + (size_t)t * kv_dim + (size_t)kvh * hd;
+            const double e = exp((double)sc[t] - (double)mx);
+            sum += e;
+            for (int i = 0; i < hd; i++) o[i] = fma(e, (double)vt[i], o[i]);
+        }
+        for (int i = 0; i < hd; i++) att[(size_t)hh * hd + i] = (float)(o[i] / sum);
+    }
+    free(sc); free(o);
 }
 
 /* Causal GQA attention of one query over positions 0..pos of a cache laid out
@@ -305,20 +363,24 @@ ORC_API int orc_forward(const orc_model* m, orc_state* s, int token, int pos, fl
         mv(s, m->wq[l], NH * HD, E, s->xb, m->bq[l], s->q, 1);
         mv(s, m->wk[l], kv_dim, E, s->xb, m->bk[l], s->k, 0);
         mv(s, m->wv[l], kv_dim, E, s->xb, m->bv[l], s->v, 0);
-        orc_rope(s->q, NH, HD, pos, m->rope_base);
-        orc_rope(s->k, NKV, HD, pos, m->rope_base);
+        if (s->act_q8) { orc_rope_d(s->q, NH, HD, pos, m->rope_base); orc_rope_d(s->k, NKV, HD, pos, m->rope_base); }
+        else { orc_rope(s->q, NH, HD, pos, m->rope_base); orc_rope(s->k, NKV, HD, pos, m->rope_base); }
         if (s->kv_f16) { round_f16(s->k, kv_dim); round_f16(s->v, kv_dim); }
         float* kc = s->kc + (size_t)l * s->max_seq * kv_dim;
         float* vc = s->vc + (size_t)l * s->max_seq * kv_dim;
         memcpy(kc + (size_t)pos * kv_dim, s->k, sizeof(float) * kv_dim);
         memcpy(vc + (size_t)pos * kv_dim, s->v, sizeof(float) * kv_dim);
-        orc_attention(s->q, kc, vc, pos, NH, NKV, HD, s->att);
+        if (s->act_q8) orc_attention_d(s->q, kc, vc, pos, NH, NKV, HD, s->att);
+        else orc_attention(s->q, kc, vc, pos, NH, NKV, HD, s->att);
         mv(s, m->wo[l], E, NH * HD, s->att, NULL, s->proj, 1);
         for (int i = 0; i < E; i++) s->h[i] += s->proj[i];
         orc_rmsnorm(s->h, m->ffn_norm[l], E, m->rms_eps, s->xb);
         mv(s, m->wg[l], FF, E, s->xb, NULL, s->gbuf, 1);
         mv(s, m->wu[l], FF, E, s->xb, NULL, s->ubuf, 0);
-        for (int i = 0; i < FF; i++) { float x = s->gbuf[i]; s->gbuf[i] = (x / (1.f + expf(-x))) * s->ubuf[i]; }
+        if (s->act_q8)
+            for (int i = 0; i < FF; i++) { const double x = s->gbuf[i]; s->gbuf[i] = (float)((x / (1.0 + exp(-x))) * (double)s->ubuf[i]); }
+        else
+            for (int i = 0; i < FF; i++) { float x = s->gbuf[i]; s->gbuf[i] = (x / (1.f + expf(-x))) * s->ubuf[i]; }
         mv(s, m->wd[l], E, FF, s->gbuf, NULL, s->proj, 1);
         for (int i = 0; i < E; i++) s->h[i] += s->proj[i];
         if (hidden_out) memcpy(hidden_out + (size_t)l * E, s->h, sizeof(float) * E);
@@ -331,6 +393,10 @@ ORC_API int orc_forward(const orc_model* m, orc_state* s, int token, int pos, fl
     if (!logits) free(lg);
     return best;
 }
+
+/* The fp32 KV cache of a state ([layer][max_seq][kv_dim]), for cache-content checks. */
+ORC_API float* orc_state_kc(orc_state* s) { return s->kc; }
+ORC_API float* orc_state_vc(orc_state* s) { return s->vc; }
 
 ORC_API int orc_num_threads(void) {
 #ifdef _OPENMP

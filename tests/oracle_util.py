@@ -44,6 +44,8 @@ def lib():
         L.orc_state_free.argtypes = [_vp]
         L.orc_forward.restype, L.orc_forward.argtypes = _i32, [_vp, _vp, _i32, _i32, _vp, _vp]
         L.orc_num_threads.restype = _i32
+        L.orc_state_kc.restype, L.orc_state_kc.argtypes = C.POINTER(C.c_float), [_vp]
+        L.orc_state_vc.restype, L.orc_state_vc.argtypes = C.POINTER(C.c_float), [_vp]
         _lib = L
     return _lib
 
@@ -193,6 +195,14 @@ class OracleModel:
         tok = lib().orc_forward(C.byref(self.m), self.state, int(token), self.pos, _p(logits), _p(hidden))
         self.pos += 1
         return tok, logits, hidden
+
+    def kv_cache(self, max_seq):
+        """(K, V) caches as [layer][max_seq][kv_dim] float32 views."""
+        cfg = self.cfg
+        shape = (cfg["n_layer"], max_seq, cfg["n_head_kv"] * cfg["head_dim"])
+        n = int(np.prod(shape))
+        return (np.ctypeslib.as_array(lib().orc_state_kc(self.state), shape=(n,)).reshape(shape),
+                np.ctypeslib.as_array(lib().orc_state_vc(self.state), shape=(n,)).reshape(shape))
 
     def generate(self, prompt, n_gen):
         """Greedy continuation exactly as the reference CLI prints it: n_gen ids,

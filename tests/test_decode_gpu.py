@@ -1,0 +1,152 @@
+"""GPU parity of the fused decode step (per-phase launches and the persistent
+kernel) against the CPU oracle in q8_0-activation / fp16-KV mode, and against the
+greedy streams the reference's own cpu_infer printed (tests/golden/streams_ref.json).
+
+Bars: greedy token streams identical to the q8 oracle; fp32 logits within 1e-3
+relative (max |a-b| / max |b|) of the q8 oracle at every step, teacher-forced on
+the oracle's tokens so that positions stay comparable.
+"""
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import gguf_util as gu
+import oracle_util as ou
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+REL_TOL = 1e-3
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def cases(tmp_path_factory):
+    d = tmp_path_factory.mktemp("models")
+    out = []
+    for i, c in enumerate(json.loads((GOLD / "streams_ref.json").read_text())):
+        p = gu.make_synthetic(d / f"m{i}.gguf", c["preset"], seed=c["seed"], std=c["std"], extra=["--bias-std", c["bias_std"]])
+        out.append((p, c))
+    return out
+
+
+@pytest.mark.parametrize("mode_name", ["per_phase", "persistent"])
+def test_tiny_streams_and_logits_match_q8_oracle(ctx, pkg, cases, mode_name):
+    import torch
+    mode = pkg.DECODE_PER_PHASE if mode_name == "per_phase" else pkg.DECODE_PERSISTENT
+    for path, c in cases:
+        g = gu.GgufReader(path)
+        prompt, n_gen = c["prompt"], c["n_gen"]
+        n_steps = len(prompt) + n_gen - 1
+        orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n_steps + 1)
+        want = orc.generate(prompt, n_gen)
+        m = pkg.Model(ctx, path, max_seq=n_steps + 1)
+        got, _ = m.generate(prompt, n_gen, mode=mode)
+        assert got == want, f"greedy stream differs from the q8 oracle (std {c['std']})"
+        # teacher-forced logits at every position
+        seq = prompt + want[:-1]
+        orc2 = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n_steps + 1)
+        logits = torch.zeros((n_steps, g.config()["n_vocab"]), dtype=torch.float32, device="cuda")
+        pred, _ = m.decode(seq, n_steps, 0, logits, mode)
+        lg = logits.cpu().numpy()
+        worst = 0.0
+        for s, t in enumerate(seq):
+            tok, lo, _ = orc2.forward(t)
+            worst = max(worst, rel_err(lg[s], lo))
+            assert pred[s] == tok
+        assert worst < REL_TOL, f"logits deviate {worst:.2e} from the q8 oracle"
+        m.free()
+
+
+def test_streams_against_reference_cpu_infer_golden(ctx, pkg, cases):
+    """cpu_infer multiplies fp32 activations; this engine quantizes them to q8_0 (as the
+    reference's GPU engines do), so agreement is exact only while no near-tie flips:
+    the two milder models must match in full; on the liveliest one (weights std 0.3, near-ties
+    everywhere) only the first token is required, and the q8 oracle is the judge instead."""
+    for path, c in cases:
+        m = pkg.Model(ctx, path, max_seq=len(c["prompt"]) + c["n_gen"])
+        got, _ = m.generate(c["prompt"], c["n_gen"])
+        ref = c["ref_ids"]
+        agree = next((i for i, (a, b) in enumerate(zip(got, ref)) if a != b), len(ref))
+        if c["std"] <= 0.1:
+            assert got == ref
+        else:
+            assert agree >= 1, f"only {agree} leading tokens agree with cpu_infer"
+        m.free()
+
+
+def test_hidden_state_after_every_layer(ctx, pkg, cases):
+    path, c = cases[1]
+    g = gu.GgufReader(path)
+    cfg = g.config()
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=4)
+    m = pkg.Model(ctx, path, max_seq=4)
+    for pos, tok in enumerate([5, 77, 300]):
+        _, _, hidden = orc.forward(tok, want_logits=False, want_hidden=True)
+        for l in range(cfg["n_layer"]):
+            m.run_phases(tok, pos, 5 * l, 5 * (l + 1))
+            h = m.state("h", np.float32, cfg["n_embd"])
+            assert rel_err(h, hidden[l]) < REL_TOL, f"residual stream after layer {l} at pos {pos}"
+        m.run_phases(tok, pos, 5 * cfg["n_layer"], 5 * cfg["n_layer"] + 1)
+    m.free()
+
+
+def test_kv_cache_is_fp16_of_oracle_values(ctx, pkg, cases):
+    path, c = cases[2]
+    g = gu.GgufReader(path)
+    cfg = g.config()
+    kvd = cfg["n_head_kv"] * cfg["head_dim"]
+    m = pkg.Model(ctx, path, max_seq=8)
+    toks = [9, 8, 7, 6]
+    m.decode(toks, len(toks), 0, None, pkg.DECODE_PER_PHASE)
+    kc = m.state("kcache", np.float16, cfg["n_layer"] * 8 * kvd).reshape(cfg["n_layer"], 8, kvd).astype(np.float32)
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=8)
+    for t in toks:
+        orc.forward(t, want_logits=False)
+    kc_ref, _ = orc.kv_cache(8)
+    # fp16 rounding of values that differ by fp32 summation order: allow one fp16 ulp
+    assert np.abs(kc[:, :4] - kc_ref[:, :4]).max() <= 2e-3 * max(1.0, np.abs(kc_ref).max())
+    m.free()
+
+
+def test_persistent_equals_per_phase_bit_for_bit(ctx, pkg, cases):
+    import torch
+    path, c = cases[2]
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    seq = list(np.random.default_rng(4).integers(0, V, 40))
+    outs = []
+    for mode in (pkg.DECODE_PER_PHASE, pkg.DECODE_PERSISTENT, pkg.DECODE_PERSISTENT):
+        m = pkg.Model(ctx, path, max_seq=64)
+        logits = torch.zeros((len(seq), V), dtype=torch.float32, device="cuda")
+        pred, _ = m.decode(seq, len(seq), 0, logits, mode)
+        outs.append((pred, logits.cpu().numpy()))
+        m.free()
+    for pred, lg in outs[1:]:
+        assert pred == outs[0][0]
+        assert np.array_equal(lg, outs[0][1])
+
+
+def test_decode_argument_checks(ctx, pkg, cases, tmp_path):
+    path, _ = cases[0]
+    m = pkg.Model(ctx, path, max_seq=8)
+    with pytest.raises(pkg.MinferError):
+        m.decode([1, 2, 3], 9, 0)                     # beyond the KV cache
+    with pytest.raises(pkg.MinferError):
+        m.decode([100000], 1, 0)                      # token id out of range
+    assert m.decode([], 0, 0)[0] == []
+    with pytest.raises(pkg.MinferError):
+        pkg.Model(ctx, tmp_path / "missing.gguf", 8)
+    bad = tmp_path / "bad.gguf"
+    bad.write_bytes(b"GGUF" + b"\x00" * 10)
+    with pytest.raises(pkg.MinferError):
+        pkg.Model(ctx, bad, 8)
+    trunc = tmp_path / "trunc.gguf"
+    trunc.write_bytes(Path(path).read_bytes()[:100000])
+    with pytest.raises(pkg.MinferError):
+        pkg.Model(ctx, trunc, 8)
+    m.free()
