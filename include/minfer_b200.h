@@ -75,6 +75,13 @@ MI_API const char* mi_last_error(const mi_ctx* ctx);
 /* Number of SMs the context sizes its grids for. */
 MI_API int mi_ctx_sm_count(const mi_ctx* ctx);
 
+/* Plain device memory for callers that have no CUDA binding of their own
+ * (activations, logits).  mi_memcpy_* are synchronous on the context's stream. */
+MI_API int mi_device_malloc(mi_ctx* ctx, size_t bytes, void** out_dev);
+MI_API int mi_device_free(mi_ctx* ctx, void* ptr_dev);
+MI_API int mi_memcpy_to_device(mi_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
+MI_API int mi_memcpy_to_host(mi_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
+
 /* ---- weights: GGUF q4_0 -> tiled device layout --------------------------- */
 
 /* Upload `count` consecutive row-major q4_0 matrices of rows x cols (18-byte
@@ -143,8 +150,15 @@ typedef struct mi_model_config {
 enum { MI_DECODE_PERSISTENT = 0,   /* one cooperative launch: all phases, layers and steps in one persistent kernel */
        MI_DECODE_PER_PHASE = 1 };  /* the same kernel launched once per phase (plain stream order, no grid barrier) */
 
+/* MI_STATE_H: residual stream at the input of the layer whose QKV phase ran last;
+ * MI_STATE_H_MID: residual stream after the attention block of the layer whose gate/up phase ran last. */
 enum { MI_STATE_H = 0, MI_STATE_Q = 1, MI_STATE_ATT = 2, MI_STATE_KCACHE = 3, MI_STATE_VCACHE = 4,
-       MI_STATE_ACT_Q = 5, MI_STATE_ACT_D = 6 };
+       MI_STATE_ACT_Q = 5, MI_STATE_ACT_D = 6,
+       MI_STATE_PROFILE = 7,
+       MI_STATE_H_MID = 8 };  /* 32 x uint64 nanoseconds per phase part on CTA 0, filled when the model was loaded
+                                 * with MINFER_PROFILE set in the environment: slots 2k / 2k+1 = staging / work of phase
+                                 * kind k (0 QKV, 1 attention, 2 O, 3 gate-up, 4 down, 5 lm_head), 12 = grid barrier,
+                                 * 13 = per-step prologue.  The reference's PROFILE=1 (src/mega.cu:111-119). */
 
 /* Load an all-q4_0 Qwen2-architecture GGUF file (metadata keys and tensor names
  * exactly as the reference drivers read them: src/cpu_infer.cpp:71-98), repack

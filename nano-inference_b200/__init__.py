@@ -41,6 +41,10 @@ SIGNATURES = {
     "mi_ctx_sync": (_i32, [_vp]),
     "mi_last_error": (C.c_char_p, [_vp]),
     "mi_ctx_sm_count": (_i32, [_vp]),
+    "mi_device_malloc": (_i32, [_vp, C.c_size_t, C.POINTER(_vp)]),
+    "mi_device_free": (_i32, [_vp, _vp]),
+    "mi_memcpy_to_device": (_i32, [_vp, _vp, _vp, C.c_size_t]),
+    "mi_memcpy_to_host": (_i32, [_vp, _vp, _vp, C.c_size_t]),
     "mi_weight_upload_q4_0": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
     "mi_weight_repack_q4_0_dev": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
     "mi_weight_download_q4_0": (_i32, [_vp, _vp, _vp]),
@@ -60,7 +64,7 @@ SIGNATURES = {
 }
 
 DECODE_PERSISTENT, DECODE_PER_PHASE = 0, 1
-STATE = {"h": 0, "q": 1, "att": 2, "kcache": 3, "vcache": 4, "act_q": 5, "act_d": 6}
+STATE = {"h": 0, "q": 1, "att": 2, "kcache": 3, "vcache": 4, "act_q": 5, "act_d": 6, "profile": 7, "h_mid": 8}
 
 
 class ModelConfig(C.Structure):

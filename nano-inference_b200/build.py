@@ -92,7 +92,7 @@ def build_host(force=False, verbose=False):
         if not src.exists():
             continue
         exe = BIN / name
-        if force or _newer(exe, [src, LIB, HOST / "gguf_file.hpp", ROOT / "include" / "minfer_b200.h"]):
+        if force or _newer(exe, [src, LIB, HOST / "driver_common.hpp", ROOT / "include" / "minfer_b200.h"]):
             _run([GXX, "-O2", "-std=c++17", "-I", ROOT / "include", "-I", HOST, "-o", exe, src,
                   "-L", LIB.parent, "-lminfer_b200", "-Wl,-rpath,$ORIGIN/../lib"], verbose)
         out.append(exe)

@@ -138,3 +138,40 @@ extern "C" int mi_ctx_sync(mi_ctx* ctx) {
 
 extern "C" const char* mi_last_error(const mi_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
 extern "C" int mi_ctx_sm_count(const mi_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+extern "C" int mi_device_malloc(mi_ctx* ctx, size_t bytes, void** out_dev) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!out_dev) return set_error(ctx, MI_ERR_INVALID, "device_malloc: null output");
+    *out_dev = nullptr;
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaError_t e = cudaMalloc(out_dev, bytes ? bytes : 1);
+    if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "device_malloc(%zu): %s", bytes, cudaGetErrorString(e));
+    return MI_OK;
+}
+
+extern "C" int mi_device_free(mi_ctx* ctx, void* ptr_dev) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!ptr_dev) return MI_OK;
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    MI_CUDA(ctx, cudaFree(ptr_dev));
+    return MI_OK;
+}
+
+extern "C" int mi_memcpy_to_device(mi_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (bytes == 0) return MI_OK;
+    if (!dst_dev || !src_host) return set_error(ctx, MI_ERR_INVALID, "memcpy_to_device: null pointer");
+    MI_CUDA(ctx, cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MI_OK;
+}
+
+extern "C" int mi_memcpy_to_host(mi_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (bytes == 0) return MI_OK;
+    if (!dst_host || !src_dev) return set_error(ctx, MI_ERR_INVALID, "memcpy_to_host: null pointer");
+    MI_CUDA(ctx, cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MI_OK;
+}

@@ -25,8 +25,9 @@ struct mi_model {
     int* d_in_tokens = nullptr; int in_capacity = 0;
     int* d_out_tokens = nullptr; int out_capacity = 0;
     size_t smem = 0;
-    size_t part_count = 0, n_counters = 0;
+    size_t part_count = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    unsigned long long* prof_buf = nullptr;
 };
 
 namespace {
@@ -84,28 +85,14 @@ int alloc_tiled(mi_ctx* ctx, mi_model* m, int64_t rows, int64_t cols, uint8_t** 
     return dev_alloc(ctx, m, out, groups * nt * tile_bytes(kb), true);
 }
 
-// Cost model for the K-split of one job (smaller is better): the slowest warp's tile
-// count against the busiest SM's share of the stream, plus a charge for the fold.
-int plan_ks(int groups, int nt, int nacc, int rot, int grid) {
-    const int W = grid * DNW;
-    double best_cost = 1e30; int best = 1;
-    std::vector<int> warp_tiles(W), cta_tiles(grid);
-    for (int ks = 1; ks <= std::min(nt, 40); ks++) {
-        std::fill(warp_tiles.begin(), warp_tiles.end(), 0);
-        std::fill(cta_tiles.begin(), cta_tiles.end(), 0);
-        const long long n_units = (long long)groups * ks;
-        for (long long u = 0; u < n_units; u++) {
-            const int sp = (int)(u % ks), t0 = (int)((long long)sp * nt / ks), t1 = (int)((long long)(sp + 1) * nt / ks);
-            const int slot = (int)((u + rot) % W);
-            warp_tiles[slot] += nacc * (t1 - t0);
-            cta_tiles[slot % grid] += nacc * (t1 - t0);
-        }
-        const int mw = *std::max_element(warp_tiles.begin(), warp_tiles.end());
-        const int mc = *std::max_element(cta_tiles.begin(), cta_tiles.end());
-        double cost = std::max(0.20 * mw, 0.105 * mc) + (ks > 1 ? 0.25 + 0.03 * ks : 0.0);
-        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
-    }
-    return best;
+// Cross-CTA K-split of a per-layer job.  A job whose result feeds an in-phase epilogue
+// (QKV: bias + RoPE + stores; gate/up: SwiGLU + q8_0) is never split across CTAs: its
+// eight warps already share every unit.  The O and down projections only emit partial
+// sums for the next prologue, so they are split until every CTA has a unit.
+int plan_ks(int kind, int groups, int nt, int grid) {
+    if (kind != JOB_O && kind != JOB_DOWN) return 1;
+    int ks = grid / std::max(groups, 1);
+    return std::max(1, std::min(ks, nt));
 }
 
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
@@ -235,16 +222,23 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
     // ---- layers
     std::vector<LayerPtrs> lp(L);
     const int qkv_rows = NQ + 2 * KVD, W = m->grid * DNW;
-    int rot = 0; size_t part_off = 0, cnt_off = 0;
+    int rot = 0, wrot = 0; size_t part_off = 0;
     auto add_job = [&](const uint8_t* base, int groups, int cols, int nacc, int kind, int layer) {
         Job jb{}; jb.base = base; jb.groups = groups; jb.nb = cols / 32; jb.kb = choose_kb(jb.nb); jb.nt = jb.nb / jb.kb;
-        jb.nacc = nacc; jb.kind = kind; jb.layer = layer; jb.rot = rot;
+        jb.nacc = nacc; jb.kind = kind; jb.layer = layer;
         const char* force = getenv("MINFER_KS");
-        jb.ks = force ? std::max(1, std::min(atoi(force), jb.nt)) : plan_ks(groups, jb.nt, nacc, rot, m->grid);
+        jb.ks = plan_ks(kind, groups, jb.nt, m->grid);
+        if (force && (kind == JOB_O || kind == JOB_DOWN)) jb.ks = std::max(1, std::min(atoi(force), jb.nt));
         jb.n_units = groups * jb.ks;
-        jb.part_off = (int)part_off; jb.cnt_off = (int)cnt_off;
-        part_off += (size_t)groups * jb.ks * nacc * 32; cnt_off += (size_t)groups;
-        rot = (int)(((long long)rot + jb.n_units) % W);
+        jb.part_off = (int)part_off;
+        if (kind == JOB_O || kind == JOB_DOWN) part_off += (size_t)groups * jb.ks * 32;
+        if (kind == JOB_LM) { jb.rot = 0; jb.wrot = 0; }
+        else {
+            // successive jobs start where the previous one stopped, over CTAs and over the warps of a CTA
+            jb.rot = rot; jb.wrot = wrot;
+            rot = (int)(((long long)rot + jb.n_units) % m->grid);
+            wrot = (wrot + nacc * ((jb.nt + jb.ks - 1) / jb.ks)) & (DNW - 1);
+        }
         m->jobs.push_back(jb);
     };
     for (int l = 0; l < L; l++) {
@@ -290,6 +284,53 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
     m->weight_bytes_q4 += (int64_t)V * E / 32 * 18;
     MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
 
+    // ---- per-warp tile lists: the order in which each warp of the grid consumes tiles during one step
+    {
+        const int nj = (int)m->jobs.size(), G = m->grid;
+        std::vector<std::vector<unsigned long long>> lists((size_t)G * DNW);
+        std::vector<unsigned> start((size_t)G * DNW * (nj + 1), 0);
+        for (int j = 0; j < nj; j++) {
+            const Job& jb = m->jobs[j];
+            const size_t tb = (size_t)jb.kb * kTileRowBytes;
+            const unsigned long long code = jb.kb == 8 ? 3 : jb.kb == 4 ? 2 : jb.kb == 2 ? 1 : 0;
+            for (int slot = 0; slot < G * DNW; slot++) start[(size_t)slot * (nj + 1) + j] = (unsigned)lists[slot].size();
+            if (jb.kind == JOB_LM) {
+                for (int u = 0; u < jb.n_units; u++) {                  // warp unit u -> slot sid = (u + rot) % W, sid = warp*G + cta
+                    const int sid = (int)(((long long)u + jb.rot) % W), cta = sid % G, warp = sid / G;
+                    auto& L = lists[(size_t)cta * DNW + warp];
+                    for (int t = 0; t < jb.nt; t++) L.push_back((unsigned long long)(uintptr_t)(jb.base + ((size_t)u * jb.nt + t) * tb) | code);
+                }
+            } else {
+                for (int cta = 0; cta < G; cta++) {
+                    const int r = jb.rot % G, u0 = cta >= r ? cta - r : cta + G - r;
+                    int uidx = 0;
+                    for (int u = u0; u < jb.n_units; u += G, uidx++) {
+                        const int g = u / jb.ks, sp = u % jb.ks, t0 = sp * jb.nt / jb.ks, ntu = (sp + 1) * jb.nt / jb.ks - t0, n = jb.nacc * ntu;
+                        const int wr = (jb.wrot + uidx * 3) & (DNW - 1);
+                        for (int warp = 0; warp < DNW; warp++)
+                            for (int i = (warp - wr) & (DNW - 1); i < n; i += DNW) {
+                                const int a = i / ntu, t = t0 + i % ntu;
+                                lists[(size_t)cta * DNW + warp].push_back(
+                                    (unsigned long long)(uintptr_t)(jb.base + ((size_t)(g * jb.nacc + a) * jb.nt + t) * tb) | code);
+                            }
+                    }
+                }
+            }
+        }
+        size_t stride = 1;
+        for (int slot = 0; slot < G * DNW; slot++) {
+            start[(size_t)slot * (nj + 1) + nj] = (unsigned)lists[slot].size();
+            stride = std::max(stride, lists[slot].size());
+        }
+        std::vector<unsigned long long> tab((size_t)G * DNW * stride, 0ull);
+        for (int slot = 0; slot < G * DNW; slot++) std::copy(lists[slot].begin(), lists[slot].end(), tab.begin() + (size_t)slot * stride);
+        unsigned long long* d_tab; unsigned* d_start;
+        if ((st = dev_alloc(ctx, m, &d_tab, tab.size())) || (st = dev_alloc(ctx, m, &d_start, start.size()))) return st;
+        MI_CUDA(ctx, cudaMemcpy(d_tab, tab.data(), tab.size() * 8, cudaMemcpyHostToDevice));
+        MI_CUDA(ctx, cudaMemcpy(d_start, start.data(), start.size() * 4, cudaMemcpyHostToDevice));
+        P.tile_tab = d_tab; P.tile_start = d_start; P.tile_stride = (int)stride;
+    }
+
     LayerPtrs* d_lp; Job* d_jobs;
     if ((st = dev_alloc(ctx, m, &d_lp, lp.size())) || (st = dev_alloc(ctx, m, &d_jobs, m->jobs.size()))) return st;
     MI_CUDA(ctx, cudaMemcpy(d_lp, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice));
@@ -304,17 +345,19 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
     P.rope_freq = d_freq;
 
     // ---- state
-    m->part_count = part_off; m->n_counters = cnt_off;
-    if ((st = dev_alloc(ctx, m, &P.h, E)) || (st = dev_alloc(ctx, m, &P.q, NQ)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
+    m->part_count = part_off;
+    if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.q, NQ)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
         (st = dev_alloc(ctx, m, &P.att_q, NQ)) || (st = dev_alloc(ctx, m, &P.att_d, NQ / 32)) ||
         (st = dev_alloc(ctx, m, &P.act_q, FF)) || (st = dev_alloc(ctx, m, &P.act_d, FF / 32)) ||
         (st = dev_alloc(ctx, m, &P.kc, (size_t)L * max_seq * KVD)) || (st = dev_alloc(ctx, m, &P.vc, (size_t)L * max_seq * KVD)) ||
         (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NKV)) ||
-        (st = dev_alloc(ctx, m, &P.part, part_off)) || (st = dev_alloc(ctx, m, &P.counters, cnt_off)) ||
+        (st = dev_alloc(ctx, m, &P.part, part_off)) ||
         (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
-        (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 1)))
+        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 1)))
         return st;
     P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
+    m->prof_buf = P.prof;
+    if (!getenv("MINFER_PROFILE")) P.prof = nullptr;         // the buffer exists either way; kernels only write it when asked
     m->smem = decode_smem_bytes((int)m->jobs.size(), E, FF, HD, m->G);
     if (m->smem > (size_t)ctx->smem_optin)
         return set_error(ctx, MI_ERR_UNSUPPORTED, "model: decode kernel needs %zu bytes of shared memory, %d available", m->smem, ctx->smem_optin);
@@ -340,13 +383,15 @@ extern "C" int mi_model_state_ptr(const mi_model* m, int which, void** ptr, int6
     const DecodeParams& P = m->P;
     const int NQ = m->NH * m->HD;
     switch (which) {
-        case MI_STATE_H: *ptr = P.h; if (bytes) *bytes = (int64_t)m->E * 4; break;
+        case MI_STATE_H: *ptr = P.h_in; if (bytes) *bytes = (int64_t)m->E * 4; break;
+        case MI_STATE_H_MID: *ptr = P.h_mid; if (bytes) *bytes = (int64_t)m->E * 4; break;
         case MI_STATE_Q: *ptr = P.q; if (bytes) *bytes = (int64_t)NQ * 4; break;
         case MI_STATE_ATT: *ptr = P.att; if (bytes) *bytes = (int64_t)NQ * 4; break;
         case MI_STATE_KCACHE: *ptr = P.kc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
         case MI_STATE_VCACHE: *ptr = P.vc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
         case MI_STATE_ACT_Q: *ptr = P.act_q; if (bytes) *bytes = (int64_t)m->FF; break;
         case MI_STATE_ACT_D: *ptr = P.act_d; if (bytes) *bytes = (int64_t)m->FF / 32 * 2; break;
+        case MI_STATE_PROFILE: *ptr = m->prof_buf; if (bytes) *bytes = (int64_t)kProfSlots * 8; break;
         default: return MI_ERR_INVALID;
     }
     return MI_OK;

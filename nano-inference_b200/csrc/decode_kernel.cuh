@@ -1,32 +1,42 @@
 // The fused decode step for sm_100a: one persistent kernel that runs any range of
 // the per-token phases
-//     per layer:  QKV  (rmsnorm -> q8 -> GEMV -> +bias, RoPE, q / fp16 KV store)
+//     per layer:  QKV  (residual fold -> rmsnorm -> q8 -> GEMV -> +bias, RoPE, q / fp16 KV store)
 //                 ATTN (split-KV attention over the fp16 cache, merge, -> q8)
-//                 O    (GEMV -> residual add)
-//                 GU   (rmsnorm -> q8 -> gate & up GEMV -> SwiGLU -> q8)
-//                 DOWN (GEMV -> residual add)
-//     finally:    LM   (rmsnorm -> q8 -> lm_head GEMV -> argmax)
+//                 O    (GEMV -> partial sums)
+//                 GU   (residual fold -> rmsnorm -> q8 -> gate & up GEMV -> SwiGLU -> q8)
+//                 DOWN (GEMV -> partial sums)
+//     finally:    LM   (residual fold -> rmsnorm -> q8 -> lm_head GEMV -> argmax)
 // for any range of steps.  Launched with one phase per launch it is a plain
 // kernel sequence; launched cooperatively over all phases and steps it is the
 // persistent decode loop, phases separated by a bounded-wait grid barrier.
 //
-// Weight streaming.  Every GEMV phase is a "job": a tiled q4_0 matrix cut into
-// units (row group, K-split) dealt to the grid's warps by a fixed rule.  The
-// whole tile sequence of a warp - across phases, layers and steps - is therefore
-// known up front, and lane 0 of every warp keeps a private shared-memory ring
-// full with bulk copies that run ahead of the barriers: weights are immutable,
-// so the HBM stream never has to wait for a phase boundary, only for ring space.
+// Work split.  Every GEMV phase is a "job" over a tiled q4_0 matrix.  For the
+// per-layer matrices a unit is (32-row group [gate/up: a pair of groups], K-split)
+// and belongs to a CTA: its eight warps take the unit's tiles round-robin and
+// fold their double partial sums through shared memory, so no fence or atomic
+// sits on the critical path.  Where a job has fewer row groups than the grid has
+// CTAs (O and down projections) the K dimension is additionally split across
+// CTAs; those partial sums go to global scratch as doubles and are added by the
+// NEXT phase's prologue, behind the grid barrier that separates the phases
+// anyway.  The lm_head has thousands of row groups: there a unit is a row group
+// and belongs to one warp.
+//
+// Weight streaming.  The whole tile sequence of a warp - across phases, layers
+// and steps - follows from shapes and indices alone, so lane 0 of every warp
+// keeps a private shared-memory ring full with bulk copies that run ahead of
+// the barriers: weights are immutable, the HBM stream never waits for a phase
+// boundary, only for ring space.
 //
 // Numerics follow the reference (paths relative to its root): quantizer
-// src/cuda_infer.cu:80-89; block dot + rounded accumulate src/mega.cu:151-165;
-// RMSNorm / RoPE / SwiGLU / argmax src/cpu_infer.cpp:40-61,147,153-154;
-// split-KV merge src/cuda_infer.cu:650-702.  Every sum that feeds a stored tensor
-// (GEMV rows, RMSNorm sum of squares, attention scores, softmax denominator and
-// weighted values) is carried in double and rounded to fp32 once; exp, cos and sin
-// come from the double math library.  A q8_0 quantizer is discontinuous, so this
-// is what lets two engines (or two split / step / shard configurations of this
-// one) agree bit for bit: the fp32 value of a double-carried sum does not depend
-// on the order of its terms.  Each token is processed exactly as if it were alone.
+// src/cuda_infer.cu:80-89; block dot src/mega.cu:151-165; RMSNorm / RoPE / SwiGLU /
+// argmax src/cpu_infer.cpp:40-61,147,153-154; split-KV merge
+// src/cuda_infer.cu:650-702.  Every sum that feeds a stored tensor (GEMV rows,
+// RMSNorm sum of squares, attention scores, softmax denominator and weighted
+// values) is carried in double and rounded to fp32 once; exp, cos and sin come
+// from the double math library.  A q8_0 quantizer is discontinuous, so this is
+// what lets two engines (or two split / step / shard configurations of this one)
+// agree bit for bit: the fp32 value of a double-carried sum does not depend on
+// the order of its terms.  Each token is processed exactly as if it were alone.
 #pragma once
 #include "gemv_core.cuh"
 
@@ -38,6 +48,9 @@ constexpr int DS = 3;             // ring slots per warp
 constexpr int DSLOT = 4608;       // bytes per slot: the largest tile (8 blocks)
 constexpr int kAttnChunk = 64;    // smallest KV range worth its own CTA
 
+// profile slots: 2*k = staging of phase kind k, 2*k+1 = its main work; 12 = barrier, 13 = step prologue
+enum { kProfBarrier = 12, kProfStep = 13, kProfSlots = 32 };
+
 enum JobKind { JOB_QKV = 0, JOB_O = 1, JOB_GU = 2, JOB_DOWN = 3, JOB_LM = 4 };
 
 struct Job {
@@ -45,9 +58,9 @@ struct Job {
     int groups;            // unit groups; one unit group = nacc consecutive 32-row groups
     int nt, ks, nb, kb, nacc, kind;
     int n_units;           // groups * ks
-    int rot;               // warp slot that gets unit 0
-    int part_off;          // offset (in doubles) of this job's split-K partials
-    int cnt_off;           // offset of this job's arrival counters
+    int rot;               // CTA (per-layer jobs) or warp slot (lm_head) that gets unit 0
+    int wrot;              // warp that gets tile 0 of a CTA unit
+    int part_off;          // offset (in doubles) of this job's cross-CTA partials: [groups][ks][32]
     int layer;
 };
 
@@ -57,23 +70,29 @@ struct DecodeParams {
     int L, E, FF, NH, NKV, HD, KVD, V;
     float eps;
     const Job* jobs;                 // [4L+1] in phase order
+    const unsigned long long* tile_tab;   // per warp slot: source address | kb code of every tile of one step, in consumption order
+    const unsigned* tile_start;      // [grid*DNW][4L+2]: index of each job's first tile in the warp's list (last = count)
+    int tile_stride;                 // entries reserved per warp slot in tile_tab
     const LayerPtrs* layers;         // [L]
     const float* out_norm;
     const float* rope_freq;          // [HD/2]: base^(-2i/HD), computed on the host with powf
     const uint8_t* emb_base;         // tiled token embedding (may alias the lm_head)
     int emb_nt, emb_kb;
     // state (global, written and read across CTAs: always accessed through L2)
-    float* h; float* q; float* att;
+    float* h_in;                     // residual stream at the input of the current layer
+    float* h_mid;                    // residual stream after the attention block
+    float* q; float* att;
     int8_t* att_q; __half* att_d;    // q8_0 of the merged attention output
     int8_t* act_q; __half* act_d;    // q8_0 of SwiGLU(gate, up)
     __half* kc; __half* vc; int max_seq;       // [L][max_seq][KVD]
     double* attn_part; unsigned* attn_cnt; int max_chunks;  // [NH][max_chunks][HD+2], [NKV]
-    double* part; unsigned* counters;          // split-K scratch
+    double* part;                              // cross-CTA partial sums of the O / down projections
     float* cand_val; int* cand_idx; unsigned* cand_cnt;     // per-CTA argmax candidates
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
     float* logits; long long logits_stride;    // optional [n_steps][stride]
     int pos0;
     unsigned* bar; int* err;
+    unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA 0 (see kProf*)
 };
 
 // number of KV chunks for a causal range of Lp positions (host and device agree)
@@ -85,18 +104,25 @@ __host__ __device__ inline int attn_chunks(int Lp, int max_chunks) {
 #ifdef __CUDACC__
 
 struct DecodeSmem {
-    uint8_t* ring; uint64_t* bars; Job* jobs; float* cs; double* red; uint8_t* stage;
+    uint8_t* ring; uint64_t* bars; Job* jobs; LayerPtrs* lp; float* cs; double* red; double* fold; uint8_t* stage;
 };
+
+constexpr int kFoldBytes = 2 * DNW * 2 * 32 * 8;      // two buffers of [warp][acc][lane] doubles
 
 __host__ __device__ inline size_t decode_stage_bytes(int E, int FF, int HD, int G) {
     const int maxin = E > FF ? E : FF;
-    size_t a = (size_t)E * 4 + maxin + (size_t)(maxin / 32) * 8;
-    size_t b = (size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * HD * 4;   // attention: states, weights, q
+    size_t a = (size_t)E * 8 + maxin + (size_t)(maxin / 32) * 8;      // hs, norm weights, xq, xs
+    size_t b = (size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * HD * 8;   // attention: states, weights, q (double)
     return ((a > b ? a : b) + 127) / 128 * 128;
 }
 __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, int HD, int G) {
-    return (size_t)DNW * DS * DSLOT + 256 + ((size_t)njobs * sizeof(Job) + 127) / 128 * 128 + 1024 + 256 +
+    return (size_t)DNW * DS * DSLOT + 256 + ((size_t)njobs * sizeof(Job) + 127) / 128 * 128 + 64 * sizeof(LayerPtrs) + 1024 + 256 + kFoldBytes +
            decode_stage_bytes(E, FF, HD, G);
+}
+
+// close the current profile interval: charge the time since t to slot k (CTA 0, thread 0 only)
+__device__ __forceinline__ void prof_mark(const DecodeParams& P, unsigned long long& t, int k) {
+    if (P.prof && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); P.prof[k] += n - t; t = n; }
 }
 
 // ---- grid barrier: monotonic arrival counter, bounded wait -----------------------
@@ -125,110 +151,142 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned& target, in
 }
 
 // ---- the per-warp weight stream -----------------------------------------------
-struct StreamCursor { int step, j, u, a, t, t0, t1; };
+// Tiles of a unit are numbered i = a*ntu + (t - t0) (a = accumulator, ntu = tiles of
+// the unit's K range).  In a CTA unit warp w owns the tiles with (i + wrot(u)) % 8 == w;
+// in a warp unit (lm_head) the owning warp takes all of them.
+struct UnitShape { int g, sp, t0, ntu, n, wrot; };
 
+__device__ __forceinline__ UnitShape unit_shape(const Job& jb, int u, int uidx) {
+    UnitShape s;
+    if (jb.ks == 1) { s.g = u; s.sp = 0; s.t0 = 0; s.ntu = jb.nt; }
+    else {
+        s.g = u / jb.ks; s.sp = u - s.g * jb.ks;
+        s.t0 = s.sp * jb.nt / jb.ks;                      // all operands are small: 32-bit is exact
+        s.ntu = (s.sp + 1) * jb.nt / jb.ks - s.t0;
+    }
+    s.n = jb.nacc * s.ntu;
+    s.wrot = (jb.wrot + uidx * 3) & (DNW - 1);      // uidx: how many units this CTA had before u in the job
+    return s;
+}
+
+// Producer side of a warp's ring.  The order in which a warp consumes tiles is a pure
+// function of shapes and indices, so the host lists it once per model: entry k of a warp's
+// list is the global address of its k-th tile of a step (16-byte aligned; the low two bits
+// carry log2 of the tile depth).  The producer walks that list, wrapping at the end of the
+// launch's job range, with the next entry already loaded so that issuing a copy costs a
+// handful of instructions and no division.
 struct WarpStream {
     uint8_t* ring; uint64_t* bars; const Job* jobs;
-    StreamCursor pc;
+    const unsigned long long* tab;   // this warp's list
+    unsigned e0, e1, c;              // entry range of the launch's jobs within a step; cursor
+    long long left;                  // tiles still to issue in this launch
+    unsigned long long next;         // entry at the cursor (valid while left > 0)
     int issued, consumed;
-    int step1, j0, j1;      // steps end; job range per step
-    int W, sid;             // warp slots in the grid, this warp's slot
+    int W, sid, warp;                // warp slots in the grid, this warp's slot, warp in CTA
+    uint64_t policy;                 // L2 evict-first for the weight stream
 
-    __device__ __forceinline__ int first_unit(const Job& jb) const {
-        const int r = jb.rot % W;
-        return sid >= r ? sid - r : sid + W - r;
-    }
-    __device__ __forceinline__ void set_tiles(const Job& jb) {
-        const int sp = pc.u % jb.ks;
-        pc.t0 = (int)((long long)sp * jb.nt / jb.ks);
-        pc.t1 = (int)((long long)(sp + 1) * jb.nt / jb.ks);
-        pc.t = pc.t0; pc.a = 0;
-    }
-    // move the producer to the next (step, job) that has a unit for this warp
-    __device__ __forceinline__ void seek() {
-        while (pc.step < step1) {
-            const Job& jb = jobs[pc.j];
-            if (pc.u < jb.n_units) { set_tiles(jb); return; }
-            if (++pc.j == j1) { pc.j = j0; pc.step++; }
-            if (pc.step < step1) pc.u = first_unit(jobs[pc.j]);
-        }
-    }
-    __device__ __forceinline__ void init(const DecodeSmem& sm, int warp, int lane, int step0, int step1_, int j0_, int j1_) {
+    __device__ __forceinline__ void init(const DecodeSmem& sm, const DecodeParams& P, int warp_, int step0, int step1, int j0, int j1) {
+        warp = warp_; policy = l2_policy_evict_first();
         ring = sm.ring + (size_t)warp * DS * DSLOT; bars = sm.bars + warp * DS; jobs = sm.jobs;
-        W = gridDim.x * DNW; sid = warp * gridDim.x + blockIdx.x;      // consecutive units land on different SMs
-        step1 = step1_; j0 = j0_; j1 = j1_; issued = consumed = 0;
-        pc.step = (j0 < j1) ? step0 : step1; pc.j = j0;
-        if (pc.step < step1) { pc.u = first_unit(jobs[pc.j]); seek(); }
+        W = gridDim.x * DNW; sid = warp * gridDim.x + blockIdx.x;      // consecutive warp units land on different SMs
+        const int slot = blockIdx.x * DNW + warp, nj = 4 * P.L + 2;
+        tab = P.tile_tab + (size_t)slot * P.tile_stride;
+        e0 = __ldg(P.tile_start + (size_t)slot * nj + j0);
+        e1 = __ldg(P.tile_start + (size_t)slot * nj + j1);
+        c = e0; issued = consumed = 0;
+        left = j0 < j1 ? (long long)(step1 - step0) * (e1 - e0) : 0;
+        next = left > 0 ? __ldg(tab + c) : 0ull;
     }
     __device__ __forceinline__ void issue_one() {       // lane 0 only
-        if (pc.step >= step1) return;
-        const Job& jb = jobs[pc.j];
-        const int g = pc.u / jb.ks, tb = jb.kb * kTileRowBytes, slot = issued % DS;
-        const uint8_t* src = jb.base + ((size_t)(g * jb.nacc + pc.a) * jb.nt + pc.t) * tb;
+        if (left <= 0) return;
+        const unsigned long long e = next;
+        const int tb = kTileRowBytes << (int)(e & 3ull), slot = issued % DS;
         mbar_expect_tx(&bars[slot], tb);
-        bulk_g2s(ring + (size_t)slot * DSLOT, src, tb, &bars[slot]);
+        bulk_g2s_hint(ring + (size_t)slot * DSLOT, reinterpret_cast<const void*>(e & ~15ull), tb, &bars[slot], policy);
         issued++;
-        if (++pc.t == pc.t1) {
-            if (++pc.a < jb.nacc) pc.t = pc.t0;
-            else { pc.u += W; seek(); }
-        }
+        if (++c == e1) c = e0;
+        if (--left > 0) next = __ldg(tab + c);
     }
     __device__ __forceinline__ void drain() {
-        for (int i = consumed; i < issued; i++) (void)mbar_wait_bounded(&bars[i % DS], (i / DS) & 1);
+        for (int k = consumed; k < issued; k++) (void)mbar_wait_bounded(&bars[k % DS], (k / DS) & 1);
+    }
+    __device__ __forceinline__ int first_cta_unit(const Job& jb) const {
+        const int G = (int)gridDim.x, r = jb.rot % G, b = (int)blockIdx.x;
+        return b >= r ? b - r : b + G - r;
+    }
+    __device__ __forceinline__ int first_warp_unit(const Job& jb) const {
+        const int r = jb.rot % W; return sid >= r ? sid - r : sid + W - r;
     }
 };
 
-template <int KB>
-__device__ __forceinline__ double tiles_dot(WarpStream& ws, int lane, int t0, int t1, const int8_t* xq_s, const float2* xs_s, bool& ok) {
-    double acc = 0.0;
-    for (int t = t0; t < t1; t++) {
-        const int slot = ws.consumed % DS;
-        if (!mbar_wait_bounded(&ws.bars[slot], (ws.consumed / DS) & 1)) { ok = false; return acc; }
-        acc = tile_dot_row<KB, false>(ws.ring + (size_t)slot * DSLOT, lane, t * KB, xq_s, xs_s, acc, nullptr);
-        ws.consumed++;
-        __syncwarp();
-        if (lane == 0) ws.issue_one();
+// consume the next tile of this warp's stream into acc (block index b0 = t * kb)
+__device__ __forceinline__ double tile_consume(WarpStream& ws, int lane, int kb, int t, const int8_t* xq_s, const float2* xs_s,
+                                               double acc, bool& ok, const DecodeParams* PP = nullptr, unsigned long long* tp = nullptr) {
+    if (!ok) return acc;
+    const int slot = ws.consumed % DS;
+    if (tp) prof_mark(*PP, *tp, 18);
+    if (!mbar_wait_bounded(&ws.bars[slot], (ws.consumed / DS) & 1)) { ok = false; return acc; }
+    if (tp) prof_mark(*PP, *tp, 20);
+    const uint8_t* tile = ws.ring + (size_t)slot * DSLOT;
+    switch (kb) {
+        case 8: acc = tile_dot_row<8, false>(tile, lane, t * 8, xq_s, xs_s, acc, nullptr); break;
+        case 4: acc = tile_dot_row<4, false>(tile, lane, t * 4, xq_s, xs_s, acc, nullptr); break;
+        case 2: acc = tile_dot_row<2, false>(tile, lane, t * 2, xq_s, xs_s, acc, nullptr); break;
+        default: acc = tile_dot_row<1, false>(tile, lane, t, xq_s, xs_s, acc, nullptr); break;
     }
+    ws.consumed++;
+    __syncwarp();
+    if (tp) prof_mark(*PP, *tp, 21);
+    if (lane == 0) ws.issue_one();
+    __syncwarp();
+    if (tp) prof_mark(*PP, *tp, 22);
     return acc;
 }
 
-// Consume this warp's units of job j.  epi(g, lane, v0, v1): complete sums (fp32 of the double sum) of rows
-// (g*nacc + a)*32 + lane, a = 0 (v0) and 1 (v1, only when nacc == 2).
+// Per-layer job: this CTA's units, tiles split over its warps, partial sums folded in
+// shared memory in warp order by warp 0.
+//   ks == 1 : epi(g, lane, v0, v1) with the complete sums (fp32 of the double sum);
+//   ks  > 1 : the double partial of (g, sp) goes to P.part for the next prologue.
+// Every warp passes the same number of __syncthreads, also after a wait gave up.
 template <class Epi>
-__device__ __forceinline__ bool run_job(WarpStream& ws, const DecodeParams& P, int j, int lane, const int8_t* xq_s,
-                                        const float2* xs_s, Epi epi) {
-    const Job& jb = ws.jobs[j];
+__device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& P, const DecodeSmem& sm, int j, int lane,
+                                            const int8_t* xq_s, const float2* xs_s, unsigned long long& tp, Epi epi) {
+    const Job jb = ws.jobs[j];                          // registers: the fields are used many times
     bool ok = true;
-    for (int u = ws.first_unit(jb); u < jb.n_units && ok; u += ws.W) {
-        const int g = u / jb.ks, sp = u % jb.ks;
-        const int t0 = (int)((long long)sp * jb.nt / jb.ks), t1 = (int)((long long)(sp + 1) * jb.nt / jb.ks);
-        double v0 = 0.0, v1 = 0.0;
-        switch (jb.kb) {
-            case 8: v0 = tiles_dot<8>(ws, lane, t0, t1, xq_s, xs_s, ok); if (jb.nacc == 2 && ok) v1 = tiles_dot<8>(ws, lane, t0, t1, xq_s, xs_s, ok); break;
-            case 4: v0 = tiles_dot<4>(ws, lane, t0, t1, xq_s, xs_s, ok); if (jb.nacc == 2 && ok) v1 = tiles_dot<4>(ws, lane, t0, t1, xq_s, xs_s, ok); break;
-            case 2: v0 = tiles_dot<2>(ws, lane, t0, t1, xq_s, xs_s, ok); if (jb.nacc == 2 && ok) v1 = tiles_dot<2>(ws, lane, t0, t1, xq_s, xs_s, ok); break;
-            default: v0 = tiles_dot<1>(ws, lane, t0, t1, xq_s, xs_s, ok); if (jb.nacc == 2 && ok) v1 = tiles_dot<1>(ws, lane, t0, t1, xq_s, xs_s, ok); break;
+    int uidx = 0;
+    for (int u = ws.first_cta_unit(jb); u < jb.n_units; u += (int)gridDim.x, uidx++) {
+        const UnitShape s = unit_shape(jb, u, uidx);
+        double a0 = 0.0, a1 = 0.0;
+        for (int i = (ws.warp - s.wrot) & (DNW - 1); i < s.n; i += DNW) {
+            if (i < s.ntu) a0 = tile_consume(ws, lane, jb.kb, s.t0 + i, xq_s, xs_s, a0, ok, &P, &tp);
+            else a1 = tile_consume(ws, lane, jb.kb, s.t0 + i - s.ntu, xq_s, xs_s, a1, ok, &P, &tp);
         }
-        if (!ok) break;
-        if (jb.ks == 1) { epi(g, lane, __double2float_rn(v0), __double2float_rn(v1)); continue; }
-        double* part = P.part + jb.part_off + (size_t)g * jb.ks * jb.nacc * 32;
-        __stcg(part + (sp * jb.nacc) * 32 + lane, v0);
-        if (jb.nacc == 2) __stcg(part + (sp * 2 + 1) * 32 + lane, v1);
-        __threadfence();
-        __syncwarp();
-        unsigned prev = 0;
-        if (lane == 0) prev = atomicAdd(P.counters + jb.cnt_off + g, 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == (unsigned)jb.ks - 1) {              // last split in: fold all of them in split order
-            __threadfence();
-            double s0 = __ldcg(part + lane), s1 = jb.nacc == 2 ? __ldcg(part + 32 + lane) : 0.0;
-            for (int s = 1; s < jb.ks; s++) {
-                s0 = __dadd_rn(s0, __ldcg(part + (s * jb.nacc) * 32 + lane));
-                if (jb.nacc == 2) s1 = __dadd_rn(s1, __ldcg(part + (s * 2 + 1) * 32 + lane));
-            }
-            if (lane == 0) P.counters[jb.cnt_off + g] = 0;
-            epi(g, lane, __double2float_rn(s0), __double2float_rn(s1));
+        prof_mark(P, tp, 18);
+        double* fb = sm.fold + (size_t)(uidx & 1) * DNW * 2 * 32;
+        fb[(ws.warp * 2) * 32 + lane] = a0;
+        fb[(ws.warp * 2 + 1) * 32 + lane] = a1;
+        __syncthreads();
+        if (ws.warp == 0) {
+            double v0 = fb[lane], v1 = fb[32 + lane];
+            #pragma unroll
+            for (int w = 1; w < DNW; w++) { v0 = __dadd_rn(v0, fb[(w * 2) * 32 + lane]); v1 = __dadd_rn(v1, fb[(w * 2 + 1) * 32 + lane]); }
+            if (jb.ks == 1) epi(s.g, lane, __double2float_rn(v0), __double2float_rn(v1));
+            else __stcg(P.part + jb.part_off + ((size_t)s.g * jb.ks + s.sp) * 32 + lane, v0);
         }
+        prof_mark(P, tp, 19);
+    }
+    return ok;
+}
+
+// lm_head: a unit (row group) belongs to one warp; epi(g, lane, v).
+template <class Epi>
+__device__ __forceinline__ bool run_warp_job(WarpStream& ws, int j, int lane, const int8_t* xq_s, const float2* xs_s, Epi epi) {
+    const Job jb = ws.jobs[j];
+    bool ok = true;
+    for (int u = ws.first_warp_unit(jb); u < jb.n_units && ok; u += ws.W) {
+        double acc = 0.0;
+        for (int t = 0; t < jb.nt; t++) acc = tile_consume(ws, lane, jb.kb, t, xq_s, xs_s, acc, ok);
+        if (ok) epi(u, lane, __double2float_rn(acc));
     }
     return ok;
 }
@@ -254,12 +312,54 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
     return q;
 }
 
-// hs[0..E) (shared, fp32) -> rmsnorm * w -> q8_0 in xq_s / xs_s.  Sum of squares in
-// double (every x*x is exact there), then the reference's fp32 expression
-// x * (1/sqrt(float(ss/n) + eps)) * w (src/cpu_infer.cpp:40-46).
-__device__ __forceinline__ void stage_norm_q8(const float* hs, const float* __restrict__ w, int E, float eps, double* red,
-                                              int8_t* xq_s, float2* xs_s) {
+// Residual fold + RMSNorm + q8_0 staging:
+//   hs = src (global fp32; null: hs already holds the vector)
+//        + fp32(sum of the ks cross-CTA partials of the previous projection)   [if part]
+//   CTA 0 publishes hs to commit (the residual stream other phases read later);
+//   xq_s / xs_s = q8_0( hs * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
+// The vector, the partials and the norm weights are all requested before anything
+// waits on them (the weights are cold: read once per token).  Sum of squares in
+// double (every x*x is exact there).
+__device__ __forceinline__ void stage_norm_q8(const float* src, const double* part, int ks, float* commit, float* hs, float* ws_s,
+                                              const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    constexpr int U = 4;
+    for (int i0 = 0; i0 < E; i0 += DNT * U) {
+        float xv[U], wv[U]; double pv[U];
+        #pragma unroll
+        for (int k = 0; k < U; k++) {
+            const int i = i0 + k * DNT + tid;
+            pv[k] = 0.0; xv[k] = 0.f; wv[k] = 0.f;
+            if (i < E) {
+                wv[k] = __ldg(w + i);
+                if (src) xv[k] = __ldcg(src + i);
+                if (part) {
+                    const double* pp = part + (size_t)(i >> 5) * ks * 32 + (i & 31);
+                    double s = 0.0;
+                    for (int sp0 = 0; sp0 < ks; sp0 += 4) {           // four splits requested together
+                        double t4[4];
+                        #pragma unroll
+                        for (int q = 0; q < 4; q++) t4[q] = sp0 + q < ks ? __ldcg(pp + (sp0 + q) * 32) : 0.0;
+                        #pragma unroll
+                        for (int q = 0; q < 4; q++) if (sp0 + q < ks) s = __dadd_rn(s, t4[q]);
+                    }
+                    pv[k] = s;
+                }
+            }
+        }
+        #pragma unroll
+        for (int k = 0; k < U; k++) {
+            const int i = i0 + k * DNT + tid;
+            if (i < E) {
+                ws_s[i] = wv[k];
+                float x = src ? xv[k] : hs[i];
+                if (part) x = __fadd_rn(x, __double2float_rn(pv[k]));
+                hs[i] = x;
+                if (commit && blockIdx.x == 0) __stcg(commit + i, x);
+            }
+        }
+    }
+    __syncthreads();
     double ss = 0.0;
     for (int i = tid; i < E; i += DNT) { const double x = hs[i]; ss = __fma_rn(x, x, ss); }
     #pragma unroll
@@ -273,7 +373,7 @@ __device__ __forceinline__ void stage_norm_q8(const float* hs, const float* __re
     const float scale = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, eps)));
     for (int b = warp; b < E / 32; b += DNW) {
         const int e = b * 32 + lane;
-        const float v = __fmul_rn(__fmul_rn(hs[e], scale), __ldg(w + e));
+        const float v = __fmul_rn(__fmul_rn(hs[e], scale), ws_s[e]);
         xq_s[e] = (int8_t)quant_block_warp(v, lane, xs_s + b, nullptr);
     }
     __syncthreads();
@@ -311,22 +411,16 @@ __device__ __forceinline__ void embed_row(const DecodeParams& P, int token, floa
 // CTA = (kv head, chunk of the causal range); its warps split the chunk.  A warp
 // walks its positions 32 at a time in two passes.  Pass 1, lane = position: the
 // full q.k dot of the lane's K row against all G query heads of the kv head (q
-// comes from shared memory as broadcast reads, so there is no cross-lane
-// reduction and one K read serves the whole GQA group).  Pass 2, lane = dims
-// {lane + 32 i}: the 32 positions' softmax weights (parked in shared memory) times
-// their V rows.  Running state per head: max m (an fp32 score), denominator l and
-// output o[] in double.  States fold warps -> chunk (shared memory, warp order) ->
-// head (global scratch, chunk order, by the last CTA of the kv head to arrive);
-// then o/l is rounded to fp32, stored, and quantized to q8_0 for the O projection.
-__device__ __forceinline__ void softmax_merge(float& m, double& l, float ma, double la, float mb, double lb, double& fa, double& fb) {
-    m = fmaxf(ma, mb);
-    fa = ma == -INFINITY ? 0.0 : exp((double)ma - (double)m);
-    fb = mb == -INFINITY ? 0.0 : exp((double)mb - (double)m);
-    l = __fma_rn(la, fa, __dmul_rn(lb, fb));
-}
-
+// waits in shared memory as doubles, read as broadcasts: no cross-lane reduction,
+// and one K read serves the whole GQA group).  Pass 2, lane = dims {lane + 32 i}:
+// the 32 positions' softmax weights (parked in shared memory) times their V rows.
+// Running state per head: max m (an fp32 score), denominator l and output o[] in
+// double.  States fold warps -> chunk (shared memory) -> head (global scratch, by
+// the last CTA of the kv head to arrive), each fold against the common maximum so
+// that the rescale factors are independent of one another; then o/l is rounded to
+// fp32, stored, and quantized to q8_0 for the O projection.
 template <int HD, int G>
-__device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage) {
+__device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp) {
     constexpr int DPW = HD / 32;           // dims per lane in pass 2 and while folding (dim = lane + 32*i)
     constexpr int SW = HD + 2;             // doubles per (head) state: o[HD], m, l
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -336,9 +430,10 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     const int p0 = (int)((long long)ch * Lp / nch), p1 = (int)((long long)(ch + 1) * Lp / nch);
     double* scr = reinterpret_cast<double*>(stage);                        // [warp][G][SW]
     double* wts = scr + DNW * G * SW;                                       // [warp][32][G]
-    float* qs = reinterpret_cast<float*>(wts + DNW * 32 * G);               // [G][HD]
-    for (int i = tid; i < G * HD; i += DNT) qs[i] = __ldcg(P.q + (size_t)kvh * G * HD + i);
+    double* qs = wts + DNW * 32 * G;                                        // [G][HD]
+    for (int i = tid; i < G * HD; i += DNT) qs[i] = (double)__ldcg(P.q + (size_t)kvh * G * HD + i);
     __syncthreads();
+    prof_mark(P, tp, 14);
     const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
     const int n = p1 - p0, a0 = p0 + (int)((long long)n * warp / DNW), a1 = p0 + (int)((long long)n * (warp + 1) / DNW);
     const __half* kbase = P.kc + ((size_t)l * P.max_seq) * P.KVD + (size_t)kvh * HD;
@@ -361,21 +456,27 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
             #pragma unroll
             for (int j = 0; j < G; j++) d[j] = 0.0;
             const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(valid ? p : a1 - 1) * P.KVD);
-            #pragma unroll 2
-            for (int c = 0; c < HD / 8; c++) {
-                const uint4 ku = __ldcg(kp + c);
-                const __half2* kh = reinterpret_cast<const __half2*>(&ku);
-                float kf[8];
+            constexpr int KC = HD / 8 < 8 ? HD / 8 : 8;                   // 16-byte chunks requested together
+            for (int c0 = 0; c0 < HD / 8; c0 += KC) {
+                uint4 ku[KC];
                 #pragma unroll
-                for (int e = 0; e < 4; e++) { const float2 f = __half22float2(kh[e]); kf[2 * e] = f.x; kf[2 * e + 1] = f.y; }
+                for (int c = 0; c < KC; c++) ku[c] = __ldcg(kp + c0 + c);
                 #pragma unroll
-                for (int j = 0; j < G; j++) {
-                    const float4 qa = *reinterpret_cast<const float4*>(qs + j * HD + c * 8);
-                    const float4 qb = *reinterpret_cast<const float4*>(qs + j * HD + c * 8 + 4);
-                    d[j] = __fma_rn((double)qa.x, (double)kf[0], d[j]); d[j] = __fma_rn((double)qa.y, (double)kf[1], d[j]);
-                    d[j] = __fma_rn((double)qa.z, (double)kf[2], d[j]); d[j] = __fma_rn((double)qa.w, (double)kf[3], d[j]);
-                    d[j] = __fma_rn((double)qb.x, (double)kf[4], d[j]); d[j] = __fma_rn((double)qb.y, (double)kf[5], d[j]);
-                    d[j] = __fma_rn((double)qb.z, (double)kf[6], d[j]); d[j] = __fma_rn((double)qb.w, (double)kf[7], d[j]);
+                for (int c = 0; c < KC; c++) {
+                    const __half2* kh = reinterpret_cast<const __half2*>(&ku[c]);
+                    double kf[8];
+                    #pragma unroll
+                    for (int e = 0; e < 4; e++) { const float2 f = __half22float2(kh[e]); kf[2 * e] = (double)f.x; kf[2 * e + 1] = (double)f.y; }
+                    #pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        const double* qj = qs + j * HD + (c0 + c) * 8;
+                        #pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            const double2 qq = *reinterpret_cast<const double2*>(qj + e);
+                            d[j] = __fma_rn(qq.x, kf[e], d[j]);
+                            d[j] = __fma_rn(qq.y, kf[e + 1], d[j]);
+                        }
+                    }
                 }
             }
             #pragma unroll
@@ -402,20 +503,32 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         __syncwarp();
         // pass 2: o += w[p] * V[p]
         const int np = min(32, a1 - b0);
-        for (int pp = 0; pp < np; pp++) {
-            const __half* vp = vbase + (size_t)(b0 + pp) * P.KVD;
-            double vv[DPW];
+        for (int pp0 = 0; pp0 < np; pp0 += 8) {                              // 8 positions' V rows requested together
+            unsigned short vh[8][DPW];
             #pragma unroll
-            for (int i = 0; i < DPW; i++) vv[i] = (double)__half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(vp) + lane + 32 * i)));
-            #pragma unroll
-            for (int j = 0; j < G; j++) {
-                const double w = wl[pp * G + j];
+            for (int u = 0; u < 8; u++) {
+                const unsigned short* vp = reinterpret_cast<const unsigned short*>(vbase + (size_t)(b0 + min(pp0 + u, np - 1)) * P.KVD);
                 #pragma unroll
-                for (int i = 0; i < DPW; i++) o[j][i] = __fma_rn(w, vv[i], o[j][i]);
+                for (int i = 0; i < DPW; i++) vh[u][i] = __ldcg(vp + lane + 32 * i);
+            }
+            #pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (pp0 + u < np) {
+                    double vd[DPW];
+                    #pragma unroll
+                    for (int i = 0; i < DPW; i++) vd[i] = (double)__half2float(__ushort_as_half(vh[u][i]));
+                    #pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        const double w = wl[(pp0 + u) * G + j];
+                        #pragma unroll
+                        for (int i = 0; i < DPW; i++) o[j][i] = __fma_rn(w, vd[i], o[j][i]);
+                    }
+                }
             }
         }
         __syncwarp();
     }
+    prof_mark(P, tp, 15);
     #pragma unroll
     for (int j = 0; j < G; j++) {
         double* sw = scr + (size_t)(warp * G + j) * SW;
@@ -424,59 +537,78 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         if (lane == 0) { sw[HD] = (double)m[j]; sw[HD + 1] = ls[j]; }
     }
     __syncthreads();
-    // warp j folds head j's DNW warp states in warp order and publishes the chunk partial
+    // warp j folds head j's DNW warp states against their common maximum and publishes the chunk partial
     if (warp < G) {
         const int j = warp, head = kvh * G + j;
-        double ob[DPW], ll; float mm;
-        {
-            const double* s0 = scr + (size_t)j * SW;
-            #pragma unroll
-            for (int i = 0; i < DPW; i++) ob[i] = s0[lane + 32 * i];
-            mm = (float)s0[HD]; ll = s0[HD + 1];
-        }
-        for (int w = 1; w < DNW; w++) {
-            const double* s2 = scr + (size_t)(w * G + j) * SW;
-            float mn; double ln, fa, fb;
-            softmax_merge(mn, ln, mm, ll, (float)s2[HD], s2[HD + 1], fa, fb);
-            #pragma unroll
-            for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(ob[i], fa, __dmul_rn(s2[lane + 32 * i], fb));
-            mm = mn; ll = ln;
-        }
-        double* gp = P.attn_part + ((size_t)head * P.max_chunks + ch) * SW;
+        float mm = -INFINITY;
         #pragma unroll
-        for (int i = 0; i < DPW; i++) __stcg(gp + lane + 32 * i, ob[i]);
-        if (lane == 0) { __stcg(gp + HD, (double)mm); __stcg(gp + HD + 1, ll); }
+        for (int w = 0; w < DNW; w++) mm = fmaxf(mm, (float)scr[(size_t)(w * G + j) * SW + HD]);
+        double f[DNW];
+        #pragma unroll
+        for (int w = 0; w < DNW; w++) {
+            const float mw = (float)scr[(size_t)(w * G + j) * SW + HD];
+            f[w] = mw == -INFINITY ? 0.0 : exp((double)mw - (double)mm);
+        }
+        double ob[DPW], ll = 0.0;
+        #pragma unroll
+        for (int i = 0; i < DPW; i++) ob[i] = 0.0;
+        #pragma unroll
+        for (int w = 0; w < DNW; w++) {
+            const double* s2 = scr + (size_t)(w * G + j) * SW;
+            ll = __fma_rn(s2[HD + 1], f[w], ll);
+            #pragma unroll
+            for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(s2[lane + 32 * i], f[w], ob[i]);
+        }
+        if (nch == 1) {                                                     // the chunk is the whole range: finish here
+            #pragma unroll
+            for (int i = 0; i < DPW; i++) {
+                const float v = __double2float_rn(__ddiv_rn(ob[i], ll));
+                const int e = head * HD + 32 * i + lane;
+                __stcg(P.att + e, v);
+                P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
+            }
+        } else {
+            double* gp = P.attn_part + ((size_t)head * P.max_chunks + ch) * SW;
+            #pragma unroll
+            for (int i = 0; i < DPW; i++) __stcg(gp + lane + 32 * i, ob[i]);
+            if (lane == 0) { __stcg(gp + HD, (double)mm); __stcg(gp + HD + 1, ll); }
+        }
     }
+    prof_mark(P, tp, 16);
+    if (nch == 1) return;
     __threadfence();
     __syncthreads();
     __shared__ unsigned s_prev;
     if (tid == 0) s_prev = atomicAdd(P.attn_cnt + kvh, 1u);
     __syncthreads();
     if (s_prev != (unsigned)nch - 1) return;
-    // last chunk of this kv head: fold the chunk partials in chunk order, normalise, emit fp32 + q8_0
+    // last chunk of this kv head: fold the chunk partials against their common maximum, normalise, emit fp32 + q8_0
     __threadfence();
     if (tid == 0) P.attn_cnt[kvh] = 0;
     if (warp < G) {
         const int j = warp, head = kvh * G + j;
         const double* gp = P.attn_part + (size_t)head * P.max_chunks * SW;
-        double ob[DPW], ll = __ldcg(gp + HD + 1); float mm = (float)__ldcg(gp + HD);
+        float mm = -INFINITY;
+        for (int c = lane; c < nch; c += 32) mm = fmaxf(mm, (float)__ldcg(gp + (size_t)c * SW + HD));
         #pragma unroll
-        for (int i = 0; i < DPW; i++) ob[i] = __ldcg(gp + lane + 32 * i);
-        for (int c = 1; c < nch; c++) {
+        for (int sft = 16; sft; sft >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, sft));
+        double ob[DPW], ll = 0.0;
+        #pragma unroll
+        for (int i = 0; i < DPW; i++) ob[i] = 0.0;
+        for (int c = 0; c < nch; c++) {
             const double* g2 = gp + (size_t)c * SW;
-            float mn; double ln, fa, fb;
-            softmax_merge(mn, ln, mm, ll, (float)__ldcg(g2 + HD), __ldcg(g2 + HD + 1), fa, fb);
+            const float mc = (float)__ldcg(g2 + HD);
+            const double f = mc == -INFINITY ? 0.0 : exp((double)mc - (double)mm);
+            ll = __fma_rn(__ldcg(g2 + HD + 1), f, ll);
             #pragma unroll
-            for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(ob[i], fa, __dmul_rn(__ldcg(g2 + lane + 32 * i), fb));
-            mm = mn; ll = ln;
+            for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(__ldcg(g2 + lane + 32 * i), f, ob[i]);
         }
         #pragma unroll
         for (int i = 0; i < DPW; i++) {
             const float v = __double2float_rn(__ddiv_rn(ob[i], ll));
             const int e = head * HD + 32 * i + lane;
             __stcg(P.att + e, v);
-            const int qv = quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
-            P.att_q[e] = (int8_t)qv;
+            P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
         }
     }
 }
@@ -493,13 +625,18 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     sm.bars = reinterpret_cast<uint64_t*>(smem + (size_t)DNW * DS * DSLOT);
     sm.jobs = reinterpret_cast<Job*>(smem + (size_t)DNW * DS * DSLOT + 256);
     uint8_t* after_jobs = reinterpret_cast<uint8_t*>(sm.jobs) + ((size_t)njobs * sizeof(Job) + 127) / 128 * 128;
+    sm.lp = reinterpret_cast<LayerPtrs*>(after_jobs);              // [<= 64]
+    after_jobs += 64 * sizeof(LayerPtrs);
     sm.cs = reinterpret_cast<float*>(after_jobs);                 // [HD]: cos then sin
     sm.red = reinterpret_cast<double*>(after_jobs + 1024);         // 32 doubles
-    sm.stage = after_jobs + 1024 + 256;
+    sm.fold = reinterpret_cast<double*>(after_jobs + 1024 + 256);
+    sm.stage = after_jobs + 1024 + 256 + kFoldBytes;
     __shared__ int s_ok;
 
     for (int i = tid; i < njobs * (int)(sizeof(Job) / 4); i += DNT)
         reinterpret_cast<int*>(sm.jobs)[i] = __ldg(reinterpret_cast<const int*>(P.jobs) + i);
+    for (int i = tid; i < P.L * (int)(sizeof(LayerPtrs) / 4); i += DNT)
+        reinterpret_cast<int*>(sm.lp)[i] = __ldg(reinterpret_cast<const int*>(P.layers) + i);
     if (lane == 0) {
         #pragma unroll
         for (int s = 0; s < DS; s++) mbar_init(&sm.bars[warp * DS + s], 1);
@@ -514,7 +651,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         return 4 * l + (k == 0 ? 0 : k <= 2 ? 1 : k == 3 ? 2 : 3);
     };
     WarpStream ws;
-    ws.init(sm, warp, lane, step0, step1, job_of_phase(ph0), job_of_phase(ph1));
+    ws.init(sm, P, warp, step0, step1, job_of_phase(ph0), job_of_phase(ph1));
     if (lane == 0) {
         #pragma unroll
         for (int s = 0; s < DS; s++) ws.issue_one();
@@ -523,13 +660,15 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     pdl_wait_prior();
 
     float* hs = reinterpret_cast<float*>(sm.stage);
+    float* wn_s = hs + P.E;
     const int maxin = P.E > P.FF ? P.E : P.FF;
-    int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage + (size_t)P.E * 4);
-    float2* xs_s = reinterpret_cast<float2*>(sm.stage + (size_t)P.E * 4 + maxin);
+    int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage + (size_t)P.E * 8);
+    float2* xs_s = reinterpret_cast<float2*>(sm.stage + (size_t)P.E * 8 + maxin);
     unsigned bar_target = 0;
     bool ok = true;
     const bool single = (step1 - step0 == 1) && (ph1 - ph0 == 1);
 
+    unsigned long long tp = P.prof ? gtime_ns() : 0;
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = P.pos0 + step;
         if (tid < HD / 2) {
@@ -537,25 +676,26 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             sm.cs[tid] = __double2float_rn(cos(th)); sm.cs[HD / 2 + tid] = __double2float_rn(sin(th));
         }
         __syncthreads();
+        prof_mark(P, tp, kProfStep);
         for (int ph = ph0; ph < ph1 && ok; ph++) {
             const int l = ph / 5, k = ph == nph - 1 ? 5 : ph % 5;
             if (k == 0) {
-                // ---- QKV
+                // ---- QKV: h_in = (l == 0) ? embedding : h_mid + down-projection partials of layer l-1
                 if (l == 0) {
                     const int tok = step < P.n_forced ? __ldg(P.in_tokens + step) : __ldcg(P.cur_token);
                     embed_row(P, tok, hs);
                     __syncthreads();
-                    if (blockIdx.x == 0) for (int i = tid; i < P.E; i += DNT) __stcg(P.h + i, hs[i]);
+                    stage_norm_q8(nullptr, nullptr, 0, P.h_in, hs, wn_s, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 } else {
-                    for (int i = tid; i < P.E; i += DNT) hs[i] = __ldcg(P.h + i);
-                    __syncthreads();
+                    const Job& dj = sm.jobs[4 * (l - 1) + 3];
+                    stage_norm_q8(P.h_mid, P.part + dj.part_off, dj.ks, P.h_in, hs, wn_s, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 }
-                stage_norm_q8(hs, P.layers[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
-                const float* bias = P.layers[l].bqkv;
+                prof_mark(P, tp, 0);
+                const float* bias = sm.lp[l].bqkv;
                 const int nq = P.NH * HD;
                 __half* kdst = P.kc + ((size_t)l * P.max_seq + pos) * P.KVD;
                 __half* vdst = P.vc + ((size_t)l * P.max_seq + pos) * P.KVD;
-                ok = run_job(ws, P, 4 * l + 0, lane, xq_s, xs_s, [&](int g, int ln, float v0, float) {
+                ok = run_cta_job(ws, P, sm, 4 * l + 0, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
                     const int p = g * 32 + ln;
                     const float v = __fadd_rn(v0, __ldg(bias + p));
                     const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
@@ -567,23 +707,25 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                         else { out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c))); orig = head * HD + i + HD / 2; }
                         if (p < nq) __stcg(P.q + orig, out);
                         else kdst[orig] = __float2half_rn(out);
-                    } else {
+                    } else if (p < nq + 2 * P.KVD) {
                         vdst[p - nq - P.KVD] = __float2half_rn(v);
                     }
                 });
             } else if (k == 1) {
-                attention_phase<HD, G>(P, l, pos, sm.stage);
+                attention_phase<HD, G>(P, l, pos, sm.stage, tp);
             } else if (k == 2) {
                 stage_copy_q8(P.att_q, P.att_d, P.E / 32, xq_s, xs_s);
-                ok = run_job(ws, P, 4 * l + 1, lane, xq_s, xs_s, [&](int g, int ln, float v0, float) {
-                    const int r = g * 32 + ln;
-                    if (r < P.E) __stcg(P.h + r, __fadd_rn(__ldcg(P.h + r), v0));
+                prof_mark(P, tp, 4);
+                ok = run_cta_job(ws, P, sm, 4 * l + 1, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
+                    // unsplit: the "partial" is the whole sum; keep one path for the consumer
+                    __stcg(P.part + sm.jobs[4 * l + 1].part_off + (size_t)g * 32 + ln, (double)v0);
                 });
             } else if (k == 3) {
-                for (int i = tid; i < P.E; i += DNT) hs[i] = __ldcg(P.h + i);
-                __syncthreads();
-                stage_norm_q8(hs, P.layers[l].ffn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
-                ok = run_job(ws, P, 4 * l + 2, lane, xq_s, xs_s, [&](int g, int ln, float gate, float up) {
+                // ---- gate/up: h_mid = h_in + O-projection partials
+                const Job& oj = sm.jobs[4 * l + 1];
+                stage_norm_q8(P.h_in, P.part + oj.part_off, oj.ks, P.h_mid, hs, wn_s, sm.lp[l].ffn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                prof_mark(P, tp, 6);
+                ok = run_cta_job(ws, P, sm, 4 * l + 2, lane, xq_s, xs_s, tp, [&](int g, int ln, float gate, float up) {
                     const double gd = (double)gate;
                     const float a = __double2float_rn(__dmul_rn(__ddiv_rn(gd, __dadd_rn(1.0, exp(-gd))), (double)up));
                     const int r = g * 32 + ln;                            // FF is a multiple of 32: whole q8_0 block per warp
@@ -592,18 +734,18 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 });
             } else if (k == 4) {
                 stage_copy_q8(P.act_q, P.act_d, P.FF / 32, xq_s, xs_s);
-                ok = run_job(ws, P, 4 * l + 3, lane, xq_s, xs_s, [&](int g, int ln, float v0, float) {
-                    const int r = g * 32 + ln;
-                    if (r < P.E) __stcg(P.h + r, __fadd_rn(__ldcg(P.h + r), v0));
+                prof_mark(P, tp, 8);
+                ok = run_cta_job(ws, P, sm, 4 * l + 3, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
+                    __stcg(P.part + sm.jobs[4 * l + 3].part_off + (size_t)g * 32 + ln, (double)v0);
                 });
             } else {
-                // ---- final norm, lm_head, greedy argmax (lowest index wins ties)
-                for (int i = tid; i < P.E; i += DNT) hs[i] = __ldcg(P.h + i);
-                __syncthreads();
-                stage_norm_q8(hs, P.out_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                // ---- final norm over h_mid + last down-projection partials, lm_head, greedy argmax (lowest index wins ties)
+                const Job& dj = sm.jobs[4 * (P.L - 1) + 3];
+                stage_norm_q8(P.h_mid, P.part + dj.part_off, dj.ks, nullptr, hs, wn_s, P.out_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                prof_mark(P, tp, 10);
                 float best = -INFINITY; int bidx = 0x7fffffff;
                 float* lg = P.logits ? P.logits + (long long)(step - step0) * P.logits_stride : nullptr;
-                ok = run_job(ws, P, 4 * P.L, lane, xq_s, xs_s, [&](int g, int ln, float v0, float) {
+                ok = run_warp_job(ws, 4 * P.L, lane, xq_s, xs_s, [&](int g, int ln, float v0) {
                     const int r = g * 32 + ln;
                     if (r < P.V) {
                         if (lg) lg[r] = v0;
@@ -615,7 +757,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                     const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
                     if (ob > best || (ob == best && oi < bidx)) { best = ob; bidx = oi; }
                 }
-                __syncthreads();                                        // staging region is free again
+                __syncthreads();
                 float* cv = reinterpret_cast<float*>(sm.red); int* ci = reinterpret_cast<int*>(sm.red) + 16;
                 if (lane == 0) { cv[warp] = best; ci[warp] = bidx; }
                 __syncthreads();
@@ -638,9 +780,11 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 }
             }
             ok = __syncthreads_and(ok ? 1 : 0) != 0;          // a wait that gave up in one warp stops the whole CTA
+            prof_mark(P, tp, 2 * k + 1);
             if (!ok) break;
             const bool last = (step == step1 - 1) && (ph == ph1 - 1);
             if (!single && !last) ok = grid_barrier(P.bar, bar_target, &s_ok);
+            prof_mark(P, tp, kProfBarrier);
         }
     }
     if (!ok) {

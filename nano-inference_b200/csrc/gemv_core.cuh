@@ -142,13 +142,14 @@ struct GemvWarp {
     int issued, consumed;
     long long n_units;
     int stride;          // total warps in the grid
+    uint64_t policy;     // L2 evict-first: a weight byte is read once
 
     __device__ __forceinline__ void init(uint8_t* smem, const GemvShape& sh, int warp, int lane) {
         ring = SM::ring(smem) + (size_t)warp * S * TB;
         bars = SM::bars(smem) + warp * S;
         n_units = (long long)sh.n_mats * sh.groups * sh.ks;
         stride = gridDim.x * NW;
-        issued = consumed = 0;
+        issued = consumed = 0; policy = l2_policy_evict_first();
         if (lane == 0) {
             #pragma unroll
             for (int s = 0; s < S; s++) mbar_init(&bars[s], 1);
@@ -163,7 +164,7 @@ struct GemvWarp {
         if (pc.u >= n_units) return;
         const int slot = issued % S;
         mbar_expect_tx(&bars[slot], TB);
-        bulk_g2s(ring + (size_t)slot * TB, pc.gbase + (size_t)pc.t * TB, TB, &bars[slot]);
+        bulk_g2s_hint(ring + (size_t)slot * TB, pc.gbase + (size_t)pc.t * TB, TB, &bars[slot], policy);
         issued++;
         if (++pc.t == pc.t1) cursor_set<KB>(pc, pc.u + stride, n_units, sh);
     }
