@@ -92,7 +92,7 @@ int alloc_tiled(mi_ctx* ctx, mi_model* m, int64_t rows, int64_t cols, uint8_t** 
 int plan_ks(int kind, int groups, int nt, int grid) {
     if (kind != JOB_O && kind != JOB_DOWN) return 1;
     int ks = grid / std::max(groups, 1);
-    return std::max(1, std::min(ks, nt));
+    return std::max(1, std::min(std::min(ks, nt), 4));     // the consumer prologue folds at most four partials per row
 }
 
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
@@ -228,7 +228,7 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
         jb.nacc = nacc; jb.kind = kind; jb.layer = layer;
         const char* force = getenv("MINFER_KS");
         jb.ks = plan_ks(kind, groups, jb.nt, m->grid);
-        if (force && (kind == JOB_O || kind == JOB_DOWN)) jb.ks = std::max(1, std::min(atoi(force), jb.nt));
+        if (force && (kind == JOB_O || kind == JOB_DOWN)) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
         jb.n_units = groups * jb.ks;
         jb.part_off = (int)part_off;
         if (kind == JOB_O || kind == JOB_DOWN) part_off += (size_t)groups * jb.ks * 32;
@@ -353,7 +353,7 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
         (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NKV)) ||
         (st = dev_alloc(ctx, m, &P.part, part_off)) ||
         (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
-        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 1)))
+        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 64)))
         return st;
     P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
     m->prof_buf = P.prof;
@@ -426,7 +426,7 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
     const int nph = 5 * m->L + 1;
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
     if (mode == MI_DECODE_PERSISTENT) {
-        MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, sizeof(unsigned), ctx->stream));
+        MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 64 * sizeof(unsigned), ctx->stream));
         if ((st = dispatch_launch(ctx, m, P, 0, n_steps, 0, nph, true))) return st;
     } else if (mode == MI_DECODE_PER_PHASE) {
         for (int s = 0; s < n_steps; s++) {

@@ -111,8 +111,8 @@ constexpr int kFoldBytes = 2 * DNW * 2 * 32 * 8;      // two buffers of [warp][a
 
 __host__ __device__ inline size_t decode_stage_bytes(int E, int FF, int HD, int G) {
     const int maxin = E > FF ? E : FF;
-    size_t a = (size_t)E * 8 + maxin + (size_t)(maxin / 32) * 8;      // hs, norm weights, xq, xs
-    size_t b = (size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * HD * 8;   // attention: states, weights, q (double)
+    size_t a = (size_t)maxin + (size_t)(maxin / 32) * 8;               // xq, xs
+    size_t b = (size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * (HD + 16) * 8;   // attention: states, weights, q (double, padded)
     return ((a > b ? a : b) + 127) / 128 * 128;
 }
 __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, int HD, int G) {
@@ -120,23 +120,27 @@ __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, in
            decode_stage_bytes(E, FF, HD, G);
 }
 
-// close the current profile interval: charge the time since t to slot k (CTA 0, thread 0 only)
+// close the current profile interval: charge the time since t to slot k (CTA 0, thread 0 only).
+// The sums live in shared memory and are flushed once at kernel exit, so a mark costs a
+// timer read and a shared-memory add, not a global round trip on the critical path.
+__shared__ unsigned long long s_prof[kProfSlots];
 __device__ __forceinline__ void prof_mark(const DecodeParams& P, unsigned long long& t, int k) {
-    if (P.prof && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); P.prof[k] += n - t; t = n; }
+    if (P.prof && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); s_prof[k] += n - t; t = n; }
 }
 
 // ---- grid barrier: monotonic arrival counter, bounded wait -----------------------
+// The release on the arrival orders this CTA's earlier writes (made visible to thread 0
+// by the __syncthreads) before it; the acquire on the poll orders later reads after it.
 __device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned& target, int* ok_s) {
     __syncthreads();
     if (threadIdx.x == 0) {
         target += gridDim.x;
-        __threadfence();
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar) : "memory");
         bool ok = true;
         unsigned v;
         unsigned long long t0 = 0;
         for (unsigned it = 0;; it++) {
-            asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
             if ((int)(v - target) >= 0) break;
             if ((it & 1023u) == 1023u) {
                 const unsigned long long now = gtime_ns();
@@ -293,17 +297,25 @@ __device__ __forceinline__ bool run_warp_job(WarpStream& ws, int j, int lane, co
 
 // ---- activation staging (whole CTA; ends with __syncthreads) -----------------------
 
+// Warp-wide maximum of non-negative floats and warp-wide integer sum as single redux
+// instructions (the bit pattern of a non-negative float orders like an unsigned integer);
+// a shuffle tree costs five issue slots of a pipe that retires one warp instruction per clock.
+__device__ __forceinline__ float warp_max_nonneg(float a) { return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(a))); }
+__device__ __forceinline__ int warp_sum_int(int v) { return __reduce_add_sync(0xffffffffu, v); }
+// warp-wide maximum of arbitrary finite floats (or -inf): order-preserving key
+__device__ __forceinline__ float warp_max_float(float a) {
+    const unsigned b = __float_as_uint(a), key = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    const unsigned m = __reduce_max_sync(0xffffffffu, key);
+    return __uint_as_float((m & 0x80000000u) ? (m & 0x7fffffffu) : ~m);
+}
+
 // q8_0 of one 32-element block held one element per lane; returns the int8 value,
 // writes {fp32 of fp16(a/127), float(8*sum q)} through lane 0.
 __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_out, __half* xd_out) {
-    float a = fabsf(v);
-    #pragma unroll
-    for (int o = 16; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    const float a = warp_max_nonneg(fabsf(v));
     const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
     const int q = __float2int_rn(__fmul_rn(v, inv));
-    int s = q;
-    #pragma unroll
-    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const int s = warp_sum_int(q);
     if (lane == 0) {
         const __half d = __float2half_rn(__fdiv_rn(a, 127.f));
         if (xs_out) *xs_out = make_float2(__half2float(d), __int2float_rn(8 * s));
@@ -313,70 +325,104 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
 }
 
 // Residual fold + RMSNorm + q8_0 staging:
-//   hs = src (global fp32; null: hs already holds the vector)
-//        + fp32(sum of the ks cross-CTA partials of the previous projection)   [if part]
-//   CTA 0 publishes hs to commit (the residual stream other phases read later);
-//   xq_s / xs_s = q8_0( hs * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
-// The vector, the partials and the norm weights are all requested before anything
-// waits on them (the weights are cold: read once per token).  Sum of squares in
-// double (every x*x is exact there).
-__device__ __forceinline__ void stage_norm_q8(const float* src, const double* part, int ks, float* commit, float* hs, float* ws_s,
-                                              const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    constexpr int U = 4;
-    for (int i0 = 0; i0 < E; i0 += DNT * U) {
-        float xv[U], wv[U]; double pv[U];
-        #pragma unroll
-        for (int k = 0; k < U; k++) {
-            const int i = i0 + k * DNT + tid;
-            pv[k] = 0.0; xv[k] = 0.f; wv[k] = 0.f;
-            if (i < E) {
-                wv[k] = __ldg(w + i);
-                if (src) xv[k] = __ldcg(src + i);
-                if (part) {
-                    const double* pp = part + (size_t)(i >> 5) * ks * 32 + (i & 31);
-                    double s = 0.0;
-                    for (int sp0 = 0; sp0 < ks; sp0 += 4) {           // four splits requested together
-                        double t4[4];
-                        #pragma unroll
-                        for (int q = 0; q < 4; q++) t4[q] = sp0 + q < ks ? __ldcg(pp + (sp0 + q) * 32) : 0.0;
-                        #pragma unroll
-                        for (int q = 0; q < 4; q++) if (sp0 + q < ks) s = __dadd_rn(s, t4[q]);
-                    }
-                    pv[k] = s;
-                }
-            }
+//   x = src (global fp32) or the embedding row of `token` (src == null)
+//       + fp32(sum of the ks cross-CTA partials of the previous projection)   [if part]
+//   CTA 0 publishes x to commit (the residual stream other phases read later);
+//   xq_s / xs_s = q8_0( x * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
+// Warp w owns the 32-element blocks w, w+8, ...; lane = element, so a thread holds at most
+// NB values and everything stays in registers.  All loads (vector, partials, norm weights)
+// are requested before anything waits on them, and the NB quantizer chains of a warp are
+// interleaved so their shuffle latencies overlap.  Sum of squares in double (every x*x is
+// exact there).
+template <int NB>
+__device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const float* src, int token, const double* part, int ks,
+                                                float* commit, const float* __restrict__ w, int E, float eps, double* red,
+                                                int8_t* xq_s, float2* xs_s) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nb = E / 32;
+    // pass A: request everything (vector, norm weights, up to 4 partials per element); no use of any value
+    float x[NB], wv[NB]; double pt[NB][4];
+    #pragma unroll
+    for (int k = 0; k < NB; k++) {
+        const int b = min(warp + k * DNW, nb - 1), e = b * 32 + lane;      // clamped: every address is valid
+        wv[k] = __ldg(w + e);
+        if (src) x[k] = __ldcg(src + e);
+        else {                                                  // embedding: value (nibble - 8) * d (src/gguf.h:94-102)
+            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
+            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
+            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
+            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
+            x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
         }
         #pragma unroll
-        for (int k = 0; k < U; k++) {
-            const int i = i0 + k * DNT + tid;
-            if (i < E) {
-                ws_s[i] = wv[k];
-                float x = src ? xv[k] : hs[i];
-                if (part) x = __fadd_rn(x, __double2float_rn(pv[k]));
-                hs[i] = x;
-                if (commit && blockIdx.x == 0) __stcg(commit + i, x);
-            }
+        for (int q = 0; q < 4; q++) pt[k][q] = 0.0;
+        if (part) {
+            const double* pp = part + (size_t)b * ks * 32 + lane;
+            #pragma unroll
+            for (int q = 0; q < 4; q++) if (q < ks) pt[k][q] = __ldcg(pp + q * 32);
         }
     }
-    __syncthreads();
+    // pass B: fold the partials in split order (ks <= 4, enforced when the jobs are planned)
+    double pv[NB];
+    #pragma unroll
+    for (int k = 0; k < NB; k++) {
+        double s = pt[k][0];
+        #pragma unroll
+        for (int q = 1; q < 4; q++) if (q < ks) s = __dadd_rn(s, pt[k][q]);
+        pv[k] = s;
+        if (warp + k * DNW >= nb) { x[k] = 0.f; pv[k] = 0.0; }         // a clamped duplicate: contributes nothing
+    }
+    unsigned long long tq = gtime_ns();
     double ss = 0.0;
-    for (int i = tid; i < E; i += DNT) { const double x = hs[i]; ss = __fma_rn(x, x, ss); }
+    #pragma unroll
+    for (int k = 0; k < NB; k++) {
+        if (part) x[k] = __fadd_rn(x[k], __double2float_rn(pv[k]));
+        const int b = warp + k * DNW;
+        if (b < nb && commit && blockIdx.x == 0) __stcg(commit + b * 32 + lane, x[k]);
+        const double xd = x[k]; ss = __fma_rn(xd, xd, ss);
+    }
     #pragma unroll
     for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
     if (lane == 0) red[warp] = ss;
+    prof_mark(P, tq, 23);
     __syncthreads();
+    prof_mark(P, tq, 24);
     double tot = 0.0;
     #pragma unroll
     for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
     const float mean = __double2float_rn(__ddiv_rn(tot, (double)E));
     const float scale = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    for (int b = warp; b < E / 32; b += DNW) {
-        const int e = b * 32 + lane;
-        const float v = __fmul_rn(__fmul_rn(hs[e], scale), ws_s[e]);
-        xq_s[e] = (int8_t)quant_block_warp(v, lane, xs_s + b, nullptr);
+    float v[NB], a[NB]; int q[NB], sq[NB];
+    #pragma unroll
+    for (int k = 0; k < NB; k++) { v[k] = __fmul_rn(__fmul_rn(x[k], scale), wv[k]); a[k] = fabsf(v[k]); }
+    #pragma unroll
+    for (int k = 0; k < NB; k++) a[k] = warp_max_nonneg(a[k]);
+    #pragma unroll
+    for (int k = 0; k < NB; k++) {
+        const float inv = a[k] > 0.f ? __fdiv_rn(127.f, a[k]) : 0.f;
+        q[k] = __float2int_rn(__fmul_rn(v[k], inv)); sq[k] = q[k];
     }
+    #pragma unroll
+    for (int k = 0; k < NB; k++) sq[k] = warp_sum_int(sq[k]);
+    #pragma unroll
+    for (int k = 0; k < NB; k++) {
+        const int b = warp + k * DNW;
+        if (b < nb) {
+            xq_s[b * 32 + lane] = (int8_t)q[k];
+            if (lane == 0) xs_s[b] = make_float2(__half2float(__float2half_rn(__fdiv_rn(a[k], 127.f))), __int2float_rn(8 * sq[k]));
+        }
+    }
+    prof_mark(P, tq, 25);
     __syncthreads();
+    prof_mark(P, tq, 26);
+}
+
+__device__ __forceinline__ void stage_norm_q8(const DecodeParams& P, const float* src, int token, const double* part, int ks, float* commit,
+                                              const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
+    const int per_warp = (E / 32 + DNW - 1) / DNW;
+    if (per_warp <= 4) stage_norm_q8_t<4>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+    else if (per_warp <= 8) stage_norm_q8_t<8>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+    else if (per_warp <= 16) stage_norm_q8_t<16>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+    else stage_norm_q8_t<64>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
 }
 
 // q8_0 vector already in global memory (written by another CTA): copy through L2.
@@ -391,20 +437,6 @@ __device__ __forceinline__ void stage_copy_q8(const int8_t* xq, const __half* xd
         xs_s[b] = make_float2(__half2float(d), __int2float_rn(8 * sum_x_block(xa, xc)));
     }
     __syncthreads();
-}
-
-// row `token` of the tiled embedding matrix -> hs (fp32), value (nibble - 8) * d
-// (reference src/gguf.h:94-102).
-__device__ __forceinline__ void embed_row(const DecodeParams& P, int token, float* hs) {
-    const int g = token >> 5, r = token & 31, kb = P.emb_kb, tb = kb * kTileRowBytes;
-    for (int e = threadIdx.x; e < P.E; e += DNT) {
-        const int b = e >> 5, el = e & 31, t = b / kb, k = b % kb;
-        const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * tb;
-        const uint8_t byte = __ldg(tile + ((size_t)k * 32 + r) * 16 + (el & 15));
-        const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + k) * 2)));
-        const int n = el < 16 ? (byte & 0x0F) : (byte >> 4);
-        hs[e] = __fmul_rn(__int2float_rn(n - 8), d);
-    }
 }
 
 // ---- attention --------------------------------------------------------------------
@@ -430,8 +462,12 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     const int p0 = (int)((long long)ch * Lp / nch), p1 = (int)((long long)(ch + 1) * Lp / nch);
     double* scr = reinterpret_cast<double*>(stage);                        // [warp][G][SW]
     double* wts = scr + DNW * G * SW;                                       // [warp][32][G]
-    double* qs = wts + DNW * 32 * G;                                        // [G][HD]
-    for (int i = tid; i < G * HD; i += DNT) qs[i] = (double)__ldcg(P.q + (size_t)kvh * G * HD + i);
+    constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2;                   // lanes per position in pass 1, dims per lane, padded stride
+    double* qs = wts + DNW * 32 * G;                                        // [G][LPP][QSTR]: 16-byte skew per lane, conflict-free
+    for (int i = tid; i < G * HD; i += DNT) {
+        const int j = i / HD, d = i % HD;
+        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.q + (size_t)kvh * G * HD + i);
+    }
     __syncthreads();
     prof_mark(P, tp, 14);
     const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
@@ -447,62 +483,88 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         for (int i = 0; i < DPW; i++) o[j][i] = 0.0;
     }
     for (int b0 = a0; b0 < a1; b0 += 32) {                                  // warp-uniform trip count
-        const int p = b0 + lane;
-        const bool valid = p < a1;
-        // pass 1: scores of position p for the G heads
-        float sc[G];
+        const int np = min(32, a1 - b0);
+        // pass 1: eight lanes share a position (DPL dims each), four positions per sweep; the
+        // scores of the batch are parked in the weights buffer, one row per position.  All K rows
+        // of the batch are requested before the first one is used.
         {
-            double d[G];
+            const int sub = lane >> 3, li = lane & 7;
+            constexpr int KV4 = DPL * 2 / 16 > 0 ? DPL * 2 / 16 : 1;        // 16-byte loads per lane and position
+            uint4 kraw[8][KV4];
             #pragma unroll
-            for (int j = 0; j < G; j++) d[j] = 0.0;
-            const uint4* kp = reinterpret_cast<const uint4*>(kbase + (size_t)(valid ? p : a1 - 1) * P.KVD);
-            constexpr int KC = HD / 8 < 8 ? HD / 8 : 8;                   // 16-byte chunks requested together
-            for (int c0 = 0; c0 < HD / 8; c0 += KC) {
-                uint4 ku[KC];
-                #pragma unroll
-                for (int c = 0; c < KC; c++) ku[c] = __ldcg(kp + c0 + c);
-                #pragma unroll
-                for (int c = 0; c < KC; c++) {
-                    const __half2* kh = reinterpret_cast<const __half2*>(&ku[c]);
-                    double kf[8];
+            for (int sw = 0; sw < 8; sw++) {
+                if (sw * 4 >= np) continue;                                  // warp-uniform
+                const int pi = min(sw * 4 + sub, np - 1);
+                const __half* kr = kbase + (size_t)(b0 + pi) * P.KVD + li * DPL;
+                if constexpr (DPL >= 8) {
                     #pragma unroll
-                    for (int e = 0; e < 4; e++) { const float2 f = __half22float2(kh[e]); kf[2 * e] = (double)f.x; kf[2 * e + 1] = (double)f.y; }
-                    #pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        const double* qj = qs + j * HD + (c0 + c) * 8;
-                        #pragma unroll
-                        for (int e = 0; e < 8; e += 2) {
-                            const double2 qq = *reinterpret_cast<const double2*>(qj + e);
-                            d[j] = __fma_rn(qq.x, kf[e], d[j]);
-                            d[j] = __fma_rn(qq.y, kf[e + 1], d[j]);
-                        }
-                    }
+                    for (int c = 0; c < KV4; c++) kraw[sw][c] = __ldcg(reinterpret_cast<const uint4*>(kr) + c);
+                } else {
+                    const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(kr));
+                    kraw[sw][0] = make_uint4(k2.x, k2.y, 0u, 0u);
                 }
             }
             #pragma unroll
-            for (int j = 0; j < G; j++) sc[j] = valid ? __fmul_rn(__double2float_rn(d[j]), inv) : -INFINITY;
+            for (int sw = 0; sw < 8; sw++) {
+                if (sw * 4 < np) {                                           // warp-uniform
+                    const int pi = sw * 4 + sub;
+                    double kd[DPL];
+                    #pragma unroll
+                    for (int c = 0; c < KV4; c++) {
+                        const __half2* hh = reinterpret_cast<const __half2*>(&kraw[sw][c]);
+                        #pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            if (c * 8 + 2 * e < DPL) {
+                                const float2 f = __half22float2(hh[e]);
+                                kd[c * 8 + 2 * e] = (double)f.x; kd[c * 8 + 2 * e + 1] = (double)f.y;
+                            }
+                        }
+                    }
+                    double d[G];
+                    #pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        const double* qj = qs + (j * LPP + li) * QSTR;
+                        double acc = 0.0;
+                        #pragma unroll
+                        for (int e = 0; e < DPL; e += 2) {
+                            const double2 qq = *reinterpret_cast<const double2*>(qj + e);
+                            acc = __fma_rn(qq.x, kd[e], acc);
+                            acc = __fma_rn(qq.y, kd[e + 1], acc);
+                        }
+                        d[j] = acc;
+                    }
+                    #pragma unroll
+                    for (int sft = 1; sft <= 4; sft <<= 1)
+                        #pragma unroll
+                        for (int j = 0; j < G; j++) d[j] = __dadd_rn(d[j], __shfl_xor_sync(0xffffffffu, d[j], sft));
+                    if (li == 0 && pi < np) {
+                        #pragma unroll
+                        for (int j = 0; j < G; j++) wl[pi * G + j] = (double)__fmul_rn(__double2float_rn(d[j]), inv);
+                    }
+                }
+            }
         }
+        __syncwarp();
+        const bool valid = lane < np;
+        float sc[G];
+        #pragma unroll
+        for (int j = 0; j < G; j++) sc[j] = valid ? (float)wl[lane * G + j] : -INFINITY;
+        __syncwarp();
         // new running max, rescale, this batch's weights
         #pragma unroll
         for (int j = 0; j < G; j++) {
-            float bm = sc[j];
-            #pragma unroll
-            for (int sft = 16; sft; sft >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, sft));
+            const float bm = warp_max_float(sc[j]);
             const float mn = fmaxf(m[j], bm);                                // finite: the batch holds a valid position
             const double cr = m[j] == -INFINITY ? 0.0 : exp((double)m[j] - (double)mn);
             const double w = valid ? exp((double)sc[j] - (double)mn) : 0.0;
-            wl[lane * G + j] = w;
-            double wsum = w;
-            #pragma unroll
-            for (int sft = 16; sft; sft >>= 1) wsum = __dadd_rn(wsum, __shfl_xor_sync(0xffffffffu, wsum, sft));
-            ls[j] = __fma_rn(ls[j], cr, wsum);
+            wl[lane * G + j] = w;                                            // the denominator picks the weights up in pass 2
+            ls[j] = __dmul_rn(ls[j], cr);
             #pragma unroll
             for (int i = 0; i < DPW; i++) o[j][i] = __dmul_rn(o[j][i], cr);
             m[j] = mn;
         }
         __syncwarp();
         // pass 2: o += w[p] * V[p]
-        const int np = min(32, a1 - b0);
         for (int pp0 = 0; pp0 < np; pp0 += 8) {                              // 8 positions' V rows requested together
             unsigned short vh[8][DPW];
             #pragma unroll
@@ -520,6 +582,7 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
                     #pragma unroll
                     for (int j = 0; j < G; j++) {
                         const double w = wl[(pp0 + u) * G + j];
+                        ls[j] = __dadd_rn(ls[j], w);
                         #pragma unroll
                         for (int i = 0; i < DPW; i++) o[j][i] = __fma_rn(w, vd[i], o[j][i]);
                     }
@@ -632,6 +695,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     sm.fold = reinterpret_cast<double*>(after_jobs + 1024 + 256);
     sm.stage = after_jobs + 1024 + 256 + kFoldBytes;
     __shared__ int s_ok;
+    if (tid < kProfSlots) s_prof[tid] = 0;
 
     for (int i = tid; i < njobs * (int)(sizeof(Job) / 4); i += DNT)
         reinterpret_cast<int*>(sm.jobs)[i] = __ldg(reinterpret_cast<const int*>(P.jobs) + i);
@@ -659,12 +723,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     pdl_launch_dependents();
     pdl_wait_prior();
 
-    float* hs = reinterpret_cast<float*>(sm.stage);
-    float* wn_s = hs + P.E;
     const int maxin = P.E > P.FF ? P.E : P.FF;
-    int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage + (size_t)P.E * 8);
-    float2* xs_s = reinterpret_cast<float2*>(sm.stage + (size_t)P.E * 8 + maxin);
-    unsigned bar_target = 0;
+    int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage);
+    float2* xs_s = reinterpret_cast<float2*>(sm.stage + maxin);
+    unsigned bar_gen = 0;
     bool ok = true;
     const bool single = (step1 - step0 == 1) && (ph1 - ph0 == 1);
 
@@ -683,12 +745,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 // ---- QKV: h_in = (l == 0) ? embedding : h_mid + down-projection partials of layer l-1
                 if (l == 0) {
                     const int tok = step < P.n_forced ? __ldg(P.in_tokens + step) : __ldcg(P.cur_token);
-                    embed_row(P, tok, hs);
-                    __syncthreads();
-                    stage_norm_q8(nullptr, nullptr, 0, P.h_in, hs, wn_s, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                    stage_norm_q8(P, nullptr, tok, nullptr, 0, P.h_in, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 } else {
                     const Job& dj = sm.jobs[4 * (l - 1) + 3];
-                    stage_norm_q8(P.h_mid, P.part + dj.part_off, dj.ks, P.h_in, hs, wn_s, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                    stage_norm_q8(P, P.h_mid, 0, P.part + dj.part_off, dj.ks, P.h_in, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 }
                 prof_mark(P, tp, 0);
                 const float* bias = sm.lp[l].bqkv;
@@ -723,7 +783,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             } else if (k == 3) {
                 // ---- gate/up: h_mid = h_in + O-projection partials
                 const Job& oj = sm.jobs[4 * l + 1];
-                stage_norm_q8(P.h_in, P.part + oj.part_off, oj.ks, P.h_mid, hs, wn_s, sm.lp[l].ffn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                stage_norm_q8(P, P.h_in, 0, P.part + oj.part_off, oj.ks, P.h_mid, sm.lp[l].ffn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 prof_mark(P, tp, 6);
                 ok = run_cta_job(ws, P, sm, 4 * l + 2, lane, xq_s, xs_s, tp, [&](int g, int ln, float gate, float up) {
                     const double gd = (double)gate;
@@ -741,7 +801,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             } else {
                 // ---- final norm over h_mid + last down-projection partials, lm_head, greedy argmax (lowest index wins ties)
                 const Job& dj = sm.jobs[4 * (P.L - 1) + 3];
-                stage_norm_q8(P.h_mid, P.part + dj.part_off, dj.ks, nullptr, hs, wn_s, P.out_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                stage_norm_q8(P, P.h_mid, 0, P.part + dj.part_off, dj.ks, nullptr, P.out_norm, P.E, P.eps, sm.red, xq_s, xs_s);
                 prof_mark(P, tp, 10);
                 float best = -INFINITY; int bidx = 0x7fffffff;
                 float* lg = P.logits ? P.logits + (long long)(step - step0) * P.logits_stride : nullptr;
@@ -783,9 +843,13 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             prof_mark(P, tp, 2 * k + 1);
             if (!ok) break;
             const bool last = (step == step1 - 1) && (ph == ph1 - 1);
-            if (!single && !last) ok = grid_barrier(P.bar, bar_target, &s_ok);
+            if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
             prof_mark(P, tp, kProfBarrier);
         }
+    }
+    if (P.prof && blockIdx.x == 0) {
+        __syncthreads();
+        if (tid < kProfSlots) P.prof[tid] += s_prof[tid];
     }
     if (!ok) {
         if (lane == 0) atomicMax(P.err, MI_ERR_TIMEOUT);
