@@ -1,18 +1,25 @@
 #!/usr/bin/env python
 """Benchmark of the B200-native quantized decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemv|decode]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|gemv]
 
 Prints ONE JSON line on rank 0.  For N > 1 it is launched by torch.distributed.run
-(one rank per GPU).  See DESIGN.md, "Measurement", for what each field means.
+(one rank per GPU).  DESIGN.md, "Measurement", says what each field means.
 
-Workload "gemv" (config 1 of BASELINE.json): the six q4_0 GEMV shapes, each as
-one launch over a stack of distinct matrices totalling >= 512 MiB so that every
-weight byte comes from HBM (inputs larger than the 126 MB L2; no flush needed).
-A step is one pass over all six stacks.  value = algorithmic weight bytes / time.
+Workload "decode" (default; config 2 of BASELINE.json): Qwen2.5-1.5B-shape all-q4_0
+model with seeded random weights (written by the package's gguf_synth), fp16 KV cache
+for 4096 positions, a 64-token seeded prompt, then batch-1 greedy decode.  A step is
+one generated token; K steps run inside one launch of the persistent decode kernel.
+value = tokens / second.  The roofline object is the decode kernel's algorithmic bytes
+(q4_0 weights + fp16 KV read/written per token) over its device time; `gemv_roofline`
+adds the standalone q4_0 GEMV kernel measured on the six sweep shapes of config 1.
 
-`--impl reference` times the reference's own CPU path (its matvec, compiled from
-the reference sources into oracle/_ref) on a bounded sample of the same workload.
+Workload "gemv" (config 1): only the six-shape GEMV sweep, each shape as one launch over
+a stack of distinct matrices (>= 512 MiB, larger than the L2), value in GB/s.
+
+`--impl reference` times the reference's own CPU program on the box's host cores:
+cpu_infer (compiled unmodified into oracle/_ref) on the same GGUF file for the decode
+workload, its matvec for the gemv workload, on a bounded sample.
 """
 from __future__ import annotations
 
@@ -30,6 +37,12 @@ sys.path.insert(0, str(ROOT))
 
 SWEEP = [(1536, 1536), (256, 1536), (8960, 1536), (1536, 8960), (151936, 1536), (11008, 2048)]   # (out, in)
 STACK_BYTES = 512 << 20
+MODEL_PRESET = "1.5b"
+MODEL_SEED = 20251
+PROMPT_LEN = 64
+MAX_SEQ = 4096
+DECODE_METRIC = "batch-1 greedy decode tok/s, Qwen2.5-1.5B shape, all-q4_0 weights, q8_0 activations, fp16 KV"
+GEMV_METRIC = "q4_0 GEMV HBM GB/s (6-shape sweep, algorithmic q4_0 weight bytes / time)"
 
 
 def q4_bytes(rows, cols):
@@ -42,6 +55,28 @@ def measured_peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def model_path():
+    return Path(os.environ.get("MINFER_BENCH_DIR", tempfile.gettempdir())) / f"minfer_bench_{MODEL_PRESET}_seed{MODEL_SEED}.gguf"
+
+
+def ensure_model():
+    """The synthetic GGUF both arms read (written once per box)."""
+    p = model_path()
+    if not p.exists():
+        synth = ROOT / "nano-inference_b200" / "bin" / "gguf_synth"
+        if not synth.exists():
+            raise SystemExit(f"{synth} not built: run `python nano-inference_b200/build.py`")
+        tmp = p.with_suffix(f".tmp{os.getpid()}")
+        subprocess.run([str(synth), str(tmp), "--preset", MODEL_PRESET, "--seed", str(MODEL_SEED)], check=True, capture_output=True)
+        os.replace(tmp, p)
+    return p
+
+
+def prompt_ids(vocab):
+    import numpy as np
+    return [int(t) for t in np.random.default_rng(MODEL_SEED).integers(0, vocab, PROMPT_LEN)]
 
 
 # ------------------------------------------------------------------ clocks sampling
@@ -90,12 +125,17 @@ class ClockSampler:
 
 # ------------------------------------------------------------------ reference arm (CPU)
 
-def ref_matvec_sample(seconds_per_shape=2.0, shapes=None):
-    """Time the reference's matvec (src/cpu_infer.cpp:22-32, all OpenMP threads) on one
-    matrix per sweep shape.  Returns (GB/s over algorithmic q4_0 bytes, threads, description, ms per pass)."""
+def _oracle_util():
     sys.path.insert(0, str(ROOT / "tests"))
-    import numpy as np
     import oracle_util as ou
+    return ou
+
+
+def ref_matvec_sample(seconds_per_shape=2.0, shapes=None):
+    """The reference's matvec (src/cpu_infer.cpp:22-32, all OpenMP threads) on one matrix per sweep shape.
+    Returns (GB/s over algorithmic q4_0 bytes, threads, kind, ms per pass)."""
+    import numpy as np
+    ou = _oracle_util()
     shapes = shapes or SWEEP
     kind = "reference" if ou.have_ref() else "port"
     rng = np.random.default_rng(0)
@@ -120,31 +160,72 @@ def ref_matvec_sample(seconds_per_shape=2.0, shapes=None):
                 break
         tot_bytes += q4_bytes(rows, cols)
         tot_s += dt / n
+    return tot_bytes / tot_s / 1e9, ou.lib().orc_num_threads(), kind, tot_s * 1e3
+
+
+def ref_decode_sample(n_forwards, warm_forwards=1):
+    """The reference's cpu_infer (unmodified, all host threads) on the bench model: seconds per forward pass,
+    measured as the difference between a run of warm_forwards and a run of warm_forwards + n_forwards passes
+    (which removes process start, mmap and page-in).  Falls back to the oracle port where oracle/_ref is absent.
+    Returns (tok/s, threads, kind, description)."""
+    ou = _oracle_util()
+    path = ensure_model()
     threads = ou.lib().orc_num_threads()
-    return tot_bytes / tot_s / 1e9, threads, kind, tot_s * 1e3
+    ids = prompt_ids(151936)
+    if ou.have_ref():
+        def run(forwards):                      # cpu_infer runs len(prompt) + n_gen forward passes
+            _, dt = ou.run_ref_cpu_infer(path, forwards - 1, ids[:1], threads=threads)
+            return dt
+        kind = "reference"
+    else:
+        import gguf_util as gu
+        g = gu.GgufReader(path)
+
+        def run(forwards):
+            m = ou.OracleModel(g, act_q8=False, kv_f16=False, max_seq=forwards + 1)
+            t0 = time.perf_counter()
+            tok = ids[0]
+            for _ in range(forwards):
+                tok, _, _ = m.forward(tok, want_logits=False)
+            return time.perf_counter() - t0
+        kind = "port"
+    t_a = run(max(2, warm_forwards + 1))
+    t_b = run(max(2, warm_forwards + 1) + n_forwards)
+    per = max(t_b - t_a, 1e-9) / n_forwards
+    desc = (f"{n_forwards} forward passes of cpu_infer (fp32 activations, fp32 KV) on the bench model at positions "
+            f"{max(2, warm_forwards + 1)}..{max(2, warm_forwards + 1) + n_forwards - 1}, all host threads; start-up subtracted")
+    return 1.0 / per, threads, kind, desc
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    steps = max(1, args.steps)
-    per_shape = min(2.0, 120.0 / (6 * (steps + args.warmup)))
-    for _ in range(args.warmup):
-        ref_matvec_sample(per_shape)
-    vals, ms = [], []
-    for _ in range(steps):
-        v, threads, kind, m = ref_matvec_sample(per_shape)
-        vals.append(v); ms.append(m)
-    value = sum(vals) / len(vals)
-    sample = "one matrix per sweep shape (1 of the GPU arm's stacked copies), fp32 activations, cpu_infer matvec"
+    if args.workload == "gemv":
+        steps = max(1, args.steps)
+        per_shape = min(2.0, 120.0 / (6 * (steps + args.warmup)))
+        for _ in range(args.warmup):
+            ref_matvec_sample(per_shape)
+        vals, ms = [], []
+        for _ in range(steps):
+            v, threads, kind, m = ref_matvec_sample(per_shape)
+            vals.append(v); ms.append(m)
+        value, ms_step, unit, metric = sum(vals) / len(vals), sum(ms) / len(ms), "GB/s", GEMV_METRIC
+        sample = "one matrix per sweep shape (1 of the GPU arm's stacked copies), fp32 activations, cpu_infer matvec"
+        workload = "gemv_sweep(config 1): " + ", ".join(f"{r}x{c}" for r, c in SWEEP)
+    else:
+        steps = max(1, min(args.steps, 24))                     # bounded: a forward pass takes seconds on a CPU
+        value, threads, kind, sample = ref_decode_sample(steps, max(1, min(args.warmup, 3)))
+        ms_step, unit, metric = 1e3 / value, "tok/s", DECODE_METRIC
+        if steps != args.steps:
+            sample += f"; {steps} of the {args.steps} requested steps were run to keep the run within minutes"
+        workload = f"decode(config 2): {MODEL_PRESET} shape, batch 1"
     print(json.dumps({
-        "impl": "reference", "metric": "q4_0 GEMV HBM GB/s (6-shape sweep, algorithmic q4_0 weight bytes / time)",
-        "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
-        "ms_per_step": round(sum(ms) / len(ms), 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": metric, "value": round(value, 4), "unit": unit, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 (reference CPU path dequantizes q4_0 rows to fp32)", "data": "synthetic",
-        "config": {"workload": "gemv_sweep(config 1): " + ", ".join(f"{r}x{c}" for r, c in SWEEP)},
-        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": kind, "sample": sample},
-        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": workload},
+        "cpu_baseline": {"value": round(value, 4), "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -178,6 +259,37 @@ def build_stacks(ctx, torch, rank, world):
     return stacks
 
 
+def time_gemv_sweep(ctx, torch, stacks, steps, barrier):
+    """Returns (ms per step, [ms per launch per shape]) with CUDA events on the launching stream."""
+    for _ in range(3):
+        for s in stacks:
+            ctx.gemv_q4_q8(s["w"], s["xq"], s["xd"], s["y"])
+    barrier()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stacks) + 1)] for _ in range(steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(steps):
+        ev[k][0].record()
+        for i, s in enumerate(stacks):
+            ctx.gemv_q4_q8(s["w"], s["xq"], s["xd"], s["y"])
+            ev[k][i + 1].record()
+    e1.record()
+    barrier()
+    ctx.sync()
+    kern_ms = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(steps)) / steps for i in range(len(stacks))]
+    return e0.elapsed_time(e1) / steps, kern_ms
+
+
+def gemv_roofline(stacks, kern_ms, peak, peak_kind):
+    step_bytes = sum(s["bytes"] for s in stacks)
+    ach = step_bytes / (sum(kern_ms) * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+            "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": 1.06 * step_bytes / len(stacks),
+            "traffic_note": "dram read+write per launch = 1.06 x algorithmic bytes, from the ncu capture in profiles/gemv_q4_q8_kernel__gemv_sweep.md scaled by bytes",
+            "kernel": "gemv_q4_q8_kernel", "algorithmic_bytes_per_launch": step_bytes // len(stacks),
+            "per_shape_gbs": {f"{r}x{c}": round(s["bytes"] / (m * 1e-3) / 1e9, 1) for (r, c), s, m in zip(SWEEP, stacks, kern_ms)}}
+
+
 def run_ours(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -192,90 +304,133 @@ def run_ours(args, rank, world, local_rank):
     pkg = ge.load_package()
     ctx = pkg.Context(local_rank)
     ctx.use_torch_stream()
-    stacks = build_stacks(ctx, torch, rank, world)
-    step_bytes = sum(s["bytes"] for s in stacks)
-
-    def step():
-        for s in stacks:
-            ctx.gemv_q4_q8(s["w"], s["xq"], s["xd"], s["y"])
+    peak, peak_kind = measured_peaks()
+    warmup = max(3, args.warmup)
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    # --- timed region: K steps, CUDA events on the launching stream
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(stacks) + 1)] for _ in range(args.steps)]
-    barrier()
-    t_wall0 = time.perf_counter()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for k in range(args.steps):
-        ev[k][0].record()
-        for i, s in enumerate(stacks):
-            ctx.gemv_q4_q8(s["w"], s["xq"], s["xd"], s["y"])
-            ev[k][i + 1].record()
-    e1.record()
-    barrier()
-    ctx.sync()
-    wall_ms = (time.perf_counter() - t_wall0) * 1e3
-    total_ms = e0.elapsed_time(e1)
-    # per-kernel durations (one launch per stack) for the roofline of the dominant kernel
-    kern_ms = [sum(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps)) / args.steps for i in range(len(stacks))]
-    # --- end to end through the host-buffer entry point: H2D of x, D2H of y inside the timed region
-    e2e_steps = max(1, min(args.steps, 5))
-    youts = [np.empty((s["count"], s["rows"]), np.float32) for s in stacks]
-    for s, yo in zip(stacks, youts):
-        ctx.gemv_q4_f32_host(s["w"], s["x_host"], yo)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    def reduce_max_sum(vals_max, vals_sum):
+        if dist is None:
+            return vals_max, vals_sum
+        a = torch.tensor(vals_max, device="cuda", dtype=torch.float64); dist.all_reduce(a, op=dist.ReduceOp.MAX)
+        b = torch.tensor(vals_sum, device="cuda", dtype=torch.float64); dist.all_reduce(b, op=dist.ReduceOp.SUM)
+        return [float(v) for v in a], [float(v) for v in b]
+
+    if args.workload == "gemv":
+        stacks = build_stacks(ctx, torch, rank, world)
+        step_bytes = sum(s["bytes"] for s in stacks)
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        barrier()
+        ms_per_step, kern_ms = time_gemv_sweep(ctx, torch, stacks, args.steps, barrier)
+        e2e_steps = max(1, min(args.steps, 5))
+        youts = [np.empty((s["count"], s["rows"]), np.float32) for s in stacks]
         for s, yo in zip(stacks, youts):
             ctx.gemv_q4_f32_host(s["w"], s["x_host"], yo)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for s, yo in zip(stacks, youts):
+                ctx.gemv_q4_f32_host(s["w"], s["x_host"], yo)
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        clocks = sampler.stop() if sampler else None
+        (ms_per_step, e2e_ms), (all_bytes,) = reduce_max_sum([ms_per_step, e2e_ms], [float(step_bytes)])
+        if rank != 0:
+            return
+        cpu_v, cpu_threads, cpu_kind, _ = ref_matvec_sample(1.5)
+        out = {
+            "metric": GEMV_METRIC, "value": round(all_bytes / (ms_per_step * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int4 dot products (dp4a, int32) with fp16 block scales, fp64 accumulate rounded to fp32",
+            "data": "synthetic",
+            "config": {"workload": "gemv_sweep(config 1): " + ", ".join(f"{r}x{c}" for r, c in SWEEP),
+                       "stack_bytes_per_shape_per_gpu": STACK_BYTES, "l2": "inputs larger than L2 (each launch streams >= 512 MiB of distinct weights)",
+                       "sharding": "rows of every matrix split across ranks by 32-row groups, no collective"},
+            "roofline": gemv_roofline(stacks, kern_ms, peak, peak_kind),
+            "cpu_baseline": {"value": round(cpu_v, 3), "unit": "GB/s", "cores": cpu_threads, "kind": cpu_kind,
+                             "sample": "one matrix per sweep shape, ~1.5 s each, reference matvec (fp32 activations) on all host threads"},
+            "e2e": {"value": round(all_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+                    "h2d_bytes_per_step": int(sum(s["cols"] * 4 for s in stacks)),
+                    "d2h_bytes_per_step": int(sum(s["count"] * s["rows"] * 4 for s in stacks)),
+                    "api": "mi_gemv_q4_f32_host (host x in, host y out; weights resident)"},
+            "gpu_launches": args.steps * len(stacks), "clocks": clocks,
+        }
+        print(json.dumps(out))
+        return
+
+    # ---------------- decode workload
+    if rank == 0:
+        ensure_model()
+    barrier()
+    path = ensure_model()
+    model = pkg.Model(ctx, path, MAX_SEQ)
+    cfg = model.config
+    ids = prompt_ids(cfg.n_vocab)
+    K = args.steps
+    if PROMPT_LEN + warmup + K + 1 > MAX_SEQ:
+        raise SystemExit(f"--steps {K} does not fit the {MAX_SEQ}-position KV cache of the workload")
+    # untimed: prefill of the prompt, then W warm-up decode steps
+    pre, _ = model.decode(ids, PROMPT_LEN, 0)
+    warm, _ = model.decode([pre[-1]], warmup, PROMPT_LEN)
+    pos0 = PROMPT_LEN + warmup
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    # timed region: K steps inside one launch of the persistent kernel, device time from CUDA events on the launching stream
+    gen, ms = model.decode([warm[-1]], K, pos0, None, pkg.DECODE_PERSISTENT)
+    barrier()
+    # the same K steps as a kernel sequence (one launch per phase), for the record
+    _, ms_seq = model.decode([warm[-1]], min(K, 32), pos0, None, pkg.DECODE_PER_PHASE)
+    ms_seq = ms_seq / min(K, 32)
+    # end to end through the call a host program makes per token: host token in, host token out, every step
+    e2e_steps = min(K, 64)
+    tok = warm[-1]
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(e2e_steps):
+        out, _ = model.decode([tok], 1, pos0 + s, None, pkg.DECODE_PERSISTENT)
+        tok = out[0]
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
     clocks = sampler.stop() if sampler else None
-
-    if dist is not None:
-        t = torch.tensor([total_ms, e2e_ms, float(step_bytes)], device="cuda", dtype=torch.float64)
-        tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, all_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
-    else:
-        all_bytes = float(step_bytes)
+    # algorithmic bytes of the timed region: every step streams all q4_0 weights once, reads the fp16 K and V of
+    # every cached position (pos + 1 of them) and writes one position
+    kvb = cfg.kv_bytes_per_position
+    bytes_region = sum(cfg.q4_weight_bytes_per_token + kvb * (pos0 + s + 1) + kvb for s in range(K))
+    (ms, e2e_ms), (tok_s_sum,) = reduce_max_sum([ms, e2e_ms], [K / (ms * 1e-3)])
+    # the standalone GEMV kernel on the sweep shapes (the other half of the metric), a few steps
+    model.free()
+    stacks = build_stacks(ctx, torch, rank, world)
+    _, kern_ms = time_gemv_sweep(ctx, torch, stacks, 5, barrier)
     if rank != 0:
         return
-    ms_per_step = total_ms / args.steps
-    value = all_bytes / (ms_per_step * 1e-3) / 1e9
-    peak, peak_kind = measured_peaks()
-    # dominant kernel: the GEMV (the only kernel of this workload); achieved over all six launches of a step
-    ach = step_bytes / (sum(kern_ms) * 1e-3) / 1e9
-    cpu_v, cpu_threads, cpu_kind, _ = ref_matvec_sample(1.5)
+    value = world * K / (ms * 1e-3) if world > 1 else K / (ms * 1e-3)
+    ach = bytes_region / (ms * 1e-3) / 1e9
+    roof_tok_s = peak * 1e9 / (bytes_region / K)
+    cpu_v, cpu_threads, cpu_kind, cpu_desc = ref_decode_sample(6, 1)
     out = {
-        "metric": "q4_0 GEMV HBM GB/s (6-shape sweep, algorithmic q4_0 weight bytes / time)",
-        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x int4 dot products (dp4a, int32) with fp16 block scales, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": "gemv_sweep(config 1): " + ", ".join(f"{r}x{c}" for r, c in SWEEP),
-                   "stack_bytes_per_shape_per_gpu": STACK_BYTES, "l2": "inputs larger than L2 (each launch streams >= 512 MiB of distinct weights)",
-                   "sharding": "rows of every matrix split across ranks by 32-row groups, no collective"},
+        "metric": DECODE_METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": warmup,
+        "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "weak" if world > 1 else "strong", "vs_baseline": None,
+        "dtype": "int8 x int4 dot products (dp4a, int32) with fp16 block scales; sums carried in fp64, stored fp32; fp16 KV",
+        "data": "synthetic",
+        "config": {"workload": f"decode(config 2): Qwen2.5-{MODEL_PRESET} shape, L={cfg.n_layer} d={cfg.n_embd} ff={cfg.n_ff} H={cfg.n_head}/{cfg.n_head_kv} "
+                               f"V={cfg.n_vocab}, seeded N(0,0.02) weights quantized to q4_0, {PROMPT_LEN}-token seeded prompt, batch 1, positions {pos0}..{pos0 + K - 1}",
+                   "kv_cache_positions": MAX_SEQ, "engine": "persistent kernel (one cooperative launch for all timed steps)",
+                   "l2": "inputs larger than L2 (868 MB of weights streamed per step, marked evict-first)",
+                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas, one per GPU (tensor parallelism is not implemented yet)",
+                   "grid_ctas": cfg.grid_ctas},
         "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None,
-                     "kernel": "gemv_q4_q8_kernel", "per_shape_gbs": {f"{r}x{c}": round(s["bytes"] / (m * 1e-3) / 1e9, 1)
-                                                                      for (r, c), s, m in zip(SWEEP, stacks, kern_ms)}},
-        "cpu_baseline": {"value": round(cpu_v, 3), "unit": "GB/s", "cores": cpu_threads, "kind": cpu_kind,
-                         "sample": "one matrix per sweep shape, ~1.5 s each, reference matvec (fp32 activations) on all host threads"},
-        "e2e": {"value": round(all_bytes / (e2e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
-                "h2d_bytes_per_step": int(sum(s["cols"] * 4 for s in stacks)),
-                "d2h_bytes_per_step": int(sum(s["count"] * s["rows"] * 4 for s in stacks)),
-                "api": "mi_gemv_q4_f32_host (host x in, host y out; weights resident)"},
-        "gpu_launches": args.steps * len(stacks),
-        "clocks": clocks,
-        "wall_ms_timed_region": round(wall_ms, 2),
+                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None, "kernel": "decode_kernel",
+                     "algorithmic_bytes_per_launch": int(bytes_region), "bytes_per_token": int(bytes_region / K),
+                     "roofline_tok_s": round(roof_tok_s, 1), "frac_of_roofline_tok_s": round((K / (ms * 1e-3)) / roof_tok_s, 4)},
+        "gemv_roofline": gemv_roofline(stacks, kern_ms, peak, peak_kind),
+        "kernel_sequence_engine_tok_s": round(1e3 / ms_seq, 1),
+        "cpu_baseline": {"value": round(cpu_v, 4), "unit": "tok/s", "cores": cpu_threads, "kind": cpu_kind, "sample": cpu_desc},
+        "e2e": {"value": round(world * 1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "api": "mi_decode(n_steps=1) per token: host token id in, host token id out, one launch and one sync per step"},
+        "gpu_launches": 1, "clocks": clocks, "first_tokens": gen[:8],
     }
     print(json.dumps(out))
 
@@ -283,12 +438,15 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per shape per GPU (MiB); small values are for profiler captures")
-    ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the sweep (profiler captures)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
+    ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per GEMV shape per GPU (MiB); small values are for profiler captures")
+    ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the GEMV sweep (profiler captures)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 512 if args.workload == "decode" else 200
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
