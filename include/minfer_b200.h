@@ -130,6 +130,28 @@ MI_API int mi_gemv_q4_q8_ex(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_de
  * code as the GEMV.  For bit-exact parity checks. */
 MI_API int mi_block_isums_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, int32_t* isum_dev);
 
+/* Same product as mi_gemv_q4_q8, for callers that must not allocate device memory
+ * once they are running: a serving loop whose whole memory budget was handed to
+ * another allocator at start-up (a later cudaMalloc could fail, or stall every
+ * stream of the device while it runs), or a host that audits its plugins and
+ * forbids allocation after initialisation.  mi_gemv_q4_q8 grows a scratch buffer
+ * with cudaMalloc the first time a shape needs K-splitting; this entry point never
+ * does.  Its split-K scratch (partial sums and arrival counters) is a fixed array
+ * inside the library image: 65536 partial sums and 2048 counters, 528 KB that every
+ * GPU which loads the library holds until the process exits.  A call whose stack
+ * needs more (row groups x K-splits x 32 > 65536, or more than 2048 row groups
+ * over the whole stack when it is K-split) returns MI_ERR_LIMIT and does nothing.
+ * It calls no cudaMalloc, cudaFree or other allocating routine.
+ * The first call on a device looks the array's device address up (one symbol
+ * query, with that device current); make that first call before any stream
+ * capture begins.  All calls share the one array and it keeps whatever the last
+ * call left in it (the counters are cleared at the start of every call): two calls
+ * that overlap on the GPU - different streams, or different contexts on the same
+ * device - race on it and give wrong results; serialize them.
+ * This entry point has no counterpart in the reference. */
+MI_API int mi_gemv_q4_q8_noalloc(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
+                                 const float* bias_dev, float* y_dev);
+
 /* Host-buffer convenience: quantize x_host [cols] on the device, run the GEMV on
  * matrix stack w, and copy y back to y_host [count][rows].  Host-to-device and
  * device-to-host copies are inside the call; it returns when y_host is valid. */

@@ -53,6 +53,7 @@ SIGNATURES = {
     "mi_quant_q8": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
     "mi_gemv_q4_q8": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "mi_gemv_q4_q8_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32]),
+    "mi_gemv_q4_q8_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "mi_block_isums_q4_q8": (_i32, [_vp, _vp, _vp, _vp]),
     "mi_gemv_q4_f32_host": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "mi_model_load_gguf": (_i32, [_vp, C.c_char_p, _i32, C.POINTER(_vp)]),
@@ -165,6 +166,10 @@ class Context:
 
     def gemv_q4_q8(self, w, xq, xd, y, bias=None, ksplit=0, variant=0):
         self.check(self.lib.mi_gemv_q4_q8_ex(self.h, w.h, _ptr(xq), _ptr(xd), _ptr(bias), _ptr(y), ksplit, variant), "mi_gemv_q4_q8")
+
+    def gemv_q4_q8_noalloc(self, w, xq, xd, y, bias=None):
+        """The GEMV through the entry point that never allocates (fixed built-in scratch)."""
+        self.check(self.lib.mi_gemv_q4_q8_noalloc(self.h, w.h, _ptr(xq), _ptr(xd), _ptr(bias), _ptr(y)), "mi_gemv_q4_q8_noalloc")
 
     def block_isums(self, w, xq, isum):
         self.check(self.lib.mi_block_isums_q4_q8(self.h, w.h, _ptr(xq), _ptr(isum)), "mi_block_isums_q4_q8")

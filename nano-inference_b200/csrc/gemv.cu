@@ -39,8 +39,11 @@ gemv_q4_q8_kernel(const __grid_constant__ GemvShape sh, const __grid_constant__ 
 // variant -> {warps per CTA, ring stages per warp}; see launch_kb
 constexpr int kNumVariants = 8;
 
+// fixed: scratch supplied by the caller (with its capacity) instead of the context's growable buffers
+struct FixedScratch { double* part; unsigned* counters; size_t part_cap, counter_cap; };
+
 template <int KB, int NW, int S, bool DUMP>
-static int launch_one(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksplit) {
+static int launch_one(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksplit, const FixedScratch* fixed = nullptr) {
     using SM = GemvSmem<KB, NW, S>;
     const size_t smem = SM::bytes(w->nb);
     if (smem > (size_t)ctx->smem_optin)
@@ -66,7 +69,14 @@ static int launch_one(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksp
     if (ctas > ctx->sm_count) ctas = ctx->sm_count;
     GemvShape sh{w->dev, (long long)w->mat_stride, (int)w->count, w->groups, w->nt, ks, w->nb, (int)w->rows};
     GemvScratch sc{nullptr, nullptr};
-    if (ks > 1) {
+    if (ks > 1 && fixed) {
+        if ((size_t)base_units * ks * 32 > fixed->part_cap || (size_t)base_units > fixed->counter_cap)
+            return set_error(ctx, MI_ERR_LIMIT,
+                             "gemv (no-allocation entry point): %lld row groups x %d K-splits need %zu partial sums and %lld counters; "
+                             "the built-in scratch holds %zu and %zu", base_units, ks, (size_t)base_units * ks * 32, base_units,
+                             fixed->part_cap, fixed->counter_cap);
+        sc.part = fixed->part; sc.counters = fixed->counters;
+    } else if (ks > 1) {
         int st = ensure_scratch(ctx, (size_t)base_units * ks * 32, (size_t)base_units);
         if (st != MI_OK) return st;
         sc.part = ctx->part; sc.counters = ctx->counters;
@@ -103,9 +113,58 @@ static int launch_gemv(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ks
     }
 }
 
+// ---- scratch that needs no allocation ---------------------------------------------------
+// Split-K scratch of the allocation-free entry point: partial sums and arrival counters live
+// in the library image itself.  Every GPU that loads the library holds these 528 KB until the
+// process exits.  In host code these names are only stand-ins for the symbols; the device
+// addresses come from cudaGetSymbolAddress (see noalloc_scratch).
+constexpr size_t kNoAllocPartials = 65536;        // doubles: row groups x K-splits x 32 rows
+constexpr size_t kNoAllocCounters = 2048;         // one per row group of the stack
+static __device__ __align__(256) double g_noalloc_part[kNoAllocPartials];
+static __device__ __align__(256) unsigned g_noalloc_counters[kNoAllocCounters];
+
+// Device addresses of the two arrays on the context's device, looked up once per device with
+// that device current.  No allocation happens here or later.
+static int noalloc_scratch(mi_ctx* ctx, FixedScratch* out) {
+    static double* part_addr[16] = {nullptr};
+    static unsigned* counter_addr[16] = {nullptr};
+    if (ctx->device < 0 || ctx->device >= 16) return set_error(ctx, MI_ERR_UNSUPPORTED, "no-allocation gemv: device index %d beyond 15", ctx->device);
+    if (!part_addr[ctx->device]) {
+        MI_CUDA(ctx, cudaSetDevice(ctx->device));
+        double* p = nullptr; unsigned* c = nullptr;
+        MI_CUDA(ctx, cudaGetSymbolAddress((void**)&p, g_noalloc_part));
+        MI_CUDA(ctx, cudaGetSymbolAddress((void**)&c, g_noalloc_counters));
+        part_addr[ctx->device] = p; counter_addr[ctx->device] = c;
+    }
+    out->part = part_addr[ctx->device]; out->counters = counter_addr[ctx->device];
+    out->part_cap = kNoAllocPartials; out->counter_cap = kNoAllocCounters;
+    return MI_OK;
+}
+
 }  // namespace mi
 
 using namespace mi;
+
+extern "C" int mi_gemv_q4_q8_noalloc(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
+                                     const float* bias_dev, float* y_dev) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!w || !xq_dev || !xd_dev || !y_dev) return set_error(ctx, MI_ERR_INVALID, "gemv: null argument");
+    if (((uintptr_t)xq_dev & 15) != 0) return set_error(ctx, MI_ERR_INVALID, "gemv: xq_dev must be 16-byte aligned");
+    if (w->rows == 0 || w->count == 0) return MI_OK;
+    FixedScratch fx;
+    int st = noalloc_scratch(ctx, &fx);
+    if (st != MI_OK) return st;
+    // the counters must read zero when the kernel starts, whatever an earlier call left behind
+    MI_CUDA(ctx, cudaMemsetAsync(fx.counters, 0, kNoAllocCounters * sizeof(unsigned), ctx->stream));
+    GemvIO io{xq_dev, reinterpret_cast<const __half*>(xd_dev), bias_dev, y_dev, (long long)w->rows, (int)w->rows, nullptr, ctx->d_err};
+    switch (w->kb) {
+        case 8: return launch_one<8, 8, 3, false>(ctx, w, io, 0, &fx);
+        case 4: return launch_one<4, 8, 3, false>(ctx, w, io, 0, &fx);
+        case 2: return launch_one<2, 8, 3, false>(ctx, w, io, 0, &fx);
+        case 1: return launch_one<1, 8, 3, false>(ctx, w, io, 0, &fx);
+        default: return set_error(ctx, MI_ERR_INVALID, "gemv: bad tile depth %d", w->kb);
+    }
+}
 
 extern "C" int mi_gemv_q4_q8_ex(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
                                 const float* bias_dev, float* y_dev, int ksplit, int variant) {
