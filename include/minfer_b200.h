@@ -212,6 +212,38 @@ MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host
  * inspection.  For per-phase parity checks. */
 MI_API int mi_decode_phases(mi_ctx* ctx, mi_model* model, int32_t token, int pos, int phase_begin, int phase_end);
 
+/* ---- tensor parallelism (one process per GPU) --------------------------------- */
+
+/* The reference is single-GPU (README.md:54); this part has no counterpart in it.
+ * Every GEMV job of the decode step is sharded by rows: GPU `rank` of `world` owns a
+ * contiguous range of each matrix's 32-row groups (mi_tp_partition) and streams only
+ * those rows.  What a sharded phase produces lands in a buffer that all GPUs lay out
+ * identically, with the entries a GPU does not own left at zero; an all-reduce (sum)
+ * of that buffer between the phases - NCCL, issued by the host program - therefore
+ * reproduces, bit for bit, what one GPU computes (x + 0 is exact for every type).
+ * Attention is replicated.  Per token and layer: all-reduce after the QKV phase
+ * (MI_TP_QKV), the O phase (MI_TP_PART_O), the gate/up phase (MI_TP_ACT) and the down
+ * phase (MI_TP_PART_DOWN); after the lm_head each GPU holds the best logit of its rows
+ * (MI_TP_BEST: {float value, int32 token}); gather those and call mi_tp_pick. */
+enum { MI_TP_QKV = 0, MI_TP_PART_O = 1, MI_TP_ACT = 2, MI_TP_PART_DOWN = 3, MI_TP_BEST = 4 };
+
+/* Range [begin, end) of `groups` row groups owned by `rank`.  Pure arithmetic, no GPU needed. */
+MI_API void mi_tp_partition(int groups, int rank, int world, int* begin, int* end);
+/* mi_model_load_gguf for GPU `tp_rank` of `tp_world`. */
+MI_API int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq, int tp_rank, int tp_world, mi_model** out);
+/* Device address and byte size of an exchanged buffer (layer is ignored where it does not apply). */
+MI_API int mi_model_tp_region(const mi_model* model, int which, int layer, void** ptr, int64_t* bytes);
+/* Enqueue phases [phase_begin, phase_end) of the step at position pos, one launch per phase, WITHOUT
+ * waiting; the input token is the model's device-resident current token.  On a sharded model the
+ * buffer a phase writes is zeroed first.  The caller interleaves its all-reduces on the same stream. */
+MI_API int mi_decode_launch(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
+/* Set (asynchronously) / read back (synchronously) the model's current token. */
+MI_API int mi_model_set_token(mi_ctx* ctx, mi_model* model, int32_t token);
+MI_API int mi_model_get_token(mi_ctx* ctx, mi_model* model, int32_t* token, float* best_val);
+/* gathered_dev: [world] x {float, int32} as published under MI_TP_BEST by each GPU; makes the overall
+ * greedy token (largest value, lowest id on ties) the current token. */
+MI_API int mi_tp_pick(mi_ctx* ctx, mi_model* model, const void* gathered_dev, int world);
+
 #ifdef __cplusplus
 }
 #endif

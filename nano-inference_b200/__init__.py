@@ -62,7 +62,15 @@ SIGNATURES = {
     "mi_model_state_ptr": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
     "mi_decode": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, C.POINTER(C.c_float)]),
     "mi_decode_phases": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32]),
+    "mi_tp_partition": (None, [_i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_i32)]),
+    "mi_model_load_gguf_tp": (_i32, [_vp, C.c_char_p, _i32, _i32, _i32, C.POINTER(_vp)]),
+    "mi_model_tp_region": (_i32, [_vp, _i32, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
+    "mi_decode_launch": (_i32, [_vp, _vp, _i32, _i32, _i32]),
+    "mi_model_set_token": (_i32, [_vp, _vp, _i32]),
+    "mi_model_get_token": (_i32, [_vp, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
+    "mi_tp_pick": (_i32, [_vp, _vp, _vp, _i32]),
 }
+TP_QKV, TP_PART_O, TP_ACT, TP_PART_DOWN, TP_BEST = range(5)
 
 DECODE_PERSISTENT, DECODE_PER_PHASE = 0, 1
 STATE = {"h": 0, "q": 1, "att": 2, "kcache": 3, "vcache": 4, "act_q": 5, "act_d": 6, "profile": 7, "h_mid": 8}
@@ -205,10 +213,11 @@ class Weight:
 class Model:
     """A loaded GGUF model with its KV cache and decode state: wraps mi_model."""
 
-    def __init__(self, ctx, path, max_seq):
+    def __init__(self, ctx, path, max_seq, tp_rank=0, tp_world=1):
         self.ctx = ctx
+        self.tp_rank, self.tp_world = tp_rank, tp_world
         h = _vp()
-        ctx.check(ctx.lib.mi_model_load_gguf(ctx.h, str(path).encode(), max_seq, C.byref(h)), "mi_model_load_gguf")
+        ctx.check(ctx.lib.mi_model_load_gguf_tp(ctx.h, str(path).encode(), max_seq, tp_rank, tp_world, C.byref(h)), "mi_model_load_gguf_tp")
         self.h = h
         self.config = ModelConfig()
         ctx.check(ctx.lib.mi_model_info(h, C.byref(self.config)), "mi_model_info")
@@ -227,6 +236,27 @@ class Model:
         """The reference CLI's output: n_gen greedy ids, the first predicted after the last prompt token."""
         out, ms = self.decode(prompt, len(prompt) + n_gen - 1, 0, None, mode)
         return out[len(prompt) - 1:], ms
+
+    # ---- tensor parallelism: asynchronous launches + the exchanged buffers as torch tensors
+    def tp_region(self, which, layer=0):
+        """uint8 torch tensor aliasing one exchanged buffer (no copy)."""
+        p, n = _vp(), _i64()
+        self.ctx.check(self.ctx.lib.mi_model_tp_region(self.h, which, layer, C.byref(p), C.byref(n)), "mi_model_tp_region")
+        return _as_cuda_tensor(p.value, n.value)
+
+    def launch(self, pos, ph0, ph1):
+        self.ctx.check(self.ctx.lib.mi_decode_launch(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch")
+
+    def set_token(self, tok):
+        self.ctx.check(self.ctx.lib.mi_model_set_token(self.ctx.h, self.h, int(tok)), "mi_model_set_token")
+
+    def get_token(self):
+        t, v = C.c_int32(), C.c_float()
+        self.ctx.check(self.ctx.lib.mi_model_get_token(self.ctx.h, self.h, C.byref(t), C.byref(v)), "mi_model_get_token")
+        return t.value, v.value
+
+    def tp_pick(self, gathered, world):
+        self.ctx.check(self.ctx.lib.mi_tp_pick(self.ctx.h, self.h, _ptr(gathered), world), "mi_tp_pick")
 
     def run_phases(self, token, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_phases(self.ctx.h, self.h, token, pos, ph0, ph1), "mi_decode_phases")

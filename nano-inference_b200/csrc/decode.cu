@@ -17,6 +17,7 @@ struct mi_model {
     int L = 0, E = 0, FF = 0, NH = 0, NKV = 0, HD = 0, KVD = 0, V = 0, G = 0;
     float eps = 1e-6f, rope_base = 1e6f;
     int max_seq = 0, grid = 0, max_chunks = 0;
+    int tp_rank = 0, tp_world = 1;
     bool tied = false;
     int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)
     std::vector<void*> allocs;            // everything cudaMalloc'ed for this model
@@ -28,6 +29,9 @@ struct mi_model {
     size_t part_count = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* prof_buf = nullptr;
+    uint8_t* act_buf = nullptr;          // [act_q | act_d]
+    float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
+    int qkv_rows = 0;
 };
 
 namespace {
@@ -130,11 +134,22 @@ extern "C" int mi_model_free(mi_ctx* ctx, mi_model* m) {
     return MI_OK;
 }
 
+extern "C" void mi_tp_partition(int groups, int rank, int world, int* begin, int* end) {
+    if (world < 1) world = 1;
+    if (begin) *begin = (int)((long long)groups * rank / world);
+    if (end) *end = (int)((long long)groups * (rank + 1) / world);
+}
+
 extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi_model** out) {
+    return mi_model_load_gguf_tp(ctx, path, max_seq, 0, 1, out);
+}
+
+extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq, int tp_rank, int tp_world, mi_model** out) {
     if (!ctx) return MI_ERR_INVALID;
     if (!out || !path) return set_error(ctx, MI_ERR_INVALID, "model: null argument");
     *out = nullptr;
     if (max_seq <= 0) return set_error(ctx, MI_ERR_INVALID, "model: max_seq must be positive");
+    if (tp_world < 1 || tp_rank < 0 || tp_rank >= tp_world) return set_error(ctx, MI_ERR_INVALID, "model: bad tensor-parallel rank %d of %d", tp_rank, tp_world);
     MI_CUDA(ctx, cudaSetDevice(ctx->device));
     mib200::GgufFile g;
     std::string err = g.open(path);
@@ -145,7 +160,7 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
     mi_model* m = new (std::nothrow) mi_model();
     if (!m) return set_error(ctx, MI_ERR_NOMEM, "model: host allocation failed");
     struct Guard { mi_ctx* c; mi_model* m; bool keep = false; ~Guard() { if (!keep) mi_model_free(c, m); } } guard{ctx, m};
-    m->device = ctx->device;
+    m->device = ctx->device; m->tp_rank = tp_rank; m->tp_world = tp_world;
     // hyper-parameters: the keys the reference drivers read (src/cpu_infer.cpp:71-79)
     m->L = (int)g.num("qwen2.block_count", 0);
     m->E = (int)g.num("qwen2.embedding_length", 0);
@@ -222,14 +237,22 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
     // ---- layers
     std::vector<LayerPtrs> lp(L);
     const int qkv_rows = NQ + 2 * KVD, W = m->grid * DNW;
+    m->qkv_rows = qkv_rows;
     int rot = 0, wrot = 0; size_t part_off = 0;
     auto add_job = [&](const uint8_t* base, int groups, int cols, int nacc, int kind, int layer) {
-        Job jb{}; jb.base = base; jb.groups = groups; jb.nb = cols / 32; jb.kb = choose_kb(jb.nb); jb.nt = jb.nb / jb.kb;
+        Job jb{}; jb.nb = cols / 32; jb.kb = choose_kb(jb.nb); jb.nt = jb.nb / jb.kb;
         jb.nacc = nacc; jb.kind = kind; jb.layer = layer;
+        // tensor parallelism: this GPU owns a contiguous range of the job's unit groups (rows); every GPU holds the
+        // whole matrix but streams only its rows.  The K-split is planned from the largest share so that all GPUs
+        // lay the partial sums out identically.
+        int g0, g1;
+        mi_tp_partition(groups, tp_rank, tp_world, &g0, &g1);
+        jb.g_off = g0; jb.groups = g1 - g0;
+        jb.base = base + (size_t)g0 * nacc * jb.nt * tile_bytes(jb.kb);
         const char* force = getenv("MINFER_KS");
-        jb.ks = plan_ks(kind, groups, jb.nt, m->grid);
+        jb.ks = plan_ks(kind, (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
         if (force && (kind == JOB_O || kind == JOB_DOWN)) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
-        jb.n_units = groups * jb.ks;
+        jb.n_units = jb.groups * jb.ks;
         jb.part_off = (int)part_off;
         if (kind == JOB_O || kind == JOB_DOWN) part_off += (size_t)groups * jb.ks * 32;
         if (kind == JOB_LM) { jb.rot = 0; jb.wrot = 0; }
@@ -346,15 +369,17 @@ extern "C" int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi
 
     // ---- state
     m->part_count = part_off;
-    if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.q, NQ)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
+    if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.qkv_out, (size_t)(qkv_rows + 31) / 32 * 32)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
         (st = dev_alloc(ctx, m, &P.att_q, NQ)) || (st = dev_alloc(ctx, m, &P.att_d, NQ / 32)) ||
-        (st = dev_alloc(ctx, m, &P.act_q, FF)) || (st = dev_alloc(ctx, m, &P.act_d, FF / 32)) ||
+        (st = dev_alloc(ctx, m, &m->act_buf, (size_t)FF + (size_t)FF / 32 * 2)) ||
         (st = dev_alloc(ctx, m, &P.kc, (size_t)L * max_seq * KVD)) || (st = dev_alloc(ctx, m, &P.vc, (size_t)L * max_seq * KVD)) ||
         (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NKV)) ||
         (st = dev_alloc(ctx, m, &P.part, part_off)) ||
         (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
-        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &P.cur_token, 1)) || (st = dev_alloc(ctx, m, &P.bar, 64)))
+        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) || (st = dev_alloc(ctx, m, &P.bar, 64)))
         return st;
+    P.act_q = reinterpret_cast<int8_t*>(m->act_buf); P.act_d = reinterpret_cast<__half*>(m->act_buf + FF);   // one run: exchanged as one piece
+    P.best_val = m->best_buf; P.cur_token = reinterpret_cast<int*>(m->best_buf + 1);                        // {value, token}: exchanged as one piece
     P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
     m->prof_buf = P.prof;
     if (!getenv("MINFER_PROFILE")) P.prof = nullptr;         // the buffer exists either way; kernels only write it when asked
@@ -385,7 +410,7 @@ extern "C" int mi_model_state_ptr(const mi_model* m, int which, void** ptr, int6
     switch (which) {
         case MI_STATE_H: *ptr = P.h_in; if (bytes) *bytes = (int64_t)m->E * 4; break;
         case MI_STATE_H_MID: *ptr = P.h_mid; if (bytes) *bytes = (int64_t)m->E * 4; break;
-        case MI_STATE_Q: *ptr = P.q; if (bytes) *bytes = (int64_t)NQ * 4; break;
+        case MI_STATE_Q: *ptr = P.qkv_out; if (bytes) *bytes = (int64_t)(NQ + 2 * m->KVD) * 4; break;
         case MI_STATE_ATT: *ptr = P.att; if (bytes) *bytes = (int64_t)NQ * 4; break;
         case MI_STATE_KCACHE: *ptr = P.kc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
         case MI_STATE_VCACHE: *ptr = P.vc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
@@ -460,4 +485,95 @@ extern "C" int mi_decode_phases(mi_ctx* ctx, mi_model* m, int32_t token, int pos
     if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end) return set_error(ctx, MI_ERR_INVALID, "decode: bad phase range");
     int32_t out;
     return decode_impl(ctx, m, &token, 1, 1, pos, &out, nullptr, MI_DECODE_PER_PHASE, phase_begin, phase_end, nullptr);
+}
+
+// ---- tensor parallelism: asynchronous phase launches and the buffers the GPUs exchange ------------------
+
+namespace {
+__global__ void set_token_kernel(int* dst, int tok) { *dst = tok; }
+// gathered: [world] x {float best value, int token}; the largest value wins, the lowest token id on ties
+// (the rule of src/cpu_infer.cpp:153-154 applied across the GPUs' row ranges)
+__global__ void tp_pick_kernel(const float* gathered, int world, float* best_val, int* cur_token) {
+    float b = gathered[0]; int t = reinterpret_cast<const int*>(gathered)[1];
+    for (int r = 1; r < world; r++) {
+        const float v = gathered[2 * r]; const int ix = reinterpret_cast<const int*>(gathered)[2 * r + 1];
+        if (v > b || (v == b && ix < t)) { b = v; t = ix; }
+    }
+    *best_val = b; *cur_token = t;
+}
+}  // namespace
+
+extern "C" int mi_model_tp_region(const mi_model* m, int which, int layer, void** ptr, int64_t* bytes) {
+    if (!m || !ptr || !bytes) return MI_ERR_INVALID;
+    const DecodeParams& P = m->P;
+    switch (which) {
+        case MI_TP_QKV: *ptr = P.qkv_out; *bytes = (int64_t)(m->qkv_rows + 31) / 32 * 32 * 4; return MI_OK;
+        case MI_TP_ACT: *ptr = m->act_buf; *bytes = (int64_t)m->FF + (int64_t)m->FF / 32 * 2; return MI_OK;
+        case MI_TP_BEST: *ptr = m->best_buf; *bytes = 8; return MI_OK;
+        case MI_TP_PART_O: case MI_TP_PART_DOWN: {
+            if (layer < 0 || layer >= m->L) return MI_ERR_INVALID;
+            const Job& jb = m->jobs[4 * layer + (which == MI_TP_PART_O ? 1 : 3)];
+            const int total_groups = (m->E + 31) / 32;
+            *ptr = P.part + jb.part_off; *bytes = (int64_t)total_groups * jb.ks * 32 * 8; return MI_OK;
+        }
+        default: return MI_ERR_INVALID;
+    }
+}
+
+extern "C" int mi_model_set_token(mi_ctx* ctx, mi_model* m, int32_t token) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "set_token: null model");
+    if (token < 0 || token >= m->V) return set_error(ctx, MI_ERR_INVALID, "set_token: token id %d out of range", token);
+    set_token_kernel<<<1, 1, 0, ctx->stream>>>(m->P.cur_token, token);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
+extern "C" int mi_model_get_token(mi_ctx* ctx, mi_model* m, int32_t* token, float* best_val) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "get_token: null model");
+    float h[2];
+    MI_CUDA(ctx, cudaMemcpyAsync(h, m->best_buf, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    int st = mi_ctx_sync(ctx);
+    if (st != MI_OK) return st;
+    if (best_val) *best_val = h[0];
+    if (token) memcpy(token, &h[1], 4);
+    return MI_OK;
+}
+
+extern "C" int mi_tp_pick(mi_ctx* ctx, mi_model* m, const void* gathered_dev, int world) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !gathered_dev || world < 1) return set_error(ctx, MI_ERR_INVALID, "tp_pick: bad argument");
+    tp_pick_kernel<<<1, 1, 0, ctx->stream>>>(reinterpret_cast<const float*>(gathered_dev), world, m->best_buf, m->P.cur_token);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
+extern "C" int mi_decode_launch(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int phase_end) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "decode_launch: null model");
+    const int nph = 5 * m->L + 1;
+    if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end) return set_error(ctx, MI_ERR_INVALID, "decode_launch: bad phase range");
+    if (pos < 0 || pos >= m->max_seq) return set_error(ctx, MI_ERR_LIMIT, "decode_launch: position %d outside the KV cache of %d", pos, m->max_seq);
+    int st;
+    if (m->out_capacity < 1) {
+        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, 16))) return st;
+        m->out_capacity = 16;
+    }
+    DecodeParams P = m->P;
+    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = pos; P.logits = nullptr; P.logits_stride = m->V;
+    for (int ph = phase_begin; ph < phase_end; ph++) {
+        if (m->tp_world > 1 && ph < nph - 1) {
+            // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce
+            const int l = ph / 5, k = ph % 5;
+            void* p = nullptr; int64_t nb = 0;
+            if (k == 0) mi_model_tp_region(m, MI_TP_QKV, l, &p, &nb);
+            else if (k == 2) mi_model_tp_region(m, MI_TP_PART_O, l, &p, &nb);
+            else if (k == 3) mi_model_tp_region(m, MI_TP_ACT, l, &p, &nb);
+            else if (k == 4) mi_model_tp_region(m, MI_TP_PART_DOWN, l, &p, &nb);
+            if (p) MI_CUDA(ctx, cudaMemsetAsync(p, 0, (size_t)nb, ctx->stream));
+        }
+        if ((st = dispatch_launch(ctx, m, P, 0, 1, ph, ph + 1, false))) return st;
+    }
+    return MI_OK;
 }

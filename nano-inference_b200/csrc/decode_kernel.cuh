@@ -60,8 +60,10 @@ struct Job {
     int n_units;           // groups * ks
     int rot;               // CTA (per-layer jobs) or warp slot (lm_head) that gets unit 0
     int wrot;              // warp that gets tile 0 of a CTA unit
-    int part_off;          // offset (in doubles) of this job's cross-CTA partials: [groups][ks][32]
+    int part_off;          // offset (in doubles) of this job's cross-CTA partials: [all groups][ks][32]
     int layer;
+    int g_off;             // first unit group this GPU owns (tensor parallelism; base points at it, groups counts the owned ones)
+    int pad_;
 };
 
 struct LayerPtrs { const float* attn_norm; const float* ffn_norm; const float* bqkv; };
@@ -81,13 +83,15 @@ struct DecodeParams {
     // state (global, written and read across CTAs: always accessed through L2)
     float* h_in;                     // residual stream at the input of the current layer
     float* h_mid;                    // residual stream after the attention block
-    float* q; float* att;
+    float* qkv_out;                  // [q | k | v] of the current token after bias and RoPE, packed (pair-adjacent) row order
+    float* att;
     int8_t* att_q; __half* att_d;    // q8_0 of the merged attention output
     int8_t* act_q; __half* act_d;    // q8_0 of SwiGLU(gate, up)
     __half* kc; __half* vc; int max_seq;       // [L][max_seq][KVD]
     double* attn_part; unsigned* attn_cnt; int max_chunks;  // [NH][max_chunks][HD+2], [NKV]
     double* part;                              // cross-CTA partial sums of the O / down projections
     float* cand_val; int* cand_idx; unsigned* cand_cnt;     // per-CTA argmax candidates
+    float* best_val;                 // value of this GPU's best logit (tensor parallelism: compared across GPUs)
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
     float* logits; long long logits_stride;    // optional [n_steps][stride]
     int pos0;
@@ -274,8 +278,8 @@ __device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& 
             double v0 = fb[lane], v1 = fb[32 + lane];
             #pragma unroll
             for (int w = 1; w < DNW; w++) { v0 = __dadd_rn(v0, fb[(w * 2) * 32 + lane]); v1 = __dadd_rn(v1, fb[(w * 2 + 1) * 32 + lane]); }
-            if (jb.ks == 1) epi(s.g, lane, __double2float_rn(v0), __double2float_rn(v1));
-            else __stcg(P.part + jb.part_off + ((size_t)s.g * jb.ks + s.sp) * 32 + lane, v0);
+            if (jb.ks == 1) epi(s.g + jb.g_off, lane, __double2float_rn(v0), __double2float_rn(v1));
+            else __stcg(P.part + jb.part_off + ((size_t)(s.g + jb.g_off) * jb.ks + s.sp) * 32 + lane, v0);
         }
         prof_mark(P, tp, 19);
     }
@@ -290,7 +294,7 @@ __device__ __forceinline__ bool run_warp_job(WarpStream& ws, int j, int lane, co
     for (int u = ws.first_warp_unit(jb); u < jb.n_units && ok; u += ws.W) {
         double acc = 0.0;
         for (int t = 0; t < jb.nt; t++) acc = tile_consume(ws, lane, jb.kb, t, xq_s, xs_s, acc, ok);
-        if (ok) epi(u, lane, __double2float_rn(acc));
+        if (ok) epi(u + jb.g_off, lane, __double2float_rn(acc));
     }
     return ok;
 }
@@ -464,9 +468,18 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     double* wts = scr + DNW * G * SW;                                       // [warp][32][G]
     constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2;                   // lanes per position in pass 1, dims per lane, padded stride
     double* qs = wts + DNW * 32 * G;                                        // [G][LPP][QSTR]: 16-byte skew per lane, conflict-free
+    // q of this kv head's G query heads, from the packed QKV vector: dim d of a head sits at 2d (d < HD/2) or 2(d-HD/2)+1
     for (int i = tid; i < G * HD; i += DNT) {
-        const int j = i / HD, d = i % HD;
-        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.q + (size_t)kvh * G * HD + i);
+        const int j = i / HD, d = i % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(kvh * G + j) * HD + pk);
+    }
+    if (ch == nch - 1) {                                                    // this CTA's range ends at the new position: store its K and V (fp16)
+        const int nq = P.NH * HD;
+        for (int d = tid; d < HD; d += DNT) {
+            const int pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+            P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + (size_t)kvh * HD + pk));
+            P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + P.KVD + (size_t)kvh * HD + d));
+        }
     }
     __syncthreads();
     prof_mark(P, tp, 14);
@@ -753,23 +766,18 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 prof_mark(P, tp, 0);
                 const float* bias = sm.lp[l].bqkv;
                 const int nq = P.NH * HD;
-                __half* kdst = P.kc + ((size_t)l * P.max_seq + pos) * P.KVD;
-                __half* vdst = P.vc + ((size_t)l * P.max_seq + pos) * P.KVD;
                 ok = run_cta_job(ws, P, sm, 4 * l + 0, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
                     const int p = g * 32 + ln;
                     const float v = __fadd_rn(v0, __ldg(bias + p));
                     const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+                    float out = v;
                     if (p < nq + P.KVD) {                                  // q or k: rotate the (even, odd) lane pair
-                        const int base = p < nq ? p : p - nq, head = base / HD, within = base % HD, i = within >> 1;
-                        const double c = sm.cs[i], s = sm.cs[HD / 2 + i];
-                        float out; int orig;                               // products are exact in double: one rounding each
-                        if ((within & 1) == 0) { out = __double2float_rn(__dsub_rn(__dmul_rn((double)v, c), __dmul_rn((double)partner, s))); orig = head * HD + i; }
-                        else { out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c))); orig = head * HD + i + HD / 2; }
-                        if (p < nq) __stcg(P.q + orig, out);
-                        else kdst[orig] = __float2half_rn(out);
-                    } else if (p < nq + 2 * P.KVD) {
-                        vdst[p - nq - P.KVD] = __float2half_rn(v);
+                        const int within = (p < nq ? p : p - nq) % HD, i = within >> 1;
+                        const double c = sm.cs[i], s = sm.cs[HD / 2 + i];    // products are exact in double: one rounding each
+                        if ((within & 1) == 0) out = __double2float_rn(__dsub_rn(__dmul_rn((double)v, c), __dmul_rn((double)partner, s)));
+                        else out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c)));
                     }
+                    if (p < nq + 2 * P.KVD) __stcg(P.qkv_out + p, out);
                 });
             } else if (k == 1) {
                 attention_phase<HD, G>(P, l, pos, sm.stage, tp);
@@ -835,6 +843,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                         }
                         *P.cand_cnt = 0;
                         __stcg(P.cur_token, bi);
+                        __stcg(P.best_val, b);
                         P.out_tokens[step] = bi;
                     }
                 }

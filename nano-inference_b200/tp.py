@@ -1,0 +1,64 @@
+"""Tensor-parallel decode, one process per GPU: the host side of the exchange.
+
+Each rank owns a contiguous range of every matrix's 32-row groups and runs the
+decode phases through the C ABI (mi_decode_launch, asynchronous); between phases it
+all-reduces the buffer the phase wrote (NCCL through torch.distributed, on the same
+stream).  Entries a rank does not own are zero before the reduction, so the sum
+reproduces the single-GPU values bit for bit - the buffers are reduced as raw bytes,
+which is valid for every element type because x + 0 never carries.
+
+The reference is single-GPU; this module has no counterpart in it.
+"""
+from __future__ import annotations
+
+
+def partition(groups, rank, world):
+    """Row-group range [begin, end) of `rank`; the same arithmetic as mi_tp_partition."""
+    return groups * rank // world, groups * (rank + 1) // world
+
+
+class TPDecoder:
+    """Drives one rank of a tensor-parallel model.  `dist` is torch.distributed with an
+    initialised process group (nccl on GPUs); world == 1 needs none."""
+
+    def __init__(self, pkg, model, dist=None, group=None):
+        import torch
+        self.pkg, self.model, self.dist, self.group = pkg, model, dist, group
+        self.world = model.tp_world
+        self.L = model.config.n_layer
+        self.torch = torch
+        if self.world > 1:
+            self.r_qkv = model.tp_region(pkg.TP_QKV)
+            self.r_act = model.tp_region(pkg.TP_ACT)
+            self.r_o = [model.tp_region(pkg.TP_PART_O, l) for l in range(self.L)]
+            self.r_down = [model.tp_region(pkg.TP_PART_DOWN, l) for l in range(self.L)]
+            self.r_best = model.tp_region(pkg.TP_BEST)
+            self.gathered = torch.zeros(8 * self.world, dtype=torch.uint8, device="cuda")
+
+    def _allreduce(self, t):
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
+
+    def step(self, pos):
+        """One decode step at position pos from the model's current token; leaves the next token current."""
+        m, L = self.model, self.L
+        if self.world == 1:
+            m.launch(pos, 0, 5 * L + 1)
+            return
+        for l in range(L):
+            m.launch(pos, 5 * l, 5 * l + 1); self._allreduce(self.r_qkv)
+            m.launch(pos, 5 * l + 1, 5 * l + 3); self._allreduce(self.r_o[l])
+            m.launch(pos, 5 * l + 3, 5 * l + 4); self._allreduce(self.r_act)
+            m.launch(pos, 5 * l + 4, 5 * l + 5); self._allreduce(self.r_down[l])
+        m.launch(pos, 5 * L, 5 * L + 1)
+        self.dist.all_gather_into_tensor(self.gathered, self.r_best, group=self.group)
+        m.tp_pick(self.gathered, self.world)
+
+    def decode(self, in_tokens, n_steps, pos0=0):
+        """Like Model.decode: forced tokens first, then greedy; returns the greedy token after every step."""
+        out = []
+        for s in range(n_steps):
+            if s < len(in_tokens):
+                self.model.set_token(in_tokens[s])
+            self.step(pos0 + s)
+            out.append(self.model.get_token()[0])
+        return out
