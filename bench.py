@@ -366,71 +366,107 @@ def run_ours(args, rank, world, local_rank):
         ensure_model()
     barrier()
     path = ensure_model()
-    model = pkg.Model(ctx, path, MAX_SEQ)
-    cfg = model.config
-    ids = prompt_ids(cfg.n_vocab)
     K = args.steps
     if PROMPT_LEN + warmup + K + 1 > MAX_SEQ:
         raise SystemExit(f"--steps {K} does not fit the {MAX_SEQ}-position KV cache of the workload")
-    # untimed: prefill of the prompt, then W warm-up decode steps
-    pre, _ = model.decode(ids, PROMPT_LEN, 0)
-    warm, _ = model.decode([pre[-1]], warmup, PROMPT_LEN)
+    model = pkg.Model(ctx, path, MAX_SEQ, tp_rank=rank, tp_world=world)
+    cfg = model.config
+    ids = prompt_ids(cfg.n_vocab)
     pos0 = PROMPT_LEN + warmup
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    barrier()
-    # timed region: K steps inside one launch of the persistent kernel, device time from CUDA events on the launching stream
-    gen, ms = model.decode([warm[-1]], K, pos0, None, pkg.DECODE_PERSISTENT)
-    barrier()
-    # the same K steps as a kernel sequence (one launch per phase), for the record
-    _, ms_seq = model.decode([warm[-1]], min(K, 32), pos0, None, pkg.DECODE_PER_PHASE)
-    ms_seq = ms_seq / min(K, 32)
-    # end to end through the call a host program makes per token: host token in, host token out, every step
-    e2e_steps = min(K, 64)
-    tok = warm[-1]
-    barrier()
-    t0 = time.perf_counter()
-    for s in range(e2e_steps):
-        out, _ = model.decode([tok], 1, pos0 + s, None, pkg.DECODE_PERSISTENT)
-        tok = out[0]
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    clocks = sampler.stop() if sampler else None
-    # algorithmic bytes of the timed region: every step streams all q4_0 weights once, reads the fp16 K and V of
-    # every cached position (pos + 1 of them) and writes one position
     kvb = cfg.kv_bytes_per_position
     bytes_region = sum(cfg.q4_weight_bytes_per_token + kvb * (pos0 + s + 1) + kvb for s in range(K))
-    (ms, e2e_ms), (tok_s_sum,) = reduce_max_sum([ms, e2e_ms], [K / (ms * 1e-3)])
-    # the standalone GEMV kernel on the sweep shapes (the other half of the metric), a few steps
+    ms_seq = None
+    if world == 1:
+        # untimed: prefill of the prompt, then W warm-up decode steps
+        pre, _ = model.decode(ids, PROMPT_LEN, 0)
+        warm, _ = model.decode([pre[-1]], warmup, PROMPT_LEN)
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        barrier()
+        # timed region: K steps inside one launch of the persistent kernel, device time from CUDA events on the launching stream
+        gen, ms = model.decode([warm[-1]], K, pos0, None, pkg.DECODE_PERSISTENT)
+        barrier()
+        # the same steps as a kernel sequence (one launch per phase), for the record
+        _, ms_seq = model.decode([warm[-1]], min(K, 32), pos0, None, pkg.DECODE_PER_PHASE)
+        ms_seq = ms_seq / min(K, 32)
+        # end to end through the call a host program makes per token: host token in, host token out, every step
+        e2e_steps = min(K, 64)
+        tok = warm[-1]
+        barrier()
+        t0 = time.perf_counter()
+        for s in range(e2e_steps):
+            out, _ = model.decode([tok], 1, pos0 + s, None, pkg.DECODE_PERSISTENT)
+            tok = out[0]
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        launches = 1
+        engine = "persistent kernel (one cooperative launch for all timed steps)"
+        parallelism = "single GPU"
+    else:
+        # tensor parallel: every GEMV job row-sharded over the ranks, NCCL all-reduce of the (zero-padded) phase
+        # outputs after the QKV, O, gate/up and down phases of every layer, attention replicated
+        tpmod = ge.load_submodule("tp")
+        dec = tpmod.TPDecoder(pkg, model, dist)
+        warm = dec.decode(ids, PROMPT_LEN + warmup)            # untimed: prompt, then W greedy steps
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(K):
+            dec.step(pos0 + s)
+        e1.record()
+        barrier()
+        ctx.sync()
+        ms = e0.elapsed_time(e1)
+        gen = [model.get_token()[0]]
+        e2e_steps = min(K, 32)
+        barrier()
+        t0 = time.perf_counter()
+        for s in range(e2e_steps):                              # host reads the token back after every step
+            dec.step(pos0 + K + s)
+            model.get_token()
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        L = cfg.n_layer
+        launches = K * (5 * L + 1 + 1)
+        engine = f"kernel sequence, one launch per phase; {4 * L + 1} NCCL collectives per token issued by the host"
+        parallelism = f"tp{world}: rows of every matrix sharded over {world} GPUs, attention replicated"
+    clocks = sampler.stop() if sampler else None
+    (ms, e2e_ms), _ = reduce_max_sum([ms, e2e_ms], [0.0])
     model.free()
+    # the standalone GEMV kernel on the sweep shapes (the other half of the metric), a few steps
     stacks = build_stacks(ctx, torch, rank, world)
     _, kern_ms = time_gemv_sweep(ctx, torch, stacks, 5, barrier)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
-    value = world * K / (ms * 1e-3) if world > 1 else K / (ms * 1e-3)
+    value = K / (ms * 1e-3)
     ach = bytes_region / (ms * 1e-3) / 1e9
-    roof_tok_s = peak * 1e9 / (bytes_region / K)
+    roof_tok_s = world * peak * 1e9 / (bytes_region / K)
     cpu_v, cpu_threads, cpu_kind, cpu_desc = ref_decode_sample(6, 1)
     out = {
         "metric": DECODE_METRIC, "value": round(value, 1), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": warmup,
-        "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "weak" if world > 1 else "strong", "vs_baseline": None,
+        "ms_per_step": round(ms / K, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8 x int4 dot products (dp4a, int32) with fp16 block scales; sums carried in fp64, stored fp32; fp16 KV",
         "data": "synthetic",
         "config": {"workload": f"decode(config 2): Qwen2.5-{MODEL_PRESET} shape, L={cfg.n_layer} d={cfg.n_embd} ff={cfg.n_ff} H={cfg.n_head}/{cfg.n_head_kv} "
                                f"V={cfg.n_vocab}, seeded N(0,0.02) weights quantized to q4_0, {PROMPT_LEN}-token seeded prompt, batch 1, positions {pos0}..{pos0 + K - 1}",
-                   "kv_cache_positions": MAX_SEQ, "engine": "persistent kernel (one cooperative launch for all timed steps)",
+                   "kv_cache_positions": MAX_SEQ, "engine": engine,
                    "l2": "inputs larger than L2 (868 MB of weights streamed per step, marked evict-first)",
-                   "parallelism": "single GPU" if world == 1 else f"{world} independent replicas, one per GPU (tensor parallelism is not implemented yet)",
+                   "parallelism": parallelism,
                    "grid_ctas": cfg.grid_ctas},
-        "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
-                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None, "kernel": "decode_kernel",
+        "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak * world, "unit": "GB/s", "frac": round(ach / (peak * world), 4),
+                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind}) x {world} GPU(s)", "traffic": None, "kernel": "decode_kernel",
                      "algorithmic_bytes_per_launch": int(bytes_region), "bytes_per_token": int(bytes_region / K),
                      "roofline_tok_s": round(roof_tok_s, 1), "frac_of_roofline_tok_s": round((K / (ms * 1e-3)) / roof_tok_s, 4)},
         "gemv_roofline": gemv_roofline(stacks, kern_ms, peak, peak_kind),
-        "kernel_sequence_engine_tok_s": round(1e3 / ms_seq, 1),
+        "kernel_sequence_engine_tok_s": round(1e3 / ms_seq, 1) if ms_seq else None,
         "cpu_baseline": {"value": round(cpu_v, 4), "unit": "tok/s", "cores": cpu_threads, "kind": cpu_kind, "sample": cpu_desc},
-        "e2e": {"value": round(world * 1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
-                "api": "mi_decode(n_steps=1) per token: host token id in, host token id out, one launch and one sync per step"},
-        "gpu_launches": 1, "clocks": clocks, "first_tokens": gen[:8],
+        "e2e": {"value": round(1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 if world == 1 else 0, "d2h_bytes_per_step": 4 if world == 1 else 8,
+                "api": "mi_decode(n_steps=1) per token: host token id in, host token id out, one launch and one sync per step" if world == 1
+                       else "TPDecoder.step + mi_model_get_token per token: the greedy token is read back to the host after every step"},
+        "gpu_launches": launches, "clocks": clocks, "first_tokens": gen[:8],
     }
     print(json.dumps(out))
 
@@ -447,6 +483,9 @@ def main():
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 512 if args.workload == "decode" else 200
+    # torch.distributed.run pins OMP_NUM_THREADS to 1; the CPU baseline on rank 0 is meant to use every host thread
+    if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
