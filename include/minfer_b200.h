@@ -152,6 +152,20 @@ MI_API int mi_block_isums_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* x
 MI_API int mi_gemv_q4_q8_noalloc(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev,
                                  const float* bias_dev, float* y_dev);
 
+/* ---- q4_0 x q8_0 GEMM for multi-token steps ---------------------------------- */
+
+/* Y[m][r] = the GEMV sum of row r against token vector m, for M = 1..16 token vectors in
+ * one pass over the weights (speculative verify, chunked prefill, small batches).  The
+ * integer block dot products run on the tensor cores (tcgen05.mma.kind::i8, one K=32 MMA
+ * per q4_0 block, int32 accumulators in tensor memory), the per-block fp16 scaling on the
+ * CUDA cores with the GEMV's own expression, so Y[m] carries exactly the bits
+ * mi_gemv_q4_q8 gives for xq[m] alone, whatever M is.  xq_dev [M][cols] int8, xd_dev
+ * [M][cols/32] fp16 bits, y_dev [M][rows] fp32; w must be a single matrix (count == 1).
+ * Replaces gemv_dp4a_batch<T> (src/cuda_infer.cu:183-222, T <= 8) and the mma.sync path
+ * tile_dot (src/mega.cu:197-244). */
+MI_API int mi_gemm_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* xq_dev, const uint16_t* xd_dev, int M,
+                         const float* bias_dev, float* y_dev);
+
 /* Host-buffer convenience: quantize x_host [cols] on the device, run the GEMV on
  * matrix stack w, and copy y back to y_host [count][rows].  Host-to-device and
  * device-to-host copies are inside the call; it returns when y_host is valid. */

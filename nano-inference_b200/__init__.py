@@ -54,6 +54,7 @@ SIGNATURES = {
     "mi_gemv_q4_q8": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "mi_gemv_q4_q8_ex": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32]),
     "mi_gemv_q4_q8_noalloc": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    "mi_gemm_q4_q8": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _vp]),
     "mi_block_isums_q4_q8": (_i32, [_vp, _vp, _vp, _vp]),
     "mi_gemv_q4_f32_host": (_i32, [_vp, _vp, _vp, _vp, _vp]),
     "mi_model_load_gguf": (_i32, [_vp, C.c_char_p, _i32, C.POINTER(_vp)]),
@@ -178,6 +179,10 @@ class Context:
     def gemv_q4_q8_noalloc(self, w, xq, xd, y, bias=None):
         """The GEMV through the entry point that never allocates (fixed built-in scratch)."""
         self.check(self.lib.mi_gemv_q4_q8_noalloc(self.h, w.h, _ptr(xq), _ptr(xd), _ptr(bias), _ptr(y)), "mi_gemv_q4_q8_noalloc")
+
+    def gemm_q4_q8(self, w, xq, xd, M, y, bias=None):
+        """M token vectors per weight pass on the tensor cores; y is [M][rows]."""
+        self.check(self.lib.mi_gemm_q4_q8(self.h, w.h, _ptr(xq), _ptr(xd), M, _ptr(bias), _ptr(y)), "mi_gemm_q4_q8")
 
     def block_isums(self, w, xq, isum):
         self.check(self.lib.mi_block_isums_q4_q8(self.h, w.h, _ptr(xq), _ptr(isum)), "mi_block_isums_q4_q8")
