@@ -1,0 +1,48 @@
+"""GPU parity at the benchmark's own sizes (configs 0 and 2 of the benchmark definition):
+the Qwen2.5-0.5B and -1.5B shapes with seeded random all-q4_0 weights, against the CPU
+oracle in q8_0-activation / fp16-KV mode.  The oracle needs about half a second (0.5B) to a
+second and a half (1.5B) per token on the test machine's host cores, so the number of
+positions is bounded; the GPU side runs the full prompt + generation of config 0.
+
+Bars: greedy ids identical; logits within 1e-3 relative at every compared position
+(0.0 is what the double-carried arithmetic gives in practice)."""
+import numpy as np
+import pytest
+
+import gguf_util as gu
+import oracle_util as ou
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+@pytest.mark.parametrize("preset,n_prompt,n_gen,n_logit_pos", [("0.5b", 16, 32, 6), ("1.5b", 8, 6, 3)])
+def test_fullsize_decode_matches_q8_oracle(ctx, pkg, tmp_path, preset, n_prompt, n_gen, n_logit_pos):
+    import torch
+    path = gu.make_synthetic(tmp_path / "m.gguf", preset, seed=2025)
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    prompt = [int(t) for t in np.random.default_rng(2025).integers(0, V, n_prompt)]
+    n_steps = n_prompt + n_gen - 1
+    m = pkg.Model(ctx, path, n_steps + 1)
+    got, _ = m.generate(prompt, n_gen)                                  # persistent engine, config-0 style run
+    seq = prompt + got[:-1]
+    # the oracle follows the same token sequence (teacher-forced on the GPU's ids) and must predict the same ids
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n_steps + 1)
+    logits = torch.zeros((n_steps, V), dtype=torch.float32, device="cuda")
+    m2 = pkg.Model(ctx, path, n_steps + 1)
+    pred, _ = m2.decode(seq, n_steps, 0, logits, pkg.DECODE_PER_PHASE)
+    assert pred[n_prompt - 1:] == got                                   # both engines, same stream
+    check_at = set(range(n_logit_pos)) | {n_steps - 1}
+    worst = 0.0
+    for s, t in enumerate(seq):
+        want_logits = s in check_at
+        tok, lo, _ = orc.forward(t, want_logits=want_logits)
+        assert tok == pred[s], f"greedy id differs from the oracle at position {s}"
+        if want_logits:
+            worst = max(worst, rel_err(logits[s].cpu().numpy(), lo))
+    assert worst < 1e-3, f"logits deviate {worst:.2e}"
+    m.free(); m2.free()
