@@ -361,6 +361,47 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(out))
         return
 
+    if args.workload == "gemm":
+        # multi-token GEMM (tcgen05 int8 MMA) on the lm_head shape (131 MB, larger than the L2): one weight pass for M tokens
+        rows, cols = (151936, 1536) if not args.shapes else SWEEP[0]
+        g = torch.Generator(device="cuda"); g.manual_seed(7)
+        n = rows * (cols // 32)
+        raw = torch.randint(0, 256, (n, 18), dtype=torch.uint8, device="cuda", generator=g)
+        raw[:, :2] = (torch.rand(n, device="cuda", generator=g) * 0.009 + 0.001).to(torch.float16).view(torch.uint8).reshape(n, 2)
+        w = ctx.repack_q4_0_dev(raw.reshape(-1), rows, cols, 1)
+        del raw
+        X = torch.randn((16, cols), device="cuda", generator=g)
+        xq = torch.empty((16, cols), dtype=torch.int8, device="cuda"); xd = torch.empty((16, cols // 32), dtype=torch.float16, device="cuda")
+        ctx.quant_q8(X, xq, xd, n=cols, M=16)
+        Y = torch.empty((16, rows), dtype=torch.float32, device="cuda")
+        byt = q4_bytes(rows, cols)
+        res = {}
+        for M in (1, 2, 4, 8, 16):
+            for _ in range(warmup):
+                ctx.gemm_q4_q8(w, xq, xd, M, Y)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                ctx.gemm_q4_q8(w, xq, xd, M, Y)
+            e1.record(); barrier(); ctx.sync()
+            res[M] = e0.elapsed_time(e1) / args.steps
+        if rank != 0:
+            return
+        ach = byt / (res[8] * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "q4_0 x q8_0 multi-token GEMM (tcgen05 int8 MMA): HBM GB/s of one weight pass at M=8", "value": round(ach, 1), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": round(res[8], 5), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "uint4 x int8 -> int32 on tcgen05 (kind::i8), fp64 scaling on CUDA cores", "data": "synthetic",
+            "config": {"workload": f"gemm(config 3, GEMM part): {rows}x{cols}, M in 1,2,4,8,16", "l2": "matrix larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None, "kernel": "gemm_q4_q8_tc_kernel",
+                         "algorithmic_bytes_per_launch": byt},
+            "pass_us_by_M": {str(M): round(v * 1e3, 1) for M, v in res.items()}, "cost_of_8_tokens_vs_1": round(res[8] / res[1], 3),
+            "gpu_launches": args.steps * 5,
+        }))
+        return
+
     # ---------------- decode workload
     if rank == 0:
         ensure_model()
@@ -477,12 +518,12 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm"])
     ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per GEMV shape per GPU (MiB); small values are for profiler captures")
     ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the GEMV sweep (profiler captures)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 512 if args.workload == "decode" else 200
+        args.steps = 512 if args.workload == "decode" else 200 if args.workload == "gemv" else 50
     # torch.distributed.run pins OMP_NUM_THREADS to 1; the CPU baseline on rank 0 is meant to use every host thread
     if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
