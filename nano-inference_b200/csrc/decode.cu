@@ -373,7 +373,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         (st = dev_alloc(ctx, m, &P.att_q, NQ)) || (st = dev_alloc(ctx, m, &P.att_d, NQ / 32)) ||
         (st = dev_alloc(ctx, m, &m->act_buf, (size_t)FF + (size_t)FF / 32 * 2)) ||
         (st = dev_alloc(ctx, m, &P.kc, (size_t)L * max_seq * KVD)) || (st = dev_alloc(ctx, m, &P.vc, (size_t)L * max_seq * KVD)) ||
-        (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NKV)) ||
+        (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NH)) ||
         (st = dev_alloc(ctx, m, &P.part, part_off)) ||
         (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
         (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) || (st = dev_alloc(ctx, m, &P.bar, 64)))

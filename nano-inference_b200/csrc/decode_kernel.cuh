@@ -47,6 +47,7 @@ constexpr int DNT = DNW * 32;
 constexpr int DS = 3;             // ring slots per warp
 constexpr int DSLOT = 4608;       // bytes per slot: the largest tile (8 blocks)
 constexpr int kAttnChunk = 64;    // smallest KV range worth its own CTA
+constexpr int kPerHeadAttnMax = 1024;   // up to this many cached positions a CTA handles one query head, beyond it a whole GQA group
 
 // profile slots: 2*k = staging of phase kind k, 2*k+1 = its main work; 12 = barrier, 13 = step prologue
 enum { kProfBarrier = 12, kProfStep = 13, kProfSlots = 32 };
@@ -100,8 +101,8 @@ struct DecodeParams {
 };
 
 // number of KV chunks for a causal range of Lp positions (host and device agree)
-__host__ __device__ inline int attn_chunks(int Lp, int max_chunks) {
-    int n = (Lp + kAttnChunk - 1) / kAttnChunk;
+__host__ __device__ inline int attn_chunks(int Lp, int max_chunks, int chunk = kAttnChunk) {
+    int n = (Lp + chunk - 1) / chunk;
     return n < 1 ? 1 : (n > max_chunks ? max_chunks : n);
 }
 
@@ -455,14 +456,19 @@ __device__ __forceinline__ void stage_copy_q8(const int8_t* xq, const __half* xd
 // the last CTA of the kv head to arrive), each fold against the common maximum so
 // that the rescale factors are independent of one another; then o/l is rounded to
 // fp32, stored, and quantized to q8_0 for the O projection.
-template <int HD, int G>
+// G = query heads handled by one CTA: all heads of a kv head (one K/V read serves the group: long
+// contexts, bandwidth matters) or a single head (short contexts: K/V come from L2 anyway, and six
+// times as many CTAs each carry a sixth of the serial work).  GQ = query heads per kv head.
+template <int HD, int G, int GQ>
 __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp) {
     constexpr int DPW = HD / 32;           // dims per lane in pass 2 and while folding (dim = lane + 32*i)
     constexpr int SW = HD + 2;             // doubles per (head) state: o[HD], m, l
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int Lp = pos + 1, nch = attn_chunks(Lp, P.max_chunks);
-    if ((int)blockIdx.x >= P.NKV * nch) return;
-    const int kvh = blockIdx.x / nch, ch = blockIdx.x % nch;
+    const int ngrp = P.NH / G;
+    // one head per CTA: 256 positions are one 32-position batch per warp, and a single chunk needs no cross-CTA merge
+    const int Lp = pos + 1, nch = attn_chunks(Lp, min(P.max_chunks, (int)gridDim.x / ngrp), G == 1 ? 256 : kAttnChunk);
+    if ((int)blockIdx.x >= ngrp * nch) return;
+    const int grp = blockIdx.x / nch, ch = blockIdx.x % nch, h0 = grp * G, kvh = h0 / GQ;
     const int p0 = (int)((long long)ch * Lp / nch), p1 = (int)((long long)(ch + 1) * Lp / nch);
     double* scr = reinterpret_cast<double*>(stage);                        // [warp][G][SW]
     double* wts = scr + DNW * G * SW;                                       // [warp][32][G]
@@ -471,9 +477,9 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     // q of this kv head's G query heads, from the packed QKV vector: dim d of a head sits at 2d (d < HD/2) or 2(d-HD/2)+1
     for (int i = tid; i < G * HD; i += DNT) {
         const int j = i / HD, d = i % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
-        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(kvh * G + j) * HD + pk);
+        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(h0 + j) * HD + pk);
     }
-    if (ch == nch - 1) {                                                    // this CTA's range ends at the new position: store its K and V (fp16)
+    if (ch == nch - 1) {      // this CTA's range ends at the new position: store its K and V (fp16); CTAs that share a kv head store the same bits
         const int nq = P.NH * HD;
         for (int d = tid; d < HD; d += DNT) {
             const int pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
@@ -615,7 +621,7 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     __syncthreads();
     // warp j folds head j's DNW warp states against their common maximum and publishes the chunk partial
     if (warp < G) {
-        const int j = warp, head = kvh * G + j;
+        const int j = warp, head = h0 + j;
         float mm = -INFINITY;
         #pragma unroll
         for (int w = 0; w < DNW; w++) mm = fmaxf(mm, (float)scr[(size_t)(w * G + j) * SW + HD]);
@@ -655,14 +661,14 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     __threadfence();
     __syncthreads();
     __shared__ unsigned s_prev;
-    if (tid == 0) s_prev = atomicAdd(P.attn_cnt + kvh, 1u);
+    if (tid == 0) s_prev = atomicAdd(P.attn_cnt + grp, 1u);
     __syncthreads();
     if (s_prev != (unsigned)nch - 1) return;
     // last chunk of this kv head: fold the chunk partials against their common maximum, normalise, emit fp32 + q8_0
     __threadfence();
-    if (tid == 0) P.attn_cnt[kvh] = 0;
+    if (tid == 0) P.attn_cnt[grp] = 0;
     if (warp < G) {
-        const int j = warp, head = kvh * G + j;
+        const int j = warp, head = h0 + j;
         const double* gp = P.attn_part + (size_t)head * P.max_chunks * SW;
         float mm = -INFINITY;
         for (int c = lane; c < nch; c += 32) mm = fmaxf(mm, (float)__ldcg(gp + (size_t)c * SW + HD));
@@ -780,7 +786,8 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                     if (p < nq + 2 * P.KVD) __stcg(P.qkv_out + p, out);
                 });
             } else if (k == 1) {
-                attention_phase<HD, G>(P, l, pos, sm.stage, tp);
+                if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G>(P, l, pos, sm.stage, tp);
+                else attention_phase<HD, G, G>(P, l, pos, sm.stage, tp);
             } else if (k == 2) {
                 stage_copy_q8(P.att_q, P.att_d, P.E / 32, xq_s, xs_s);
                 prof_mark(P, tp, 4);
