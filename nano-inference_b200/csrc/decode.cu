@@ -94,7 +94,7 @@ int alloc_tiled(mi_ctx* ctx, mi_model* m, int64_t rows, int64_t cols, uint8_t** 
 // eight warps already share every unit.  The O and down projections only emit partial
 // sums for the next prologue, so they are split until every CTA has a unit.
 int plan_ks(int kind, int groups, int nt, int grid) {
-    if (kind != JOB_O && kind != JOB_DOWN) return 1;
+    if (kind != JOB_DOWN) return 1;      // measured: the O projection (6 tiles per row group: one per warp) gains nothing from a split
     int ks = grid / std::max(groups, 1);
     return std::max(1, std::min(std::min(ks, nt), 4));     // the consumer prologue folds at most four partials per row
 }
@@ -249,9 +249,9 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         mi_tp_partition(groups, tp_rank, tp_world, &g0, &g1);
         jb.g_off = g0; jb.groups = g1 - g0;
         jb.base = base + (size_t)g0 * nacc * jb.nt * tile_bytes(jb.kb);
-        const char* force = getenv("MINFER_KS");
         jb.ks = plan_ks(kind, (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
-        if (force && (kind == JOB_O || kind == JOB_DOWN)) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
+        const char* force = kind == JOB_O ? getenv("MINFER_KS_O") : kind == JOB_DOWN ? getenv("MINFER_KS_DOWN") : nullptr;   // tuning knobs
+        if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
         jb.n_units = jb.groups * jb.ks;
         jb.part_off = (int)part_off;
         if (kind == JOB_O || kind == JOB_DOWN) part_off += (size_t)groups * jb.ks * 32;

@@ -156,3 +156,28 @@ def test_decode_argument_checks(ctx, pkg, cases, tmp_path):
     with pytest.raises(pkg.MinferError):
         pkg.Model(ctx, trunc, 8)
     m.free()
+
+
+def test_long_context_attention_paths_match_oracle(ctx, pkg, cases):
+    """Contexts past 1024 positions switch attention to one CTA per (kv head, 64-position chunk) with a
+    cross-CTA merge; contexts of 257..1024 use one CTA per (query head, 256-position chunk), also merged.
+    Walk a tiny model through 1100 positions and compare logits and greedy ids with the oracle on the way."""
+    import torch
+    path, c = cases[1]
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    n = 1100
+    seq = [int(t) for t in np.random.default_rng(8).integers(0, V, n)]
+    m = pkg.Model(ctx, path, n + 1)
+    check = {0, 255, 256, 257, 511, 512, 700, 1023, 1024, 1025, 1099}
+    logits = torch.zeros((n, V), dtype=torch.float32, device="cuda")
+    pred, _ = m.decode(seq, n, 0, logits, pkg.DECODE_PERSISTENT)
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n + 1)
+    worst = 0.0
+    for s, t in enumerate(seq):
+        tok, lo, _ = orc.forward(t, want_logits=s in check)
+        assert tok == pred[s], f"greedy id differs at position {s}"
+        if s in check:
+            worst = max(worst, rel_err(logits[s].cpu().numpy(), lo))
+    assert worst < REL_TOL, f"logits deviate {worst:.2e}"
+    m.free()
