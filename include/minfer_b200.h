@@ -226,6 +226,31 @@ MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host
  * inspection.  For per-phase parity checks. */
 MI_API int mi_decode_phases(mi_ctx* ctx, mi_model* model, int32_t token, int pos, int phase_begin, int phase_end);
 
+/* ---- the M-token step ----------------------------------------------------------- */
+
+/* Scores M (1..16) tokens at positions pos0 .. pos0+M-1 in ONE pass over the weights:
+ * token i is processed as if it were decoded alone after tokens 0..i-1 of the call, so
+ * its logits do not depend on M (the drafted-token verify step of the reference,
+ * src/cuda_infer.cu:990-1029 forward_batch and src/mega.cu:246-299 gemv_seq; also its chunked
+ * prompt processing, src/cuda_infer.cu:1130-1144).  Projections run as mi_gemm_q4_q8, attention
+ * as mi_attn_splitkv over the model's fp16 KV cache, which receives all M positions; a caller
+ * that accepts only a prefix simply continues at the first rejected position.
+ * out_tokens_host[i] (optional) = greedy token after token i; logits_dev (optional) = [M][n_vocab]
+ * fp32.  The model's current token becomes out_tokens[M-1].  Synchronous.  Unsharded models only. */
+MI_API int mi_verify(mi_ctx* ctx, mi_model* model, const int32_t* tokens_host, int M, int pos0,
+                     int32_t* out_tokens_host, float* logits_dev, float* elapsed_ms);
+
+/* Split-KV causal attention with grouped queries for M (1..16) consecutive query positions
+ * (replaces attn_partial + attn_combine, src/cuda_infer.cu:650-702, and mega's attention + combine,
+ * src/mega.cu:414-521, 705-741).  q_dev: [M][n_head * head_dim] fp32 in natural dimension order
+ * (after RoPE); kcache_dev / vcache_dev: fp16 bits, [positions][n_head_kv * head_dim], holding
+ * positions 0 .. pos0+M-1; query i attends to positions 0 .. pos0+i.  Scores are scaled by
+ * 1/sqrt(head_dim); the softmax merge across KV chunks uses the running-maximum rule of the
+ * reference with sums carried in double.  out_dev: [M][n_head * head_dim] fp32.  Asynchronous
+ * on the context's stream.  head_dim in {32, 64, 128}. */
+MI_API int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* kcache_dev, const uint16_t* vcache_dev,
+                           int n_head, int n_head_kv, int head_dim, int pos0, int M, float* out_dev);
+
 /* ---- tensor parallelism (one process per GPU) --------------------------------- */
 
 /* The reference is single-GPU (README.md:54); this part has no counterpart in it.

@@ -63,6 +63,8 @@ SIGNATURES = {
     "mi_model_state_ptr": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
     "mi_decode": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, C.POINTER(C.c_float)]),
     "mi_decode_phases": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32]),
+    "mi_verify": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(C.c_float)]),
+    "mi_attn_splitkv": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "mi_tp_partition": (None, [_i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_i32)]),
     "mi_model_load_gguf_tp": (_i32, [_vp, C.c_char_p, _i32, _i32, _i32, C.POINTER(_vp)]),
     "mi_model_tp_region": (_i32, [_vp, _i32, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
@@ -184,6 +186,11 @@ class Context:
         """M token vectors per weight pass on the tensor cores; y is [M][rows]."""
         self.check(self.lib.mi_gemm_q4_q8(self.h, w.h, _ptr(xq), _ptr(xd), M, _ptr(bias), _ptr(y)), "mi_gemm_q4_q8")
 
+    def attn_splitkv(self, q, kcache, vcache, n_head, n_head_kv, head_dim, pos0, M, out):
+        """Causal GQA attention of M consecutive queries over an fp16 cache [positions][n_head_kv*head_dim]."""
+        self.check(self.lib.mi_attn_splitkv(self.h, _ptr(q), _ptr(kcache), _ptr(vcache), n_head, n_head_kv, head_dim, pos0, M, _ptr(out)),
+                   "mi_attn_splitkv")
+
     def block_isums(self, w, xq, isum):
         self.check(self.lib.mi_block_isums_q4_q8(self.h, w.h, _ptr(xq), _ptr(isum)), "mi_block_isums_q4_q8")
 
@@ -236,6 +243,24 @@ class Model:
         self.ctx.check(self.ctx.lib.mi_decode(self.ctx.h, self.h, _ptr(toks) if toks.size else None, toks.size, n_steps, pos0,
                                               _ptr(out), _ptr(logits), mode, C.byref(ms)), "mi_decode")
         return out[:n_steps].tolist(), ms.value
+
+    def verify(self, tokens, pos0=0, logits=None):
+        """One M-token pass (M = len(tokens) <= 16): returns (greedy token after each, device milliseconds)."""
+        import numpy as np
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.empty(toks.size, dtype=np.int32)
+        ms = C.c_float(0)
+        self.ctx.check(self.ctx.lib.mi_verify(self.ctx.h, self.h, _ptr(toks), toks.size, pos0, _ptr(out), _ptr(logits), C.byref(ms)), "mi_verify")
+        return out.tolist(), ms.value
+
+    def prefill(self, tokens, pos0=0, chunk=16):
+        """Prompt processing through the M-token step, `chunk` tokens per weight pass; returns (token after the last one, ms)."""
+        total, last = 0.0, None
+        for i in range(0, len(tokens), chunk):
+            out, ms = self.verify(tokens[i:i + chunk], pos0 + i)
+            total += ms
+            last = out[-1]
+        return last, total
 
     def generate(self, prompt, n_gen, mode=DECODE_PERSISTENT):
         """The reference CLI's output: n_gen greedy ids, the first predicted after the last prompt token."""

@@ -1,6 +1,6 @@
 // Model loading (GGUF -> tiled device layout), job planning and launching of the
 // fused decode kernel; the model / decode part of the C ABI.
-#include "decode_kernel.cuh"
+#include "model.cuh"
 #include "gguf_file.hpp"
 
 #include <algorithm>
@@ -12,40 +12,7 @@
 
 using namespace mi;
 
-struct mi_model {
-    int device = 0;
-    int L = 0, E = 0, FF = 0, NH = 0, NKV = 0, HD = 0, KVD = 0, V = 0, G = 0;
-    float eps = 1e-6f, rope_base = 1e6f;
-    int max_seq = 0, grid = 0, max_chunks = 0;
-    int tp_rank = 0, tp_world = 1;
-    bool tied = false;
-    int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)
-    std::vector<void*> allocs;            // everything cudaMalloc'ed for this model
-    std::vector<Job> jobs;
-    DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
-    int* d_in_tokens = nullptr; int in_capacity = 0;
-    int* d_out_tokens = nullptr; int out_capacity = 0;
-    size_t smem = 0;
-    size_t part_count = 0;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-    unsigned long long* prof_buf = nullptr;
-    uint8_t* act_buf = nullptr;          // [act_q | act_d]
-    float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
-    int qkv_rows = 0;
-};
-
 namespace {
-
-template <typename T>
-int dev_alloc(mi_ctx* ctx, mi_model* m, T** p, size_t n, bool zero = true) {
-    *p = nullptr;
-    if (n == 0) n = 1;
-    cudaError_t e = cudaMalloc((void**)p, n * sizeof(T));
-    if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: cudaMalloc(%zu) failed: %s", n * sizeof(T), cudaGetErrorString(e));
-    m->allocs.push_back(*p);
-    if (zero) { e = cudaMemset(*p, 0, n * sizeof(T)); if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "model: cudaMemset failed"); }
-    return MI_OK;
-}
 
 struct Staging {       // one reusable device buffer for raw GGUF bytes
     void* d = nullptr; size_t cap = 0;
@@ -263,6 +230,11 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
             wrot = (wrot + nacc * ((jb.nt + jb.ks - 1) / jb.ks)) & (DNW - 1);
         }
         m->jobs.push_back(jb);
+        mi_weight v;                                  // the whole matrix, for the M-token step
+        v.rows = (int64_t)groups * nacc * 32; v.cols = cols; v.count = 1; v.nb = jb.nb; v.kb = jb.kb; v.nt = jb.nt;
+        v.groups = groups * nacc; v.mat_stride = 0; v.bytes = (size_t)v.groups * jb.nt * tile_bytes(jb.kb);
+        v.dev = const_cast<uint8_t*>(base);
+        m->views.push_back(v);
     };
     for (int l = 0; l < L; l++) {
         const std::string p = "blk." + std::to_string(l) + ".";
@@ -304,6 +276,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         m->weight_bytes_q4 += ((int64_t)NQ * E + 2 * (int64_t)KVD * E + (int64_t)E * NQ + 3 * (int64_t)FF * E) / 32 * 18;
     }
     add_job(d_lm, (V + 31) / 32, E, 1, JOB_LM, L);
+    m->views.back().rows = V;
     m->weight_bytes_q4 += (int64_t)V * E / 32 * 18;
     MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
 
@@ -359,6 +332,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     MI_CUDA(ctx, cudaMemcpy(d_lp, lp.data(), lp.size() * sizeof(LayerPtrs), cudaMemcpyHostToDevice));
     MI_CUDA(ctx, cudaMemcpy(d_jobs, m->jobs.data(), m->jobs.size() * sizeof(Job), cudaMemcpyHostToDevice));
     P.layers = d_lp; P.jobs = d_jobs;
+    m->layer_ptrs = lp;
 
     // rope frequencies exactly as the reference computes them on the host: powf(base, -2i/hd) (src/cpu_infer.cpp:54)
     std::vector<float> freq(HD / 2);

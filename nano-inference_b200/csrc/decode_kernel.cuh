@@ -459,7 +459,10 @@ __device__ __forceinline__ void stage_copy_q8(const int8_t* xq, const __half* xd
 // G = query heads handled by one CTA: all heads of a kv head (one K/V read serves the group: long
 // contexts, bandwidth matters) or a single head (short contexts: K/V come from L2 anyway, and six
 // times as many CTAs each carry a sixth of the serial work).  GQ = query heads per kv head.
-template <int HD, int G, int GQ>
+// STORE_KV: the CTA whose range ends at the new position writes that position's K and V from the packed QKV
+// vector (the decode loop); callers that stored them beforehand pass false.  QNAT: q is in natural dimension
+// order (the stand-alone entry point) instead of the packed pair-adjacent order of the fused QKV projection.
+template <int HD, int G, int GQ, bool STORE_KV = true, bool QNAT = false>
 __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp) {
     constexpr int DPW = HD / 32;           // dims per lane in pass 2 and while folding (dim = lane + 32*i)
     constexpr int SW = HD + 2;             // doubles per (head) state: o[HD], m, l
@@ -476,10 +479,10 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     double* qs = wts + DNW * 32 * G;                                        // [G][LPP][QSTR]: 16-byte skew per lane, conflict-free
     // q of this kv head's G query heads, from the packed QKV vector: dim d of a head sits at 2d (d < HD/2) or 2(d-HD/2)+1
     for (int i = tid; i < G * HD; i += DNT) {
-        const int j = i / HD, d = i % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+        const int j = i / HD, d = i % HD, pk = QNAT ? d : (d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1);
         qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(h0 + j) * HD + pk);
     }
-    if (ch == nch - 1) {      // this CTA's range ends at the new position: store its K and V (fp16); CTAs that share a kv head store the same bits
+    if (STORE_KV && ch == nch - 1) {      // this CTA's range ends at the new position: store its K and V (fp16); CTAs that share a kv head store the same bits
         const int nq = P.NH * HD;
         for (int d = tid; d < HD; d += DNT) {
             const int pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
@@ -574,7 +577,8 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         for (int j = 0; j < G; j++) {
             const float bm = warp_max_float(sc[j]);
             const float mn = fmaxf(m[j], bm);                                // finite: the batch holds a valid position
-            const double cr = m[j] == -INFINITY ? 0.0 : exp((double)m[j] - (double)mn);
+            // the running maximum is warp-uniform; while it stands the rescale factor is exp(0) = 1 exactly
+            const double cr = mn == m[j] ? 1.0 : (m[j] == -INFINITY ? 0.0 : exp((double)m[j] - (double)mn));
             const double w = valid ? exp((double)sc[j] - (double)mn) : 0.0;
             wl[lane * G + j] = w;                                            // the denominator picks the weights up in pass 2
             ls[j] = __dmul_rn(ls[j], cr);
@@ -670,20 +674,42 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     if (warp < G) {
         const int j = warp, head = h0 + j;
         const double* gp = P.attn_part + (size_t)head * P.max_chunks * SW;
+        // rescale factors of all chunks first (lane = chunk, so the exponentials run side by side), parked in the
+        // warp-state buffer, which nobody reads any more; then the fold in chunk order, eight chunks' loads in flight
+        double* fs = scr + (size_t)j * DNW * SW;                            // nch <= grid size / kv heads <= DNW * SW
         float mm = -INFINITY;
-        for (int c = lane; c < nch; c += 32) mm = fmaxf(mm, (float)__ldcg(gp + (size_t)c * SW + HD));
+        for (int c = lane; c < nch; c += 32) {
+            const float mc = (float)__ldcg(gp + (size_t)c * SW + HD);
+            fs[c] = (double)mc; mm = fmaxf(mm, mc);
+        }
         #pragma unroll
         for (int sft = 16; sft; sft >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, sft));
+        for (int c = lane; c < nch; c += 32) {
+            const float mc = (float)fs[c];
+            fs[c] = mc == -INFINITY ? 0.0 : exp((double)mc - (double)mm);
+        }
+        __syncwarp();
         double ob[DPW], ll = 0.0;
         #pragma unroll
         for (int i = 0; i < DPW; i++) ob[i] = 0.0;
-        for (int c = 0; c < nch; c++) {
-            const double* g2 = gp + (size_t)c * SW;
-            const float mc = (float)__ldcg(g2 + HD);
-            const double f = mc == -INFINITY ? 0.0 : exp((double)mc - (double)mm);
-            ll = __fma_rn(__ldcg(g2 + HD + 1), f, ll);
+        for (int c0 = 0; c0 < nch; c0 += 8) {
+            double lv[8], ov[8][DPW];
             #pragma unroll
-            for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(__ldcg(g2 + lane + 32 * i), f, ob[i]);
+            for (int u = 0; u < 8; u++) {
+                const double* g2 = gp + (size_t)min(c0 + u, nch - 1) * SW;
+                lv[u] = __ldcg(g2 + HD + 1);
+                #pragma unroll
+                for (int i = 0; i < DPW; i++) ov[u][i] = __ldcg(g2 + lane + 32 * i);
+            }
+            #pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (c0 + u < nch) {
+                    const double f = fs[c0 + u];
+                    ll = __fma_rn(lv[u], f, ll);
+                    #pragma unroll
+                    for (int i = 0; i < DPW; i++) ob[i] = __fma_rn(ov[u][i], f, ob[i]);
+                }
+            }
         }
         #pragma unroll
         for (int i = 0; i < DPW; i++) {

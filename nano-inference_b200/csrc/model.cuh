@@ -1,0 +1,62 @@
+// The loaded model as the decode and the M-token step see it.
+#pragma once
+#include "decode_kernel.cuh"
+
+#include <vector>
+
+namespace mi {
+// device buffers of the M-token step (all [tokens][...], token-major)
+struct VerifyBufs {
+    int cap = 0;                       // tokens the buffers hold
+    float* X = nullptr;                // residual stream [M][E]
+    float* Y = nullptr;                // projection output [M][max(qkv_rows, 2FF, E)]
+    float* qkv = nullptr;              // [M][qkv_rows (padded)] after bias and RoPE, packed row order
+    int8_t* xq = nullptr; __half* xd = nullptr;         // q8_0 of the normed input [M][E]
+    float* att = nullptr; int8_t* att_q = nullptr; __half* att_d = nullptr;   // [M][NQ]
+    int8_t* act_q = nullptr; __half* act_d = nullptr;   // [M][FF]
+    float* logits = nullptr;           // [M][V]
+    int* tokens = nullptr; int* out = nullptr;          // [M]
+    double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
+};
+}
+
+struct mi_model {
+    int device = 0;
+    int L = 0, E = 0, FF = 0, NH = 0, NKV = 0, HD = 0, KVD = 0, V = 0, G = 0;
+    float eps = 1e-6f, rope_base = 1e6f;
+    int max_seq = 0, grid = 0, max_chunks = 0;
+    int tp_rank = 0, tp_world = 1;
+    bool tied = false;
+    int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)
+    std::vector<void*> allocs;            // everything cudaMalloc'ed for this model
+    std::vector<mi::Job> jobs;
+    mi::DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
+    int* d_in_tokens = nullptr; int in_capacity = 0;
+    int* d_out_tokens = nullptr; int out_capacity = 0;
+    size_t smem = 0;
+    size_t part_count = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    unsigned long long* prof_buf = nullptr;
+    uint8_t* act_buf = nullptr;          // [act_q | act_d]
+    float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
+    int qkv_rows = 0;
+    std::vector<mi_weight> views;         // [4L+1] whole matrices in job order (QKV, O, gate/up, down per layer; lm_head), for the M-token step
+    std::vector<mi::LayerPtrs> layer_ptrs;    // host copy of the per-layer norm / bias pointers
+    mi::VerifyBufs vb;                    // buffers of the M-token step, allocated on first use
+};
+
+
+namespace mi {
+
+template <typename T>
+int dev_alloc(mi_ctx* ctx, mi_model* m, T** p, size_t n, bool zero = true) {
+    *p = nullptr;
+    if (n == 0) n = 1;
+    cudaError_t e = cudaMalloc((void**)p, n * sizeof(T));
+    if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: cudaMalloc(%zu) failed: %s", n * sizeof(T), cudaGetErrorString(e));
+    m->allocs.push_back(*p);
+    if (zero) { e = cudaMemset(*p, 0, n * sizeof(T)); if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "model: cudaMemset failed"); }
+    return MI_OK;
+}
+
+}  // namespace mi

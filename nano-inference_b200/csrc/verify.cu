@@ -1,0 +1,259 @@
+// The M-token step: M <= 16 tokens at consecutive positions scored in one pass over the
+// weights (speculative verify, chunked prompt processing), and the stand-alone split-KV
+// attention entry point.
+//
+// Replaces forward_batch (reference src/cuda_infer.cu:990-1029: quant_x_q8_batch,
+// gemv_dp4a_batch<T>, rope / kv_store / attention per token) and the M-token path of the
+// persistent kernel (reference src/mega.cu:246-299 gemv_seq, :414-521 attention).
+//
+// One pass is a sequence of launches per layer
+//     norm+q8 (M tokens) -> tcgen05 GEMM QKV -> RoPE + fp16 KV store -> attention (M queries)
+//     -> GEMM O -> residual + norm+q8 -> GEMM gate/up -> SwiGLU+q8 -> GEMM down
+// and finally norm+q8 -> GEMM lm_head -> argmax per token.  Every token goes through the
+// very expressions of the single-token decode kernel (same quantizer, same double-carried
+// sums, the same attention code with the token's own causal range and chunking), so its
+// logits do not depend on how many tokens share the pass.
+#include "model.cuh"
+
+#include <algorithm>
+
+using namespace mi;
+
+namespace {
+
+constexpr int VMAX = 16;
+
+// x = (embedding row | X) (+ Y), committed to X; q8_0(rmsnorm(x) * w) (src/cpu_infer.cpp:40-46)
+__global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const int* __restrict__ tokens, bool embed, float* X, const float* Y,
+                                                      int ystride, const float* __restrict__ w, int8_t* xq, __half* xd) {
+    extern __shared__ float xs[];
+    __shared__ double red[DNW];
+    const int m = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, E = P.E, nb = E / 32;
+    const int token = embed ? __ldg(tokens + m) : 0;
+    double ss = 0.0;
+    for (int b = warp; b < nb; b += DNW) {
+        const int e = b * 32 + lane;
+        float x;
+        if (embed) {                                                // value (nibble - 8) * d (src/gguf.h:94-102)
+            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
+            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
+            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
+            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
+            x = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
+        } else {
+            x = X[(size_t)m * E + e];
+        }
+        if (Y) x = __fadd_rn(x, Y[(size_t)m * ystride + e]);
+        X[(size_t)m * E + e] = x;
+        xs[e] = x;
+        const double xdv = x; ss = __fma_rn(xdv, xdv, ss);
+    }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    #pragma unroll
+    for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
+    const float mean = __double2float_rn(__ddiv_rn(tot, (double)E));
+    const float scale = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, P.eps)));
+    for (int b = warp; b < nb; b += DNW) {
+        const int e = b * 32 + lane;
+        const float v = __fmul_rn(__fmul_rn(xs[e], scale), __ldg(w + e));
+        xq[(size_t)m * E + e] = (int8_t)quant_block_warp(v, lane, nullptr, xd + (size_t)m * nb + b);
+    }
+}
+
+// RoPE on the packed (pair-adjacent) q and k rows of every token, fp16 K / V into the cache
+__global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, int pos0, float* qkv, int stride) {
+    const int m = blockIdx.x, pos = pos0 + m, HD = P.HD, nq = P.NH * HD;
+    float* v = qkv + (size_t)m * stride;
+    for (int pr = threadIdx.x; pr < (nq + P.KVD) / 2; pr += blockDim.x) {
+        const int p = 2 * pr, within = (p < nq ? p : p - nq) % HD, i = within >> 1;
+        const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + i));      // fp32 angle, as src/cpu_infer.cpp:54
+        const double c = (double)__double2float_rn(cos(th)), s = (double)__double2float_rn(sin(th));
+        const double x0 = v[p], x1 = v[p + 1];
+        v[p] = __double2float_rn(__dsub_rn(__dmul_rn(x0, c), __dmul_rn(x1, s)));
+        v[p + 1] = __double2float_rn(__dadd_rn(__dmul_rn(x0, s), __dmul_rn(x1, c)));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < P.KVD; e += blockDim.x) {
+        const int kvh = e / HD, d = e % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+        P.kc[((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + kvh * HD + pk]);
+        P.vc[((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + P.KVD + e]);
+    }
+}
+
+// attention of M queries: blockIdx.y = query; every query runs the decode kernel's attention over its own causal range
+template <int HD, int G, bool QNAT>
+__global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, int pos0, long long q_stride) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int m = blockIdx.y, nq = P.NH * HD;
+    DecodeParams Q = P;
+    Q.qkv_out = P.qkv_out + (size_t)m * q_stride;
+    Q.att = P.att + (size_t)m * nq; Q.att_q = P.att_q + (size_t)m * nq; Q.att_d = P.att_d + (size_t)m * (nq / 32);
+    Q.attn_part = P.attn_part + (size_t)m * P.NH * P.max_chunks * (HD + 2);
+    Q.attn_cnt = P.attn_cnt + (size_t)m * P.NH;
+    Q.prof = nullptr;
+    unsigned long long tp = 0;
+    const int pos = pos0 + m;
+    if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G, false, QNAT>(Q, l, pos, smem, tp);
+    else attention_phase<HD, G, G, false, QNAT>(Q, l, pos, smem, tp);
+}
+
+// SwiGLU of the interleaved gate / up groups -> q8_0; one warp per 32-element block
+__global__ void __launch_bounds__(DNT) vf_swiglu_quant(const float* Y, int FF, int8_t* act_q, __half* act_d) {
+    const int m = blockIdx.y, g = blockIdx.x * DNW + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (g >= FF / 32) return;
+    const float* y = Y + (size_t)m * 2 * FF + (size_t)g * 64;
+    const double gd = (double)y[lane];
+    const float a = __double2float_rn(__dmul_rn(__ddiv_rn(gd, __dadd_rn(1.0, exp(-gd))), (double)y[32 + lane]));
+    act_q[(size_t)m * FF + g * 32 + lane] = (int8_t)quant_block_warp(a, lane, nullptr, act_d + (size_t)m * (FF / 32) + g);
+}
+
+// greedy pick per token, lowest index on ties (src/cpu_infer.cpp:153-154)
+__global__ void __launch_bounds__(1024) vf_argmax(const float* logits, long long stride, int V, int* out) {
+    __shared__ float bv[32]; __shared__ int bi[32];
+    const float* lg = logits + (size_t)blockIdx.x * stride;
+    float best = -INFINITY; int idx = 0x7fffffff;
+    for (int r = threadIdx.x; r < V; r += blockDim.x) {
+        const float v = lg[r];
+        if (v > best || (v == best && r < idx)) { best = v; idx = r; }
+    }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ob > best || (ob == best && oi < idx)) { best = ob; idx = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = best; bi[threadIdx.x >> 5] = idx; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) if (bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0])) { bv[0] = bv[w]; bi[0] = bi[w]; }
+        out[blockIdx.x] = bi[0];
+    }
+}
+
+size_t attn_smem_bytes(int HD, int G) {
+    return ((size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * (HD + 16) * 8 + 127) / 128 * 128;
+}
+
+template <bool QNAT>
+int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid, int M, int l, int pos0, long long q_stride) {
+    void (*kern)(DecodeParams, int, int, long long) = nullptr;
+    #define MI_PICK(hd, g) if (HD == hd && G == g) kern = vf_attention<hd, g, QNAT>;
+    MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
+    #undef MI_PICK
+    if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "attention: head_dim %d with %d query heads per kv head is not instantiated", HD, G);
+    const size_t smem = attn_smem_bytes(HD, G);
+    MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<dim3(grid, M), DNT, smem, ctx->stream>>>(P, l, pos0, q_stride);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
+int ensure_bufs(mi_ctx* ctx, mi_model* m) {
+    VerifyBufs& b = m->vb;
+    if (b.cap >= VMAX) return MI_OK;
+    const int M = VMAX, E = m->E, FF = m->FF, NQ = m->NH * m->HD, qr = (m->qkv_rows + 31) / 32 * 32;
+    const size_t ymax = std::max<size_t>({(size_t)qr, (size_t)2 * FF, (size_t)E});
+    int st;
+    if ((st = dev_alloc(ctx, m, &b.X, (size_t)M * E)) || (st = dev_alloc(ctx, m, &b.Y, (size_t)M * ymax)) ||
+        (st = dev_alloc(ctx, m, &b.qkv, (size_t)M * qr)) ||
+        (st = dev_alloc(ctx, m, &b.xq, (size_t)M * E)) || (st = dev_alloc(ctx, m, &b.xd, (size_t)M * E / 32)) ||
+        (st = dev_alloc(ctx, m, &b.att, (size_t)M * NQ)) || (st = dev_alloc(ctx, m, &b.att_q, (size_t)M * NQ)) ||
+        (st = dev_alloc(ctx, m, &b.att_d, (size_t)M * NQ / 32)) ||
+        (st = dev_alloc(ctx, m, &b.act_q, (size_t)M * FF)) || (st = dev_alloc(ctx, m, &b.act_d, (size_t)M * FF / 32)) ||
+        (st = dev_alloc(ctx, m, &b.logits, (size_t)M * m->V)) ||
+        (st = dev_alloc(ctx, m, &b.tokens, (size_t)M)) || (st = dev_alloc(ctx, m, &b.out, (size_t)M)) ||
+        (st = dev_alloc(ctx, m, &b.attn_part, (size_t)M * m->NH * m->max_chunks * (m->HD + 2))) ||
+        (st = dev_alloc(ctx, m, &b.attn_cnt, (size_t)M * m->NH)))
+        return st;
+    b.cap = M;
+    return MI_OK;
+}
+
+}  // namespace
+
+extern "C" int mi_verify(mi_ctx* ctx, mi_model* m, const int32_t* tokens_host, int M, int pos0, int32_t* out_tokens_host,
+                         float* logits_dev, float* elapsed_ms) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !tokens_host) return set_error(ctx, MI_ERR_INVALID, "verify: null argument");
+    if (M < 1 || M > VMAX) return set_error(ctx, MI_ERR_LIMIT, "verify: M=%d tokens per pass; this entry point takes 1..%d", M, VMAX);
+    if (pos0 < 0 || pos0 + M > m->max_seq)
+        return set_error(ctx, MI_ERR_LIMIT, "verify: positions %d..%d exceed the KV cache of %d", pos0, pos0 + M - 1, m->max_seq);
+    if (m->tp_world != 1) return set_error(ctx, MI_ERR_UNSUPPORTED, "verify: the M-token step runs on an unsharded model");
+    for (int i = 0; i < M; i++)
+        if (tokens_host[i] < 0 || tokens_host[i] >= m->V) return set_error(ctx, MI_ERR_INVALID, "verify: token id %d out of range", tokens_host[i]);
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    int st;
+    if ((st = ensure_bufs(ctx, m))) return st;
+    VerifyBufs& b = m->vb;
+    const int E = m->E, FF = m->FF, L = m->L, NQ = m->NH * m->HD, qr = (m->qkv_rows + 31) / 32 * 32, V = m->V;
+    (void)qr; (void)NQ;
+    MI_CUDA(ctx, cudaMemcpyAsync(b.tokens, tokens_host, (size_t)M * 4, cudaMemcpyHostToDevice, ctx->stream));
+    DecodeParams P = m->P;
+    P.qkv_out = b.qkv; P.att = b.att; P.att_q = b.att_q; P.att_d = b.att_d; P.attn_part = b.attn_part; P.attn_cnt = b.attn_cnt;
+    P.prof = nullptr;
+    const std::vector<LayerPtrs>& lp = m->layer_ptrs;
+    float* logits = logits_dev ? logits_dev : b.logits;
+    const size_t nsm = (size_t)E * 4;
+    if (nsm > 48 * 1024) MI_CUDA(ctx, cudaFuncSetAttribute(vf_norm_quant, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nsm));
+    MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    for (int l = 0; l < L; l++) {
+        const mi_weight *wqkv = &m->views[4 * l], *wo = &m->views[4 * l + 1], *wgu = &m->views[4 * l + 2], *wdn = &m->views[4 * l + 3];
+        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, l == 0, b.X, l == 0 ? nullptr : b.Y, E, lp[l].attn_norm, b.xq, b.xd);
+        MI_CUDA(ctx, cudaGetLastError());
+        // Y rows are packed at the matrix's own row count by the GEMM: y[m * rows + r]
+        if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
+        vf_rope_kv<<<M, DNT, 0, ctx->stream>>>(P, l, pos0, b.qkv, (int)wqkv->rows);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, m->grid, M, l, pos0, wqkv->rows))) return st;
+        if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
+        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, lp[l].ffn_norm, b.xq, b.xd);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = mi_gemm_q4_q8(ctx, wgu, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.Y))) return st;
+        vf_swiglu_quant<<<dim3((FF / 32 + DNW - 1) / DNW, M), DNT, 0, ctx->stream>>>(b.Y, FF, b.act_q, b.act_d);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = mi_gemm_q4_q8(ctx, wdn, b.act_q, reinterpret_cast<const uint16_t*>(b.act_d), M, nullptr, b.Y))) return st;
+    }
+    vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, m->P.out_norm, b.xq, b.xd);
+    MI_CUDA(ctx, cudaGetLastError());
+    if ((st = mi_gemm_q4_q8(ctx, &m->views[4 * L], b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, logits))) return st;
+    vf_argmax<<<M, 1024, 0, ctx->stream>>>(logits, V, V, b.out);
+    MI_CUDA(ctx, cudaGetLastError());
+    MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    if (out_tokens_host) MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, b.out, (size_t)M * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    // the single-token loop continues from the last scored token's pick
+    MI_CUDA(ctx, cudaMemcpyAsync(m->P.cur_token, b.out + (M - 1), 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    st = mi_ctx_sync(ctx);
+    if (st != MI_OK) return st;
+    if (elapsed_ms) MI_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, m->ev0, m->ev1));
+    return MI_OK;
+}
+
+extern "C" int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* kcache_dev, const uint16_t* vcache_dev, int n_head,
+                               int n_head_kv, int head_dim, int pos0, int M, float* out_dev) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!q_dev || !kcache_dev || !vcache_dev || !out_dev) return set_error(ctx, MI_ERR_INVALID, "attention: null argument");
+    if (M < 1 || M > VMAX) return set_error(ctx, MI_ERR_LIMIT, "attention: M=%d queries per call; this entry point takes 1..%d", M, VMAX);
+    if (n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv || pos0 < 0) return set_error(ctx, MI_ERR_INVALID, "attention: bad head counts or position");
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int G = n_head / n_head_kv, grid = ctx->sm_count, max_chunks = std::max(1, grid / n_head_kv), NQ = n_head * head_dim;
+    // scratch: chunk partials as doubles, the q8_0 by-products of the decode path (unused here), arrival counters
+    const size_t part = (size_t)M * n_head * max_chunks * (head_dim + 2);
+    const size_t extra = ((size_t)M * NQ + (size_t)M * NQ / 32 * 2 + 7) / 8 + 1;        // in doubles
+    int st = ensure_scratch(ctx, part + extra, (size_t)M * n_head);
+    if (st != MI_OK) return st;
+    DecodeParams P{};
+    P.NH = n_head; P.NKV = n_head_kv; P.HD = head_dim; P.KVD = n_head_kv * head_dim;
+    P.qkv_out = const_cast<float*>(q_dev);
+    P.kc = reinterpret_cast<__half*>(const_cast<uint16_t*>(kcache_dev)); P.vc = reinterpret_cast<__half*>(const_cast<uint16_t*>(vcache_dev));
+    P.max_seq = 0;                        // one layer: the layer index never moves the base
+    P.max_chunks = max_chunks;
+    P.att = out_dev;
+    P.attn_part = ctx->part; P.attn_cnt = ctx->counters;
+    P.att_q = reinterpret_cast<int8_t*>(ctx->part + part);
+    P.att_d = reinterpret_cast<__half*>(reinterpret_cast<int8_t*>(ctx->part + part) + (size_t)M * NQ);
+    P.err = ctx->d_err;
+    return launch_attention<true>(ctx, P, head_dim, G, grid, M, 0, pos0, NQ);
+}
