@@ -402,6 +402,58 @@ def run_ours(args, rank, world, local_rank):
         }))
         return
 
+    if args.workload == "verify":
+        # M-token step on the 1.5B-shape model at cached contexts 512 / 8192 / 32768 (KV filled with N(0,1) fp16):
+        # one pass over the weights scores M drafted tokens; logits of a token must not depend on M
+        if rank == 0:
+            ensure_model()
+        barrier()
+        own = pkg.Context(local_rank)               # a stream of its own: the pass replays as a CUDA graph
+        contexts = (512, 8192, 32768)
+        model = pkg.Model(own, ensure_model(), contexts[-1] + 32)
+        cfg = model.config
+        g = torch.Generator(device="cuda"); g.manual_seed(11)
+        for name in ("kcache", "vcache"):
+            t = model.state_tensor(name).view(torch.float16)
+            for i in range(0, t.numel(), 1 << 28):
+                t[i:i + (1 << 28)].normal_(generator=g)
+        torch.cuda.synchronize()
+        ids = prompt_ids(cfg.n_vocab)[:16]
+        res, same = {}, True
+        logits = torch.zeros((16, cfg.n_vocab), dtype=torch.float32, device="cuda")
+        for c in contexts:
+            first = None
+            for M in (1, 2, 4, 8, 16):
+                for _ in range(warmup):
+                    model.verify(ids[:M], c)
+                times = [model.verify(ids[:M], c, logits)[1] for _ in range(max(3, min(args.steps, 20)))]
+                torch.cuda.synchronize()
+                row = logits[0].clone()             # token 0 at position c: the same work whatever M
+                first = row if first is None else first
+                same = same and bool(torch.equal(row.view(torch.int32), first.view(torch.int32)))
+                res[(c, M)] = sum(times) / len(times)
+        if rank != 0:
+            return
+        kvb = cfg.kv_bytes_per_position
+        head = res[(512, 8)]
+        byt = cfg.q4_weight_bytes_per_token + kvb * (512 + 8)
+        print(json.dumps({
+            "metric": "M-token verify step (tcgen05 GEMM projections + M-query split-KV attention): tokens/s at M=8, context 512",
+            "value": round(8 / (head * 1e-3), 1), "unit": "tok/s", "n_gpus": world, "steps": max(3, min(args.steps, 20)), "warmup": warmup,
+            "ms_per_step": round(head, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "uint4 x int8 -> int32 on tcgen05 (kind::i8); fp64-carried sums stored fp32; fp16 KV", "data": "synthetic",
+            "config": {"workload": "verify(config 3): Qwen2.5-1.5B shape, M in 1,2,4,8,16 drafted tokens per weight pass, KV cache N(0,1) fp16 at "
+                                   "512 / 8192 / 32768 cached positions", "l2": "868 MB of weights per pass, larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": round(byt / (head * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(byt / (head * 1e-3) / 1e9 / peak, 4), "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
+                         "traffic": None, "kernel": "whole pass (gemm_q4_q8_tc_kernel + vf_attention + glue)", "algorithmic_bytes_per_launch": byt},
+            "pass_ms": {f"ctx{c}_M{M}": round(v, 3) for (c, M), v in res.items()},
+            "tok_s": {f"ctx{c}_M{M}": round(M / (v * 1e-3), 1) for (c, M), v in res.items()},
+            "logits_identical_for_every_M": same,
+            "gpu_launches": (9 * cfg.n_layer + 3) * 15 * max(3, min(args.steps, 20)),
+        }))
+        return
+
     # ---------------- decode workload
     if rank == 0:
         ensure_model()
@@ -518,7 +570,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "verify"])
     ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per GEMV shape per GPU (MiB); small values are for profiler captures")
     ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the GEMV sweep (profiler captures)")
     args = ap.parse_args()

@@ -291,6 +291,12 @@ class Model:
     def run_phases(self, token, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_phases(self.ctx.h, self.h, token, pos, ph0, ph1), "mi_decode_phases")
 
+    def state_tensor(self, name):
+        """uint8 torch tensor aliasing a whole state buffer (no copy), e.g. to fill the KV cache for a benchmark."""
+        p, n = _vp(), _i64()
+        self.ctx.check(self.ctx.lib.mi_model_state_ptr(self.h, STATE[name], C.byref(p), C.byref(n)), "mi_model_state_ptr")
+        return _as_cuda_tensor(p.value, n.value)
+
     def state(self, name, dtype, count):
         """Copy of a state buffer as a numpy array."""
         import numpy as np

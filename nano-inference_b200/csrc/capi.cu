@@ -33,6 +33,7 @@ int ensure_scratch(mi_ctx* ctx, size_t part_count, size_t n_counters) {
         cudaError_t e = cudaMalloc(&ctx->counters, want * sizeof(unsigned));
         if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "scratch: cudaMalloc(%zu) failed: %s", want * sizeof(unsigned), cudaGetErrorString(e));
         MI_CUDA(ctx, cudaMemset(ctx->counters, 0, want * sizeof(unsigned)));
+        MI_CUDA(ctx, cudaStreamSynchronize(cudaStreamLegacy));          // the context's stream does not wait for the legacy stream
         ctx->n_counters = want;
     }
     return MI_OK;
@@ -131,6 +132,7 @@ extern "C" int mi_ctx_sync(mi_ctx* ctx) {
     MI_CUDA(ctx, cudaMemcpy(&err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (err != 0) {
         MI_CUDA(ctx, cudaMemset(ctx->d_err, 0, sizeof(int)));
+        MI_CUDA(ctx, cudaStreamSynchronize(cudaStreamLegacy));
         return set_error(ctx, err, "device reported: %s", mi_strerror(err));
     }
     return MI_OK;

@@ -27,6 +27,7 @@ struct Staging {       // one reusable device buffer for raw GGUF bytes
         // the previous repack (same stream) must be done with the buffer before it is overwritten
         MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         MI_CUDA(ctx, cudaMemcpy(d, src, n, cudaMemcpyHostToDevice));
+        MI_CUDA(ctx, cudaStreamSynchronize(cudaStreamLegacy));        // a pageable copy may return before its last DMA has landed
         return MI_OK;
     }
 };
@@ -95,6 +96,7 @@ extern "C" int mi_model_free(mi_ctx* ctx, mi_model* m) {
     cudaSetDevice(m->device);
     cudaDeviceSynchronize();
     for (void* p : m->allocs) cudaFree(p);
+    for (void* g : m->vb.graph) if (g) cudaGraphExecDestroy((cudaGraphExec_t)g);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     delete m;
@@ -362,6 +364,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         return set_error(ctx, MI_ERR_UNSUPPORTED, "model: decode kernel needs %zu bytes of shared memory, %d available", m->smem, ctx->smem_optin);
     MI_CUDA(ctx, cudaEventCreate(&m->ev0));
     MI_CUDA(ctx, cudaEventCreate(&m->ev1));
+    MI_CUDA(ctx, cudaDeviceSynchronize());           // every upload and fill of the load has landed, whatever stream it used
     guard.keep = true;
     *out = m;
     return MI_OK;

@@ -12,22 +12,32 @@
 // the very expression of the GEMV, so a token's result does not depend on how many tokens
 // share the pass (nor on the K-split: see blk_acc).
 //
-// Dataflow of a CTA (128 threads = 128 weight rows = four 32-row groups):
-//   raw tiles  : lane 0 bulk-copies the four groups' tiles of K-tile t into a 2-stage ring;
-//   unpack     : thread r splits its row's 16 nibble bytes of each block into low / high nibbles
-//                (elements 0..15 / 16..31) and writes them as the two 16-byte K-chunks of the
-//                canonical K-major core-matrix layout (8 rows x 16 bytes, no swizzle);
-//   MMA        : one thread issues one MMA per block of the tile, block k into TMEM columns
-//                [k*N, (k+1)*N), then commits to an mbarrier;
-//   drain      : thread r = TMEM lane r reads its row's N sums per block and accumulates.
-// Activations of the unit's K range wait in shared memory in the same canonical layout.
-// Every wait is bounded; TMEM is always released before the kernel returns.
+// Dataflow of a CTA (one per SM, six warps, 128 weight rows = four 32-row groups per unit):
+//   warp 5     : the loader.  One lane bulk-copies the four groups' raw tiles of K-tile after
+//                K-tile into a six-stage ring, across unit boundaries, as far ahead as the
+//                ring allows: the HBM stream never waits for the math.
+//   warps 0-3  : thread r = weight row r.  Unpack: split the row's 16 nibble bytes of each
+//                block into low / high nibbles (elements 0..15 / 16..31) and write them as the
+//                two 16-byte K-chunks of the canonical K-major core-matrix layout (8 rows x
+//                16 bytes, no swizzle) into one of two operand buffers.  Drain: thread r =
+//                TMEM lane r reads its row's N int32 sums per block (tcgen05.ld) and
+//                accumulates.  The drain of tile t-1 follows the unpack of tile t, so the
+//                tensor core works on t while the CUDA cores scale t-1.
+//   warp 4     : one lane issues one MMA per block of a tile, block k into TMEM columns
+//                [k*N, (k+1)*N) of one of two accumulator buffers, then commits to an mbarrier.
+// Hand-offs are mbarriers: ring slot full (bytes) / empty (128 rows), operand buffer full (128
+// rows), MMA done (commit) which also frees the operand buffer, accumulator buffer empty (128
+// rows).  Activations of the unit's K range wait in shared memory in the canonical layout.
+// Every wait is bounded; a wait that gives up raises an abort flag that ends all roles, the
+// copies in flight are waited for, and TMEM is always released before the kernel returns.
 #include "gemv_core.cuh"
 
 namespace mi {
 
-constexpr int TC_THREADS = 128;
+constexpr int TC_ROWS = 128;               // weight rows per unit = worker threads
+constexpr int TC_THREADS = 192;            // four worker warps, the MMA warp, the loader warp
 constexpr int TC_MAX_TILES = 8;            // K-tiles per unit (bounds the activation staging)
+constexpr int TC_STAGES = 6;               // raw-tile ring
 
 struct GemmParams {
     const uint8_t* base; long long mat_stride;
@@ -57,23 +67,51 @@ template <> __device__ __forceinline__ void tmem_ld_row<16>(uint32_t taddr, int 
                    "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) : "r"(taddr));
 }
 
+// Scale of one activation block as the drain wants it: the fp16 scale as a double and 8 * (sum of the int8s).
+// The drain evaluates blk_acc's expression  fma(double(dw*dx), double(float(isum) - float(8 sum x)), acc)  without its
+// conversions, which would bound the kernel (two per row, block and token on a pipe that retires 16 per clock and SM):
+// dw and dx are fp16 values, so their fp32 product is exact and equals double(dw) * double(dx); the bracket is an
+// exact small integer, converted by the 2^52 trick.  Same bits as blk_acc.
+struct XScale { double dx; int s8; int pad; };
+__device__ __forceinline__ double int_to_double_exact(int v) {      // |v| < 2^31
+    return __dsub_rn(__hiloint2double(0x43300000, (int)((unsigned)v ^ 0x80000000u)), 4503601774854144.0);   // 2^52 + 2^31
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }   // warps 0-3 only
+
 template <int KB, int N>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_q8_tc_kernel(const __grid_constant__ GemmParams p) {
     constexpr int TB = KB * kTileRowBytes;            // one raw tile
     constexpr int RAW_STAGE = 4 * TB;                 // four row groups
     constexpr int A_BLOCK = 128 * 32;                 // unpacked bytes of one block for 128 rows
-    constexpr int TMEM_COLS = KB * N < 32 ? 32 : KB * N;
+    constexpr int A_BUF = KB * A_BLOCK;
+    constexpr int ACC_COLS = KB * N;                  // TMEM columns of one accumulator buffer
+    constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;      // powers of two: KB, N are
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* raw = smem;                                             // [2][4][TB]
-    uint8_t* a_s = raw + 2 * RAW_STAGE;                              // [KB][2 K-chunks][16 cores][8 rows][16 B]
-    uint8_t* b_s = a_s + KB * A_BLOCK;                               // [blocks of the unit][2][N/8][8][16 B]
-    float2* xs_s = reinterpret_cast<float2*>(b_s + TC_MAX_TILES * KB * N * 32);   // [blocks][N] {dx, float(8*sum x)}
-    uint64_t* bars = reinterpret_cast<uint64_t*>(xs_s + TC_MAX_TILES * KB * N);    // raw[0], raw[1], mma
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
-    __shared__ int s_ok;
+    uint8_t* raw = smem;                                             // [TC_STAGES][4][TB]
+    uint8_t* a_s = raw + TC_STAGES * RAW_STAGE;                      // [2][KB][2 K-chunks][16 cores][8 rows][16 B]
+    uint8_t* b_s = a_s + 2 * A_BUF;                                  // [blocks of the unit][2][N/8][8][16 B]
+    XScale* xs_s = reinterpret_cast<XScale*>(b_s + TC_MAX_TILES * KB * N * 32);   // [blocks][N] {dx, 8*sum x}
+    uint64_t* bars = reinterpret_cast<uint64_t*>(xs_s + TC_MAX_TILES * KB * N);
+    uint64_t* raw_full = bars;                       // [TC_STAGES]
+    uint64_t* raw_empty = bars + TC_STAGES;          // [TC_STAGES]
+    uint64_t* a_full = bars + 2 * TC_STAGES;         // [2]
+    uint64_t* mma_done = a_full + 2;                 // [2]
+    uint64_t* acc_empty = mma_done + 2;              // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    __shared__ int s_abort;
+    __shared__ unsigned s_prev;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (tid == 0) { mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_init(&bars[2], 1); mbar_fence_init(); s_ok = 1; }
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; s++) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], TC_ROWS); }
+        for (int s = 0; s < 2; s++) { mbar_init(&a_full[s], TC_ROWS); mbar_init(&mma_done[s], 1); mbar_init(&acc_empty[s], TC_ROWS); }
+        mbar_fence_init();
+        s_abort = 0;
+    }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -82,148 +120,197 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_q4_q8_tc_kernel(const __gr
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint64_t policy = l2_policy_evict_first();
     // instruction descriptor: D = s32, A = unsigned 8-bit (raw nibbles 0..15), B = signed 8-bit, both K-major, N, M = 128
     constexpr uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
     const int sgroups = (p.groups + 3) / 4;
     const long long n_units = (long long)sgroups * p.ks;
-    int raw_issued = 0, raw_consumed = 0, mma_count = 0;
-    bool ok = true;
+    volatile int* abort_flag = &s_abort;
+    int loads_issued = 0;                                 // loader lane only
 
-    for (long long u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-        const int sg = (int)(u / p.ks), sp = (int)(u % p.ks);
-        const int t0 = sp * p.nt / p.ks, t1 = (sp + 1) * p.nt / p.ks, nblk = (t1 - t0) * KB, b0 = t0 * KB;
-        // the tile loader: four groups' tiles of K-tile t into stage s (a missing group re-reads the last one; its rows are never stored)
-        auto issue_tile = [&](int t) {
-            const int s = raw_issued & 1;
-            mbar_expect_tx(&bars[s], RAW_STAGE);
+    if (warp == 5) {
+        // ---------------- loader
+        if (lane == 0) {
+            const uint64_t policy = l2_policy_evict_first();
+            int it = 0;
+            for (long long u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+                const int sg = (int)(u / p.ks), sp = (int)(u % p.ks);
+                const int t0 = sp * p.nt / p.ks, t1 = (sp + 1) * p.nt / p.ks;
+                for (int t = t0; t < t1; t++, it++) {
+                    const int s = it % TC_STAGES;
+                    if (!mbar_wait_bounded(&raw_empty[s], ((it / TC_STAGES) & 1) ^ 1)) { *abort_flag = 1; break; }   // first round passes at once
+                    if (*abort_flag) break;
+                    mbar_expect_tx(&raw_full[s], RAW_STAGE);
+                    #pragma unroll
+                    for (int gi = 0; gi < 4; gi++) {                  // a missing group re-reads the last one; its rows are never stored
+                        const int g = min(sg * 4 + gi, p.groups - 1);
+                        bulk_g2s_hint(raw + s * RAW_STAGE + gi * TB, p.base + ((size_t)g * p.nt + t) * TB, TB, &raw_full[s], policy);
+                    }
+                    loads_issued = it + 1;
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------- MMA issuer
+        if (lane == 0) {
+            int it = 0;
+            for (long long u = blockIdx.x; u < n_units && !*abort_flag; u += gridDim.x) {
+                const int sp = (int)(u % p.ks);
+                const int t0 = sp * p.nt / p.ks, t1 = (sp + 1) * p.nt / p.ks;
+                for (int t = t0; t < t1; t++, it++) {
+                    const int b = it & 1, ph = (it >> 1) & 1;
+                    if (!mbar_wait_bounded(&acc_empty[b], ph ^ 1) || !mbar_wait_bounded(&a_full[b], ph)) { *abort_flag = 1; break; }
+                    if (*abort_flag) break;
+                    tc_fence_after();
+                    #pragma unroll
+                    for (int k = 0; k < KB; k++) {
+                        const uint64_t da = umma_smem_desc(smem_u32(a_s + b * A_BUF + k * A_BLOCK), 2048, 128);
+                        const uint64_t db = umma_smem_desc(smem_u32(b_s + (size_t)((t - t0) * KB + k) * (N * 32)), N * 16, 128);
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                            ::"r"(tmem_base + (uint32_t)(b * ACC_COLS + k * N)), "l"(da), "l"(db), "r"(idesc), "r"(0u), "r"(0u) : "memory");
+                    }
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&mma_done[b])) : "memory");
+                }
+            }
+        }
+    } else {
+        // ---------------- workers: thread tid = weight row tid of the unit = TMEM lane tid
+        int it = 0, staged_sp = -1;
+        bool ok = true;
+        for (long long u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+            const int sg = (int)(u / p.ks), sp = (int)(u % p.ks);
+            const int t0 = sp * p.nt / p.ks, t1 = (sp + 1) * p.nt / p.ks, nblk = (t1 - t0) * KB, b0 = t0 * KB;
+            // activations of the unit's K range: int8 into the canonical layout (tokens >= M are zero), scales next to them.
+            // Units of one CTA usually share the K range (always when K is unsplit): staged once.  Before a restage the
+            // previous unit's last drain is behind every worker, so nobody reads the old contents any more.  The loads of a
+            // round are all requested before the first store, one trip to L2 per round.
+            if (sp != staged_sp) {
+                workers_sync();
+                const int items = nblk * N;
+                for (int base = 0; base < items; base += 4 * TC_ROWS) {
+                    int4 xa[4], xc[4]; unsigned short xdv[4];
+                    #pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int i = base + r * TC_ROWS + tid, bl = i / N, n = i % N;
+                        xa[r] = make_int4(0, 0, 0, 0); xc[r] = xa[r]; xdv[r] = 0;
+                        if (i < items && n < p.M) {
+                            const int4* xp = reinterpret_cast<const int4*>(p.xq + ((size_t)n * p.nb + b0 + bl) * 32);
+                            xa[r] = __ldcg(xp); xc[r] = __ldcg(xp + 1);
+                            xdv[r] = __ldcg(reinterpret_cast<const unsigned short*>(p.xd) + (size_t)n * p.nb + b0 + bl);
+                        }
+                    }
+                    #pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        const int i = base + r * TC_ROWS + tid, bl = i / N, n = i % N;
+                        if (i < items) {
+                            uint8_t* dst = b_s + (size_t)bl * (N * 32) + (n >> 3) * 128 + (n & 7) * 16;
+                            *reinterpret_cast<int4*>(dst) = xa[r];
+                            *reinterpret_cast<int4*>(dst + N * 16) = xc[r];
+                            xs_s[i] = XScale{(double)__half2float(__ushort_as_half(xdv[r])), 8 * sum_x_block(xa[r], xc[r]), 0};
+                        }
+                    }
+                }
+                workers_sync();                               // the drains read scales staged by other rows
+                staged_sp = sp;
+            }
+            double acc[N];
             #pragma unroll
-            for (int gi = 0; gi < 4; gi++) {
-                const int g = min(sg * 4 + gi, p.groups - 1);
-                bulk_g2s_hint(raw + s * RAW_STAGE + gi * TB, p.base + ((size_t)g * p.nt + t) * TB, TB, &bars[s], policy);
-            }
-            raw_issued++;
-        };
-        if (tid == 0) { issue_tile(t0); if (t0 + 1 < t1) issue_tile(t0 + 1); }
-        // activations of the unit's K range: int8 into the canonical layout (tokens >= M are zero), scales next to them
-        for (int i = tid; i < nblk * N * 2; i += TC_THREADS) {
-            const int bl = i / (N * 2), rem = i % (N * 2), kc = rem / N, n = rem % N;
-            int4 v = make_int4(0, 0, 0, 0);
-            if (n < p.M) v = __ldcg(reinterpret_cast<const int4*>(p.xq + ((size_t)n * p.nb + b0 + bl) * 32 + kc * 16));
-            *reinterpret_cast<int4*>(b_s + (size_t)bl * (N * 32) + kc * (N * 16) + (n >> 3) * 128 + (n & 7) * 16) = v;
-        }
-        for (int i = tid; i < nblk * N; i += TC_THREADS) {
-            const int bl = i / N, n = i % N;
-            float2 v = make_float2(0.f, 0.f);
-            if (n < p.M) {
-                const int4* xp = reinterpret_cast<const int4*>(p.xq + ((size_t)n * p.nb + b0 + bl) * 32);
-                v = make_float2(__half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(p.xd) + (size_t)n * p.nb + b0 + bl))),
-                                __int2float_rn(8 * sum_x_block(__ldcg(xp), __ldcg(xp + 1))));
-            }
-            xs_s[bl * N + n] = v;
-        }
-        double acc[N];
-        #pragma unroll
-        for (int n = 0; n < N; n++) acc[n] = 0.0;
-
-        for (int t = t0; t < t1 && ok; t++) {
-            const int s = raw_consumed & 1;
-            if (!mbar_wait_bounded(&bars[s], (raw_consumed >> 1) & 1)) ok = false;
-            // unpack this thread's row: low nibbles = elements 0..15 (K-chunk 0), high nibbles = 16..31 (K-chunk 1)
-            const uint8_t* rt = raw + s * RAW_STAGE + warp * TB;
-            if (ok) {
+            for (int n = 0; n < N; n++) acc[n] = 0.0;
+            // drain of tile j (global index), the i-th tile of this unit
+            auto drain = [&](int j, int i) {
+                const int b = j & 1, s = j % TC_STAGES;
+                if (!mbar_wait_bounded(&mma_done[b], (j >> 1) & 1)) { ok = false; return; }
+                tc_fence_after();
+                const uint8_t* sc = raw + s * RAW_STAGE + warp * TB + KB * 512 + lane * (KB * 2);      // this row's KB fp16 scales
+                // four blocks' sums are requested together, then scaled
+                constexpr int KG = KB < 4 ? KB : 4;
+                #pragma unroll
+                for (int k0 = 0; k0 < KB; k0 += KG) {
+                    int isum[KG][N];
+                    #pragma unroll
+                    for (int k = 0; k < KG; k++)
+                        tmem_ld_row<N>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(b * ACC_COLS + (k0 + k) * N), isum[k]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    #pragma unroll
+                    for (int k = 0; k < KG; k++) {
+                        const double dwd = (double)__half2float(*reinterpret_cast<const __half*>(sc + (k0 + k) * 2));
+                        const XScale* xs = xs_s + (i * KB + k0 + k) * N;
+                        #pragma unroll
+                        for (int n = 0; n < N; n++) {
+                            const XScale s2 = xs[n];
+                            acc[n] = __fma_rn(__dmul_rn(dwd, s2.dx), int_to_double_exact(isum[k][n] - s2.s8), acc[n]);
+                        }
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(&acc_empty[b]);                   // the accumulator buffer may be overwritten
+                mbar_arrive(&raw_empty[s]);                   // and so may the ring slot (nibbles unpacked, scales used)
+            };
+            for (int t = t0; t < t1 && ok; t++, it++) {
+                const int s = it % TC_STAGES, b = it & 1;
+                if (*abort_flag || !mbar_wait_bounded(&raw_full[s], (it / TC_STAGES) & 1)) { ok = false; break; }
+                // operand buffer b is free: the MMAs of tile it-2 were waited for by its drain
+                const uint8_t* rt = raw + s * RAW_STAGE + warp * TB;
+                uint8_t* dst0 = a_s + b * A_BUF + (tid >> 3) * 128 + (tid & 7) * 16;
                 #pragma unroll
                 for (int k = 0; k < KB; k++) {
                     const uint4 w = *reinterpret_cast<const uint4*>(rt + (k * 32 + lane) * 16);
                     const unsigned Mk = 0x0F0F0F0Fu;
-                    uint8_t* dst = a_s + k * A_BLOCK + (tid >> 3) * 128 + (tid & 7) * 16;
+                    uint8_t* dst = dst0 + k * A_BLOCK;
                     *reinterpret_cast<uint4*>(dst) = make_uint4(w.x & Mk, w.y & Mk, w.z & Mk, w.w & Mk);
                     *reinterpret_cast<uint4*>(dst + 2048) = make_uint4((w.x >> 4) & Mk, (w.y >> 4) & Mk, (w.z >> 4) & Mk, (w.w >> 4) & Mk);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy writes -> visible to the tensor core's reads
+                mbar_arrive(&a_full[b]);
+                if (t > t0) drain(it - 1, t - 1 - t0);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic-proxy writes -> visible to the tensor core's reads
-            tc_fence_before();
-            ok = __syncthreads_and(ok ? 1 : 0) != 0;
+            if (ok) drain(it - 1, t1 - 1 - t0);
             if (!ok) break;
-            if (tid == 0) {
-                tc_fence_after();
+            // results of the unit: rows sg*128 + tid, tokens 0..M-1
+            const int row = sg * 128 + tid;
+            if (p.ks == 1) {
+                if (row < p.rows)
+                    for (int n = 0; n < p.M; n++) p.y[(size_t)n * p.rows + row] = __double2float_rn(acc[n]) + (p.bias ? p.bias[row] : 0.f);
+            } else {
+                double* part = p.part + ((size_t)sg * p.ks + sp) * N * 128;
                 #pragma unroll
-                for (int k = 0; k < KB; k++) {
-                    const uint64_t da = umma_smem_desc(smem_u32(a_s + k * A_BLOCK), 2048, 128);
-                    const uint64_t db = umma_smem_desc(smem_u32(b_s + (size_t)((t - t0) * KB + k) * (N * 32)), N * 16, 128);
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                        ::"r"(tmem_base + (uint32_t)(k * N)), "l"(da), "l"(db), "r"(idesc), "r"(0u), "r"(0u) : "memory");
-                }
-                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bars[2])) : "memory");
-            }
-            if (!mbar_wait_bounded(&bars[2], mma_count & 1)) ok = false;
-            mma_count++;
-            tc_fence_after();
-            if (ok) {
-                const uint8_t* sc = rt + KB * 512 + lane * (KB * 2);      // this row's KB fp16 scales
-                #pragma unroll
-                for (int k = 0; k < KB; k++) {
-                    int isum[N];
-                    tmem_ld_row<N>(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(k * N), isum);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    const float dw = __half2float(*reinterpret_cast<const __half*>(sc + k * 2));
-                    const float2* xs = xs_s + ((t - t0) * KB + k) * N;
-                    #pragma unroll
-                    for (int n = 0; n < N; n++) {
-                        const float2 s2 = xs[n];
-                        acc[n] = blk_acc(acc[n], dw, s2.x, isum[n], s2.y);
-                    }
-                }
-            }
-            raw_consumed++;
-            tc_fence_before();
-            ok = __syncthreads_and(ok ? 1 : 0) != 0;        // every row is done with the stage, the unpacked blocks and TMEM
-            if (ok && tid == 0 && t + 2 < t1) issue_tile(t + 2);
-        }
-        if (!ok) break;
-        // results of the unit: rows sg*128 + tid, tokens 0..M-1
-        const int row = sg * 128 + tid;
-        if (p.ks == 1) {
-            if (row < p.rows)
-                for (int n = 0; n < p.M; n++) p.y[(size_t)n * p.rows + row] = __double2float_rn(acc[n]) + (p.bias ? p.bias[row] : 0.f);
-        } else {
-            double* part = p.part + ((size_t)sg * p.ks + sp) * N * 128;
-            #pragma unroll
-            for (int n = 0; n < N; n++) __stcg(part + n * 128 + tid, acc[n]);
-            __threadfence();
-            __syncthreads();
-            __shared__ unsigned s_prev;
-            if (tid == 0) s_prev = atomicAdd(p.counters + sg, 1u);
-            __syncthreads();
-            if (s_prev == (unsigned)p.ks - 1) {                 // last split in: fold all of them in split order
+                for (int n = 0; n < N; n++) __stcg(part + n * 128 + tid, acc[n]);
                 __threadfence();
-                const double* p0 = p.part + (size_t)sg * p.ks * N * 128;
-                for (int n = 0; n < p.M; n++) {
-                    double s = 0.0;
-                    for (int q = 0; q < p.ks; q++) s = __dadd_rn(s, __ldcg(p0 + ((size_t)q * N + n) * 128 + tid));
-                    if (row < p.rows) p.y[(size_t)n * p.rows + row] = __double2float_rn(s) + (p.bias ? p.bias[row] : 0.f);
+                workers_sync();
+                if (tid == 0) s_prev = atomicAdd(p.counters + sg, 1u);
+                workers_sync();
+                if (s_prev == (unsigned)p.ks - 1) {                 // last split in: fold all of them in split order
+                    __threadfence();
+                    const double* p0 = p.part + (size_t)sg * p.ks * N * 128;
+                    for (int n = 0; n < p.M; n++) {
+                        double s = 0.0;
+                        for (int q = 0; q < p.ks; q++) s = __dadd_rn(s, __ldcg(p0 + ((size_t)q * N + n) * 128 + tid));
+                        if (row < p.rows) p.y[(size_t)n * p.rows + row] = __double2float_rn(s) + (p.bias ? p.bias[row] : 0.f);
+                    }
+                    if (tid == 0) p.counters[sg] = 0;
                 }
-                if (tid == 0) p.counters[sg] = 0;
             }
-            __syncthreads();
         }
-    }
-    if (!ok) {
-        if (tid == 0) atomicMax(p.err, MI_ERR_TIMEOUT);
-        for (int i = raw_consumed; i < raw_issued; i++) (void)mbar_wait_bounded(&bars[i & 1], (i >> 1) & 1);   // copies in flight target this CTA
+        if (!ok) *abort_flag = 1;
     }
     tc_fence_before();
     __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) atomicMax(p.err, MI_ERR_TIMEOUT);
+        if (warp == 5 && lane == 0)                            // copies in flight target this CTA: let them land
+            for (int j = max(0, loads_issued - TC_STAGES); j < loads_issued; j++) (void)mbar_wait_bounded(&raw_full[j % TC_STAGES], (j / TC_STAGES) & 1);
+        __syncthreads();
+    }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
 template <int KB, int N>
 static int launch_gemm(mi_ctx* ctx, const mi_weight* w, GemmParams p) {
     constexpr int TB = KB * kTileRowBytes;
-    const size_t smem = 2 * 4 * TB + (size_t)KB * 128 * 32 + (size_t)TC_MAX_TILES * KB * N * 32 + (size_t)TC_MAX_TILES * KB * N * 8 + 64;
+    const size_t smem = (size_t)TC_STAGES * 4 * TB + (size_t)2 * KB * 128 * 32 + (size_t)TC_MAX_TILES * KB * N * 32 +
+                        (size_t)TC_MAX_TILES * KB * N * sizeof(XScale) + (2 * TC_STAGES + 6) * 8 + 16;
     if (smem > (size_t)ctx->smem_optin) return set_error(ctx, MI_ERR_UNSUPPORTED, "gemm: %zu bytes of shared memory needed", smem);
     auto kern = gemm_q4_q8_tc_kernel<KB, N>;
     MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -237,7 +324,7 @@ static int launch_gemm(mi_ctx* ctx, const mi_weight* w, GemmParams p) {
         p.part = ctx->part; p.counters = ctx->counters;
     }
     long long ctas = (long long)sgroups * ks;
-    if (ctas > 2LL * ctx->sm_count) ctas = 2LL * ctx->sm_count;
+    if (ctas > ctx->sm_count) ctas = ctx->sm_count;                          // one CTA per SM walks its units; the ring runs ahead across them
     kern<<<(unsigned)ctas, TC_THREADS, smem, ctx->stream>>>(p);
     MI_CUDA(ctx, cudaGetLastError());
     return MI_OK;

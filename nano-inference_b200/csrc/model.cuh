@@ -16,6 +16,10 @@ struct VerifyBufs {
     int8_t* act_q = nullptr; __half* act_d = nullptr;   // [M][FF]
     float* logits = nullptr;           // [M][V]
     int* tokens = nullptr; int* out = nullptr;          // [M]
+    int* pos0 = nullptr;               // first position of the pass (device resident so that the launch sequence is position-free)
+    void* graph[17] = {};              // cudaGraphExec_t of the pass per M; scratch addresses they were built with
+    const void* graph_part = nullptr; const void* graph_cnt = nullptr;
+    bool warm[17] = {};
     double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
 };
 }
@@ -55,7 +59,13 @@ int dev_alloc(mi_ctx* ctx, mi_model* m, T** p, size_t n, bool zero = true) {
     cudaError_t e = cudaMalloc((void**)p, n * sizeof(T));
     if (e != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: cudaMalloc(%zu) failed: %s", n * sizeof(T), cudaGetErrorString(e));
     m->allocs.push_back(*p);
-    if (zero) { e = cudaMemset(*p, 0, n * sizeof(T)); if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "model: cudaMemset failed"); }
+    if (zero) {
+        // the fill runs on the legacy stream, which the context's own (non-blocking) stream does not wait for:
+        // finish it here, before anything enqueued later can write the buffer
+        e = cudaMemset(*p, 0, n * sizeof(T));
+        if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);
+        if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "model: cudaMemset failed");
+    }
     return MI_OK;
 }
 

@@ -16,6 +16,7 @@
 #include "model.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 using namespace mi;
 
@@ -65,8 +66,8 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
 }
 
 // RoPE on the packed (pair-adjacent) q and k rows of every token, fp16 K / V into the cache
-__global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, int pos0, float* qkv, int stride) {
-    const int m = blockIdx.x, pos = pos0 + m, HD = P.HD, nq = P.NH * HD;
+__global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, const int* pos0_dev, float* qkv, int stride) {
+    const int m = blockIdx.x, pos = __ldg(pos0_dev) + m, HD = P.HD, nq = P.NH * HD;
     float* v = qkv + (size_t)m * stride;
     for (int pr = threadIdx.x; pr < (nq + P.KVD) / 2; pr += blockDim.x) {
         const int p = 2 * pr, within = (p < nq ? p : p - nq) % HD, i = within >> 1;
@@ -86,7 +87,7 @@ __global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, i
 
 // attention of M queries: blockIdx.y = query; every query runs the decode kernel's attention over its own causal range
 template <int HD, int G, bool QNAT>
-__global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, int pos0, long long q_stride) {
+__global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, const int* pos0_dev, int pos0_val, long long q_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int m = blockIdx.y, nq = P.NH * HD;
     DecodeParams Q = P;
@@ -96,7 +97,7 @@ __global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ D
     Q.attn_cnt = P.attn_cnt + (size_t)m * P.NH;
     Q.prof = nullptr;
     unsigned long long tp = 0;
-    const int pos = pos0 + m;
+    const int pos = (pos0_dev ? __ldg(pos0_dev) : pos0_val) + m;
     if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G, false, QNAT>(Q, l, pos, smem, tp);
     else attention_phase<HD, G, G, false, QNAT>(Q, l, pos, smem, tp);
 }
@@ -138,15 +139,15 @@ size_t attn_smem_bytes(int HD, int G) {
 }
 
 template <bool QNAT>
-int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid, int M, int l, int pos0, long long q_stride) {
-    void (*kern)(DecodeParams, int, int, long long) = nullptr;
+int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid, int M, int l, const int* pos0_dev, int pos0, long long q_stride) {
+    void (*kern)(DecodeParams, int, const int*, int, long long) = nullptr;
     #define MI_PICK(hd, g) if (HD == hd && G == g) kern = vf_attention<hd, g, QNAT>;
     MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
     #undef MI_PICK
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "attention: head_dim %d with %d query heads per kv head is not instantiated", HD, G);
     const size_t smem = attn_smem_bytes(HD, G);
     MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<dim3(grid, M), DNT, smem, ctx->stream>>>(P, l, pos0, q_stride);
+    kern<<<dim3(grid, M), DNT, smem, ctx->stream>>>(P, l, pos0_dev, pos0, q_stride);
     MI_CUDA(ctx, cudaGetLastError());
     return MI_OK;
 }
@@ -164,11 +165,83 @@ int ensure_bufs(mi_ctx* ctx, mi_model* m) {
         (st = dev_alloc(ctx, m, &b.att_d, (size_t)M * NQ / 32)) ||
         (st = dev_alloc(ctx, m, &b.act_q, (size_t)M * FF)) || (st = dev_alloc(ctx, m, &b.act_d, (size_t)M * FF / 32)) ||
         (st = dev_alloc(ctx, m, &b.logits, (size_t)M * m->V)) ||
-        (st = dev_alloc(ctx, m, &b.tokens, (size_t)M)) || (st = dev_alloc(ctx, m, &b.out, (size_t)M)) ||
+        (st = dev_alloc(ctx, m, &b.tokens, (size_t)M + 1)) || (st = dev_alloc(ctx, m, &b.out, (size_t)M)) ||
         (st = dev_alloc(ctx, m, &b.attn_part, (size_t)M * m->NH * m->max_chunks * (m->HD + 2))) ||
         (st = dev_alloc(ctx, m, &b.attn_cnt, (size_t)M * m->NH)))
         return st;
+    b.pos0 = b.tokens + M;            // tokens and position travel in one copy
     b.cap = M;
+    return MI_OK;
+}
+
+}  // namespace
+
+namespace {
+
+// enqueue one pass over the tokens in b.tokens at the position in b.pos0 (both already on the device)
+int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
+    VerifyBufs& b = m->vb;
+    const int E = m->E, FF = m->FF, L = m->L, V = m->V;
+    DecodeParams P = m->P;
+    P.qkv_out = b.qkv; P.att = b.att; P.att_q = b.att_q; P.att_d = b.att_d; P.attn_part = b.attn_part; P.attn_cnt = b.attn_cnt;
+    P.prof = nullptr;
+    const std::vector<LayerPtrs>& lp = m->layer_ptrs;
+    const size_t nsm = (size_t)E * 4;
+    int st;
+    if (nsm > 48 * 1024) MI_CUDA(ctx, cudaFuncSetAttribute(vf_norm_quant, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nsm));
+    for (int l = 0; l < L; l++) {
+        const mi_weight *wqkv = &m->views[4 * l], *wo = &m->views[4 * l + 1], *wgu = &m->views[4 * l + 2], *wdn = &m->views[4 * l + 3];
+        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, l == 0, b.X, l == 0 ? nullptr : b.Y, E, lp[l].attn_norm, b.xq, b.xd);
+        MI_CUDA(ctx, cudaGetLastError());
+        // the GEMM packs its output at the matrix's own row count: y[m * rows + r]
+        if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
+        vf_rope_kv<<<M, DNT, 0, ctx->stream>>>(P, l, b.pos0, b.qkv, (int)wqkv->rows);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, m->grid, M, l, b.pos0, 0, wqkv->rows))) return st;
+        if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
+        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, lp[l].ffn_norm, b.xq, b.xd);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = mi_gemm_q4_q8(ctx, wgu, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.Y))) return st;
+        vf_swiglu_quant<<<dim3((FF / 32 + DNW - 1) / DNW, M), DNT, 0, ctx->stream>>>(b.Y, FF, b.act_q, b.act_d);
+        MI_CUDA(ctx, cudaGetLastError());
+        if ((st = mi_gemm_q4_q8(ctx, wdn, b.act_q, reinterpret_cast<const uint16_t*>(b.act_d), M, nullptr, b.Y))) return st;
+    }
+    vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, m->P.out_norm, b.xq, b.xd);
+    MI_CUDA(ctx, cudaGetLastError());
+    if ((st = mi_gemm_q4_q8(ctx, &m->views[4 * L], b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.logits))) return st;
+    vf_argmax<<<M, 1024, 0, ctx->stream>>>(b.logits, V, V, b.out);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
+// The pass as a CUDA graph per M: the launch sequence (about nine kernels per layer) is fixed
+// once tokens and position live on the device.  A graph is built on the second call with a
+// given M - the first one runs plainly and lets the GEMM grow its scratch - and rebuilt if
+// that scratch has moved since.  Streams that cannot capture (the legacy default stream) and
+// MINFER_VERIFY_GRAPH=0 run plainly.
+int run_pass(mi_ctx* ctx, mi_model* m, int M) {
+    VerifyBufs& b = m->vb;
+    static const bool use_graph = [] { const char* e = getenv("MINFER_VERIFY_GRAPH"); return !(e && atoi(e) == 0); }();
+    const bool capturable = ctx->stream != nullptr && ctx->stream != cudaStreamLegacy && ctx->stream != cudaStreamPerThread;
+    if (!use_graph || !capturable) return enqueue_pass(ctx, m, M);
+    if (b.graph[M] && (b.graph_part != (const void*)ctx->part || b.graph_cnt != (const void*)ctx->counters)) {
+        for (int i = 0; i <= VMAX; i++) if (b.graph[i]) { cudaGraphExecDestroy((cudaGraphExec_t)b.graph[i]); b.graph[i] = nullptr; }
+    }
+    if (!b.graph[M]) {
+        if (!b.warm[M]) { b.warm[M] = true; return enqueue_pass(ctx, m, M); }
+        cudaGraph_t g = nullptr;
+        MI_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        const int st = enqueue_pass(ctx, m, M);
+        const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+        if (st != MI_OK) { if (g) cudaGraphDestroy(g); return st; }
+        if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "verify: stream capture failed: %s", cudaGetErrorString(e));
+        cudaGraphExec_t ge = nullptr;
+        const cudaError_t e2 = cudaGraphInstantiate(&ge, g, 0);
+        cudaGraphDestroy(g);
+        if (e2 != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "verify: graph instantiation failed: %s", cudaGetErrorString(e2));
+        b.graph[M] = ge; b.graph_part = ctx->part; b.graph_cnt = ctx->counters;
+    }
+    MI_CUDA(ctx, cudaGraphLaunch((cudaGraphExec_t)b.graph[M], ctx->stream));
     return MI_OK;
 }
 
@@ -188,40 +261,14 @@ extern "C" int mi_verify(mi_ctx* ctx, mi_model* m, const int32_t* tokens_host, i
     int st;
     if ((st = ensure_bufs(ctx, m))) return st;
     VerifyBufs& b = m->vb;
-    const int E = m->E, FF = m->FF, L = m->L, NQ = m->NH * m->HD, qr = (m->qkv_rows + 31) / 32 * 32, V = m->V;
-    (void)qr; (void)NQ;
-    MI_CUDA(ctx, cudaMemcpyAsync(b.tokens, tokens_host, (size_t)M * 4, cudaMemcpyHostToDevice, ctx->stream));
-    DecodeParams P = m->P;
-    P.qkv_out = b.qkv; P.att = b.att; P.att_q = b.att_q; P.att_d = b.att_d; P.attn_part = b.attn_part; P.attn_cnt = b.attn_cnt;
-    P.prof = nullptr;
-    const std::vector<LayerPtrs>& lp = m->layer_ptrs;
-    float* logits = logits_dev ? logits_dev : b.logits;
-    const size_t nsm = (size_t)E * 4;
-    if (nsm > 48 * 1024) MI_CUDA(ctx, cudaFuncSetAttribute(vf_norm_quant, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nsm));
+    int32_t head[VMAX + 1] = {};
+    for (int i = 0; i < M; i++) head[i] = tokens_host[i];
+    head[VMAX] = pos0;
+    MI_CUDA(ctx, cudaMemcpyAsync(b.tokens, head, sizeof(head), cudaMemcpyHostToDevice, ctx->stream));   // pageable source: staged before the call returns
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
-    for (int l = 0; l < L; l++) {
-        const mi_weight *wqkv = &m->views[4 * l], *wo = &m->views[4 * l + 1], *wgu = &m->views[4 * l + 2], *wdn = &m->views[4 * l + 3];
-        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, l == 0, b.X, l == 0 ? nullptr : b.Y, E, lp[l].attn_norm, b.xq, b.xd);
-        MI_CUDA(ctx, cudaGetLastError());
-        // Y rows are packed at the matrix's own row count by the GEMM: y[m * rows + r]
-        if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
-        vf_rope_kv<<<M, DNT, 0, ctx->stream>>>(P, l, pos0, b.qkv, (int)wqkv->rows);
-        MI_CUDA(ctx, cudaGetLastError());
-        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, m->grid, M, l, pos0, wqkv->rows))) return st;
-        if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
-        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, lp[l].ffn_norm, b.xq, b.xd);
-        MI_CUDA(ctx, cudaGetLastError());
-        if ((st = mi_gemm_q4_q8(ctx, wgu, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.Y))) return st;
-        vf_swiglu_quant<<<dim3((FF / 32 + DNW - 1) / DNW, M), DNT, 0, ctx->stream>>>(b.Y, FF, b.act_q, b.act_d);
-        MI_CUDA(ctx, cudaGetLastError());
-        if ((st = mi_gemm_q4_q8(ctx, wdn, b.act_q, reinterpret_cast<const uint16_t*>(b.act_d), M, nullptr, b.Y))) return st;
-    }
-    vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, m->P.out_norm, b.xq, b.xd);
-    MI_CUDA(ctx, cudaGetLastError());
-    if ((st = mi_gemm_q4_q8(ctx, &m->views[4 * L], b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, logits))) return st;
-    vf_argmax<<<M, 1024, 0, ctx->stream>>>(logits, V, V, b.out);
-    MI_CUDA(ctx, cudaGetLastError());
+    if ((st = run_pass(ctx, m, M))) return st;
     MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    if (logits_dev) MI_CUDA(ctx, cudaMemcpyAsync(logits_dev, b.logits, (size_t)M * m->V * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     if (out_tokens_host) MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, b.out, (size_t)M * 4, cudaMemcpyDeviceToHost, ctx->stream));
     // the single-token loop continues from the last scored token's pick
     MI_CUDA(ctx, cudaMemcpyAsync(m->P.cur_token, b.out + (M - 1), 4, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -255,5 +302,5 @@ extern "C" int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* 
     P.att_q = reinterpret_cast<int8_t*>(ctx->part + part);
     P.att_d = reinterpret_cast<__half*>(reinterpret_cast<int8_t*>(ctx->part + part) + (size_t)M * NQ);
     P.err = ctx->d_err;
-    return launch_attention<true>(ctx, P, head_dim, G, grid, M, 0, pos0, NQ);
+    return launch_attention<true>(ctx, P, head_dim, G, grid, M, 0, nullptr, pos0, NQ);
 }

@@ -14,7 +14,9 @@
 // prompt; report top-1 agreement at every later position, as
 // src/cuda_infer.cu:1148-1160 / src/mega.cu:1192-1205), MAXSEQ=n (KV cache
 // positions; default prompt + n_gen + 8), WARMUP=n (untimed steps before the run),
-// PROFILE=1 (per-phase time on CTA 0, persistent engine), GPU=i (device index).
+// PROFILE=1 (per-phase time on CTA 0, persistent engine), GPU=i (device index),
+// TCHUNK=m (prompt / teacher-forced tokens per weight pass through the M-token step,
+// 1..16, default 16; 1 = one decode step per token; src/cuda_infer.cu:1130-1144).
 #pragma once
 #include <chrono>
 #include <cstdio>
@@ -41,6 +43,8 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
     std::vector<int32_t> ids;
     for (int i = 3; i < argc; i++) ids.push_back(atoi(argv[i]));
     const int teacher = env_int("TEACHER", 0);
+    int tchunk = env_int("TCHUNK", 16);
+    tchunk = tchunk < 1 ? 1 : tchunk > 16 ? 16 : tchunk;
     if (env_int("PROFILE", 0)) setenv("MINFER_PROFILE", "1", 1);
     if (!env_int("RAWIDS", 0)) fprintf(stderr, "minfer-%s: text output is outside this path; printing token ids (RAWIDS=1 form)\n", tag);
 
@@ -68,7 +72,16 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         float* logits = nullptr;
         if ((st = mi_device_malloc(ctx, (size_t)P * c.n_vocab * sizeof(float), (void**)&logits))) die(ctx, "mi_device_malloc", st);
         float ms = 0;
-        if ((st = mi_decode(ctx, model, ids.data(), P, P, 0, pred.data(), logits, mode, &ms))) die(ctx, "mi_decode", st);
+        if (tchunk == 1) {
+            if ((st = mi_decode(ctx, model, ids.data(), P, P, 0, pred.data(), logits, mode, &ms))) die(ctx, "mi_decode", st);
+        } else {
+            for (int i = 0; i < P; i += tchunk) {                // tchunk tokens per weight pass: same logits, bit for bit
+                const int mtok = P - i < tchunk ? P - i : tchunk;
+                float cms = 0;
+                if ((st = mi_verify(ctx, model, ids.data() + i, mtok, i, pred.data() + i, logits + (size_t)i * c.n_vocab, &cms))) die(ctx, "mi_verify", st);
+                ms += cms;
+            }
+        }
         int agree = 0, total = 0;
         for (int i = teacher - 1; i + 1 < P; i++, total++) {
             if (pred[i] == ids[i + 1]) { agree++; continue; }
@@ -86,13 +99,22 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         return 0;
     }
 
-    // prefill: one step per prompt token; the last one predicts generated token #1
+    // prefill: tchunk prompt tokens per weight pass (or one step per token); the last one predicts generated token #1
     std::vector<int32_t> out(P > 0 ? P : 1);
     float pms = 0;
     const auto t0 = std::chrono::steady_clock::now();
-    if ((st = mi_decode(ctx, model, ids.data(), P, P, 0, out.data(), nullptr, mode, &pms))) die(ctx, "mi_decode (prefill)", st);
+    if (tchunk == 1) {
+        if ((st = mi_decode(ctx, model, ids.data(), P, P, 0, out.data(), nullptr, mode, &pms))) die(ctx, "mi_decode (prefill)", st);
+    } else {
+        for (int i = 0; i < P; i += tchunk) {
+            const int mtok = P - i < tchunk ? P - i : tchunk;
+            float cms = 0;
+            if ((st = mi_verify(ctx, model, ids.data() + i, mtok, i, out.data() + i, nullptr, &cms))) die(ctx, "mi_verify (prefill)", st);
+            pms += cms;
+        }
+    }
     const double ttft = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    fprintf(stderr, "minfer-%s prefill: %d tok in %.1f ms (sequential)\n", tag, P, pms);
+    fprintf(stderr, "minfer-%s prefill: %d tok in %.1f ms (%d per pass)\n", tag, P, pms, tchunk);
     std::vector<int32_t> gen;
     int32_t next = out[P - 1];
     gen.push_back(next);

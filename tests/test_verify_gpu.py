@@ -139,3 +139,23 @@ def test_attn_splitkv_rejects_bad_arguments(ctx, pkg):
         ctx.attn_splitkv(t, t, t, 12, 2, 128, 0, 17, t)      # more queries than one call takes
     with pytest.raises(pkg.MinferError):
         ctx.attn_splitkv(t, t, t, 12, 4, 128, 0, 1, t)       # a (head_dim, group) pair that is not instantiated
+
+
+def test_graph_replay_matches_plain_launches(pkg, ctx, tiny):
+    """On a stream of its own the pass is captured into a CUDA graph on the second call with a given M and
+    replayed afterwards, with tokens and position read from device memory: same bits as the plain launches
+    (the shared `ctx` fixture runs on the legacy default stream, which cannot capture)."""
+    import torch
+    g = gu.GgufReader(tiny)
+    V = g.config()["n_vocab"]
+    n = 64
+    seq = [int(t) for t in np.random.default_rng(24).integers(0, V, n)]
+    plain = pkg.Model(ctx, tiny, n + 1)
+    want_tok, want = run_chunks(plain, seq, 8, V)
+    own = pkg.Context(0)                      # the library's own stream
+    m = pkg.Model(own, tiny, n + 1)
+    torch.cuda.synchronize()
+    got_tok, got = run_chunks(m, seq, 8, V)   # pass 1 plain, pass 2 builds the graph, passes 3.. replay it
+    assert got_tok == want_tok
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    plain.free(); m.free()
