@@ -17,8 +17,8 @@ struct VerifyBufs {
     float* logits = nullptr;           // [M][V]
     int* tokens = nullptr; int* out = nullptr;          // [M]
     int* pos0 = nullptr;               // first position of the pass (device resident so that the launch sequence is position-free)
-    void* graph[17] = {};              // cudaGraphExec_t of the pass per M; scratch addresses they were built with
-    const void* graph_part = nullptr; const void* graph_cnt = nullptr;
+    void* graph[17] = {};              // cudaGraphExec_t of the pass per M, and the scratch addresses each was built with
+    const void* graph_part[17] = {}; const void* graph_cnt[17] = {};
     bool warm[17] = {};
     double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
 };

@@ -224,8 +224,9 @@ int run_pass(mi_ctx* ctx, mi_model* m, int M) {
     static const bool use_graph = [] { const char* e = getenv("MINFER_VERIFY_GRAPH"); return !(e && atoi(e) == 0); }();
     const bool capturable = ctx->stream != nullptr && ctx->stream != cudaStreamLegacy && ctx->stream != cudaStreamPerThread;
     if (!use_graph || !capturable) return enqueue_pass(ctx, m, M);
-    if (b.graph[M] && (b.graph_part != (const void*)ctx->part || b.graph_cnt != (const void*)ctx->counters)) {
-        for (int i = 0; i <= VMAX; i++) if (b.graph[i]) { cudaGraphExecDestroy((cudaGraphExec_t)b.graph[i]); b.graph[i] = nullptr; }
+    if (b.graph[M] && (b.graph_part[M] != (const void*)ctx->part || b.graph_cnt[M] != (const void*)ctx->counters)) {
+        cudaGraphExecDestroy((cudaGraphExec_t)b.graph[M]);        // the GEMM scratch it points into has been reallocated since
+        b.graph[M] = nullptr;
     }
     if (!b.graph[M]) {
         if (!b.warm[M]) { b.warm[M] = true; return enqueue_pass(ctx, m, M); }
@@ -239,7 +240,7 @@ int run_pass(mi_ctx* ctx, mi_model* m, int M) {
         const cudaError_t e2 = cudaGraphInstantiate(&ge, g, 0);
         cudaGraphDestroy(g);
         if (e2 != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "verify: graph instantiation failed: %s", cudaGetErrorString(e2));
-        b.graph[M] = ge; b.graph_part = ctx->part; b.graph_cnt = ctx->counters;
+        b.graph[M] = ge; b.graph_part[M] = ctx->part; b.graph_cnt[M] = ctx->counters;
     }
     MI_CUDA(ctx, cudaGraphLaunch((cudaGraphExec_t)b.graph[M], ctx->stream));
     return MI_OK;

@@ -158,4 +158,17 @@ def test_graph_replay_matches_plain_launches(pkg, ctx, tiny):
     got_tok, got = run_chunks(m, seq, 8, V)   # pass 1 plain, pass 2 builds the graph, passes 3.. replay it
     assert got_tok == want_tok
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # a split-K GEMV on the same context makes the library grow (and move) the scratch the captured GEMMs point
+    # into: the next pass must notice and rebuild its graph instead of replaying the stale one
+    rows, cols = 2048, 4096
+    raw = ou.quantize_q4_0((np.random.default_rng(5).standard_normal((rows, cols)) * 0.02).astype(np.float32))
+    w = own.upload_q4_0(raw, rows, cols)
+    xq = torch.zeros(cols, dtype=torch.int8, device="cuda"); xd = torch.ones(cols // 32, dtype=torch.float16, device="cuda")
+    y = torch.zeros(rows, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    own.gemv_q4_q8(w, xq, xd, y, ksplit=8)
+    own.sync()
+    again_tok, again = run_chunks(m, seq, 8, V)
+    assert again_tok == want_tok
+    assert np.array_equal(again.view(np.uint32), want.view(np.uint32))
     plain.free(); m.free()
