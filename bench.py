@@ -402,6 +402,89 @@ def run_ours(args, rank, world, local_rank):
         }))
         return
 
+    if args.workload == "attn":
+        # stand-alone split-KV attention (mi_attn_splitkv) with the 1.5B head shape over one layer's fp16 cache
+        NH, NKV, HD = 12, 2, 128
+        g = torch.Generator(device="cuda"); g.manual_seed(5)
+        contexts = (512, 8192, 32768)
+        npos = contexts[-1] + 16
+        K = torch.randn((npos, NKV * HD), device="cuda", generator=g).to(torch.float16)
+        Vc = torch.randn((npos, NKV * HD), device="cuda", generator=g).to(torch.float16)
+        q = torch.randn((16, NH * HD), device="cuda", generator=g)
+        out = torch.empty((16, NH * HD), device="cuda")
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")          # larger than L2: written between timed calls
+        res = {}
+        for c in contexts:
+            for M in (1, 8):
+                ts = []
+                for i in range(warmup + args.steps):
+                    flush.fill_(i & 1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(); ctx.attn_splitkv(q, K.view(torch.int16), Vc.view(torch.int16), NH, NKV, HD, c - M, M, out); e1.record()
+                    torch.cuda.synchronize(); ctx.sync()
+                    if i >= warmup:
+                        ts.append(e0.elapsed_time(e1))
+                res[(c, M)] = sum(ts) / len(ts)
+        if rank != 0:
+            return
+        kv_bytes = {c: 2 * c * NKV * HD * 2 for c in contexts}
+        head = res[(32768, 1)]
+        ach = kv_bytes[32768] / (head * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "split-KV attention over an fp16 cache (one layer, 12 query / 2 kv heads, head_dim 128): GB/s of K+V at 32768 positions, M=1",
+            "value": round(ach, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": round(head, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 K/V, fp64-carried scores, weights and sums, fp32 out",
+            "data": "synthetic", "config": {"workload": "attn(config 3, attention part): contexts 512 / 8192 / 32768, M in 1, 8", "l2": "L2 flushed between timed calls"},
+            "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s", "frac": round(ach / peak, 4),
+                         "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None, "kernel": "vf_attention",
+                         "algorithmic_bytes_per_launch": kv_bytes[32768]},
+            "call_us": {f"ctx{c}_M{M}": round(v * 1e3, 1) for (c, M), v in res.items()},
+            "kv_gbs": {f"ctx{c}_M{M}": round(kv_bytes[c] / (v * 1e-3) / 1e9, 1) for (c, M), v in res.items()},
+            "gpu_launches": len(res) * (warmup + args.steps),
+        }))
+        return
+
+    if args.workload == "setup":
+        # load-time and per-token helper kernels: device-side repack of the lm_head matrix (131 MB of GGUF blocks) and the
+        # q8_0 quantizer on a vector far larger than L2 (HBM-bound form of the per-token kernel)
+        rows, cols = 151936, 1536
+        g = torch.Generator(device="cuda"); g.manual_seed(9)
+        n = rows * (cols // 32)
+        raw = torch.randint(0, 256, (n * 18,), dtype=torch.uint8, device="cuda", generator=g)
+        ts_r = []
+        for i in range(warmup + args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); w = ctx.repack_q4_0_dev(raw, rows, cols, 1); e1.record(); torch.cuda.synchronize(); ctx.sync()
+            w.free()
+            if i >= warmup:
+                ts_r.append(e0.elapsed_time(e1))
+        nel = 1 << 28                                                             # 1 GiB of fp32 in
+        x = torch.randn(nel, device="cuda", generator=g)
+        xq = torch.empty(nel, dtype=torch.int8, device="cuda"); xd = torch.empty(nel // 32, dtype=torch.float16, device="cuda")
+        ts_q = []
+        for i in range(warmup + args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); ctx.quant_q8(x, xq, xd, n=nel, M=1); e1.record(); torch.cuda.synchronize(); ctx.sync()
+            if i >= warmup:
+                ts_q.append(e0.elapsed_time(e1))
+        if rank != 0:
+            return
+        r_ms, q_ms = sum(ts_r) / len(ts_r), sum(ts_q) / len(ts_q)
+        r_bytes, q_bytes = 2 * n * 18, nel * 4 + nel + nel // 32 * 2
+        print(json.dumps({
+            "metric": "q8_0 activation quantizer: HBM GB/s (read fp32 + write int8 + fp16 scales) on 2^28 elements", "value": round(q_bytes / (q_ms * 1e-3) / 1e9, 1),
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": round(q_ms, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32 -> int8 + fp16", "data": "synthetic",
+            "config": {"workload": "setup: quant_q8_kernel on 2^28 elements; repack_q4_0_kernel on 151936x1536", "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": round(q_bytes / (q_ms * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(q_bytes / (q_ms * 1e-3) / 1e9 / peak, 4), "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})",
+                         "traffic": None, "kernel": "quant_q8_kernel", "algorithmic_bytes_per_launch": q_bytes},
+            "repack": {"ms": round(r_ms, 4), "gbs_read_plus_write": round(r_bytes / (r_ms * 1e-3) / 1e9, 1), "bytes": r_bytes,
+                       "note": "includes the allocation of the tiled buffer"},
+            "gpu_launches": 2 * (warmup + args.steps),
+        }))
+        return
+
     if args.workload == "verify":
         # M-token step on the 1.5B-shape model at cached contexts 512 / 8192 / 32768 (KV filled with N(0,1) fp16):
         # one pass over the weights scores M drafted tokens; logits of a token must not depend on M
@@ -570,12 +653,12 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "verify"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "verify", "attn", "setup"])
     ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per GEMV shape per GPU (MiB); small values are for profiler captures")
     ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the GEMV sweep (profiler captures)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 512 if args.workload == "decode" else 200 if args.workload == "gemv" else 50
+        args.steps = 512 if args.workload == "decode" else 200 if args.workload == "gemv" else 10 if args.workload in ("attn", "setup", "verify") else 50
     # torch.distributed.run pins OMP_NUM_THREADS to 1; the CPU baseline on rank 0 is meant to use every host thread
     if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)

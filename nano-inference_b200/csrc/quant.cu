@@ -1,28 +1,39 @@
-// q8_0 activation quantizer (per 32-element block), one warp per block.
+// q8_0 activation quantizer (per 32-element block): eight lanes per block, four elements per
+// lane (one 16-byte load, one 4-byte store), a warp handles four blocks per trip of a
+// grid-stride loop sized to the machine.
 #include "mi_internal.cuh"
 
 namespace mi {
 
 // a = max|x| over the block, inv = a > 0 ? 127/a : 0, xq = rint(x*inv) (round half to even),
 // xd = fp16(a/127): the arithmetic of the reference's quant_x_q8 (src/cuda_infer.cu:80-89).
-__global__ void quant_q8_kernel(const float* __restrict__ x, long long n_blocks, int8_t* __restrict__ xq,
-                                __half* __restrict__ xd) {
-    const long long blk = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (blk >= n_blocks) return;
-    const float v = x[blk * 32 + lane];
-    float a = fabsf(v);
-    #pragma unroll
-    for (int o = 16; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
-    xq[blk * 32 + lane] = (int8_t)__float2int_rn(__fmul_rn(v, inv));
-    if (lane == 0) xd[blk] = __float2half_rn(__fdiv_rn(a, 127.f));
+__global__ void __launch_bounds__(256) quant_q8_kernel(const float* __restrict__ x, long long n_blocks, int8_t* __restrict__ xq,
+                                                       __half* __restrict__ xd) {
+    const int lane = threadIdx.x & 31, sub = lane >> 3, li = lane & 7;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5), w0 = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    for (long long b4 = w0 * 4; b4 < n_blocks; b4 += warps * 4) {
+        const long long blk = b4 + sub;
+        const bool live = blk < n_blocks;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) v = __ldg(reinterpret_cast<const float4*>(x + blk * 32) + li);
+        float a = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        #pragma unroll
+        for (int o = 4; o; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+        const int q0 = __float2int_rn(__fmul_rn(v.x, inv)), q1 = __float2int_rn(__fmul_rn(v.y, inv));
+        const int q2 = __float2int_rn(__fmul_rn(v.z, inv)), q3 = __float2int_rn(__fmul_rn(v.w, inv));
+        if (live) {
+            reinterpret_cast<unsigned*>(xq + blk * 32)[li] = (unsigned)(q0 & 255) | ((unsigned)(q1 & 255) << 8) | ((unsigned)(q2 & 255) << 16) | ((unsigned)(q3 & 255) << 24);
+            if (li == 0) xd[blk] = __float2half_rn(__fdiv_rn(a, 127.f));
+        }
+    }
 }
 
 int launch_quant_q8(mi_ctx* ctx, const float* x, long long n_blocks, int8_t* xq, __half* xd) {
     if (n_blocks == 0) return MI_OK;
-    const int wpb = 8;
-    quant_q8_kernel<<<(unsigned)((n_blocks + wpb - 1) / wpb), wpb * 32, 0, ctx->stream>>>(x, n_blocks, xq, xd);
+    const long long want = (n_blocks + 31) / 32;                       // CTAs if every warp made one trip
+    const long long cap = (long long)ctx->sm_count * 8;                 // full occupancy; larger inputs loop
+    quant_q8_kernel<<<(unsigned)(want < cap ? want : cap), 256, 0, ctx->stream>>>(x, n_blocks, xq, xd);
     MI_CUDA(ctx, cudaGetLastError());
     return MI_OK;
 }
