@@ -124,6 +124,7 @@ __global__ void __launch_bounds__(tc_threads(N), 1) gemm_q4_q8_tc_kernel(const _
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();          // the next kernel in the stream may become resident; it waits for this grid to finish
     // instruction descriptor: D = s32, A = unsigned 8-bit (raw nibbles 0..15), B = signed 8-bit, both K-major, N, M = 128
     constexpr uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(tc_threads(N), 1) gemm_q4_q8_tc_kernel(const _
     } else {
         // ---------------- workers: group g, thread rt = weight row rt of the unit = TMEM lane rt
         const int g = warp >> 2, wq = warp & 3, rt = tid - g * TC_ROWS;
+        pdl_wait_prior();             // activations come from the previous kernel; the loader's weight tiles do not
         // activations of the CTA's K range: int8 into the canonical layout (tokens >= M are zero), scales next to them;
         // the loads of a round are all requested before the first store, one trip to L2 per round
         {
@@ -340,8 +342,7 @@ static int launch_gemm(mi_ctx* ctx, const mi_weight* w, GemmParams p) {
     long long ctas = (long long)sgroups * ks;
     if (ctas > ctx->sm_count) ctas = (long long)(ctx->sm_count / ks) * ks;
     if (ctas < ks) return set_error(ctx, MI_ERR_UNSUPPORTED, "gemm: K-split %d exceeds the SM count", ks);
-    kern<<<(unsigned)ctas, tc_threads(N), smem, ctx->stream>>>(p);
-    MI_CUDA(ctx, cudaGetLastError());
+    MI_CUDA(ctx, launch_k(ctx->pdl, kern, dim3((unsigned)ctas), dim3(tc_threads(N)), smem, ctx->stream, p));
     return MI_OK;
 }
 

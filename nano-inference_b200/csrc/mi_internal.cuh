@@ -20,6 +20,7 @@ struct mi_ctx {
     double* part = nullptr; size_t part_count = 0;
     unsigned* counters = nullptr; size_t n_counters = 0;
     // staging for the host-buffer convenience calls
+    bool pdl = false;                // launches may start before their predecessor in the stream has finished (see launch_k)
     void* h_pinned = nullptr; size_t h_pinned_bytes = 0;
     void* d_stage = nullptr; size_t d_stage_bytes = 0;
     std::string last_error;
@@ -51,6 +52,20 @@ int ensure_scratch(mi_ctx* ctx, size_t part_count, size_t n_counters);
 int ensure_staging(mi_ctx* ctx, size_t host_bytes, size_t dev_bytes);
 int launch_repack_map(mi_ctx* ctx, const void* raw_dev, long long src_rows, int nb, int kb, uint8_t* tiled,
                       const int* dst_row_dev, int row_offset);
+
+// Kernel launch, optionally with programmatic stream serialization: the kernel may become resident while its
+// predecessor in the stream still runs; it must execute griddepcontrol.wait (pdl_wait_prior) before it reads what the
+// predecessor wrote or writes anything the predecessor may read.  Used for the launch sequence of the M-token pass.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 #define MI_CUDA(ctx, call)                                                                    \
     do {                                                                                      \

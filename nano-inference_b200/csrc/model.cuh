@@ -21,6 +21,7 @@ struct VerifyBufs {
     const void* graph_part[17] = {}; const void* graph_cnt[17] = {};
     bool warm[17] = {};
     double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
+    unsigned long long* amax_key = nullptr; unsigned* amax_cnt = nullptr;   // [M] argmax scratch, self-clearing
 };
 }
 

@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
                                                       int ystride, const float* __restrict__ w, int8_t* xq, __half* xd) {
     extern __shared__ float xs[];
     __shared__ double red[DNW];
+    pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, E = P.E, nb = E / 32;
     const int token = embed ? __ldg(tokens + m) : 0;
     double ss = 0.0;
@@ -67,6 +68,7 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
 
 // RoPE on the packed (pair-adjacent) q and k rows of every token, fp16 K / V into the cache
 __global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, const int* pos0_dev, float* qkv, int stride) {
+    pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.x, pos = __ldg(pos0_dev) + m, HD = P.HD, nq = P.NH * HD;
     float* v = qkv + (size_t)m * stride;
     for (int pr = threadIdx.x; pr < (nq + P.KVD) / 2; pr += blockDim.x) {
@@ -89,6 +91,7 @@ __global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, c
 template <int HD, int G, bool QNAT>
 __global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, const int* pos0_dev, int pos0_val, long long q_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
+    pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.y, nq = P.NH * HD;
     DecodeParams Q = P;
     Q.qkv_out = P.qkv_out + (size_t)m * q_stride;
@@ -104,6 +107,7 @@ __global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ D
 
 // SwiGLU of the interleaved gate / up groups -> q8_0; one warp per 32-element block
 __global__ void __launch_bounds__(DNT) vf_swiglu_quant(const float* Y, int FF, int8_t* act_q, __half* act_d) {
+    pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.y, g = blockIdx.x * DNW + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (g >= FF / 32) return;
     const float* y = Y + (size_t)m * 2 * FF + (size_t)g * 64;
@@ -112,12 +116,18 @@ __global__ void __launch_bounds__(DNT) vf_swiglu_quant(const float* Y, int FF, i
     act_q[(size_t)m * FF + g * 32 + lane] = (int8_t)quant_block_warp(a, lane, nullptr, act_d + (size_t)m * (FF / 32) + g);
 }
 
-// greedy pick per token, lowest index on ties (src/cpu_infer.cpp:153-154)
-__global__ void __launch_bounds__(1024) vf_argmax(const float* logits, long long stride, int V, int* out) {
-    __shared__ float bv[32]; __shared__ int bi[32];
-    const float* lg = logits + (size_t)blockIdx.x * stride;
+// greedy pick per token, lowest index on ties (src/cpu_infer.cpp:153-154).  grid = (slices, tokens): every CTA
+// reduces its slice of the row and folds {order-preserving value bits, ~index} into a 64-bit maximum; the last CTA of
+// a token to arrive writes the index and clears the scratch for the next pass.
+constexpr int kArgmaxSlices = 32;
+__global__ void __launch_bounds__(512) vf_argmax(const float* logits, long long stride, int V, int* out, unsigned long long* key, unsigned* cnt) {
+    __shared__ float bv[16]; __shared__ int bi[16];
+    pdl_launch_dependents(); pdl_wait_prior();
+    const int m = blockIdx.y;
+    const float* lg = logits + (size_t)m * stride;
+    const int per = (V + gridDim.x - 1) / gridDim.x, r0 = blockIdx.x * per, r1 = min(V, r0 + per);
     float best = -INFINITY; int idx = 0x7fffffff;
-    for (int r = threadIdx.x; r < V; r += blockDim.x) {
+    for (int r = r0 + threadIdx.x; r < r1; r += blockDim.x) {
         const float v = lg[r];
         if (v > best || (v == best && r < idx)) { best = v; idx = r; }
     }
@@ -130,7 +140,17 @@ __global__ void __launch_bounds__(1024) vf_argmax(const float* logits, long long
     __syncthreads();
     if (threadIdx.x == 0) {
         for (int w = 1; w < (int)(blockDim.x >> 5); w++) if (bv[w] > bv[0] || (bv[w] == bv[0] && bi[w] < bi[0])) { bv[0] = bv[w]; bi[0] = bi[w]; }
-        out[blockIdx.x] = bi[0];
+        if (bi[0] != 0x7fffffff) {
+            const unsigned fb = __float_as_uint(bv[0]), ord = (fb & 0x80000000u) ? ~fb : (fb | 0x80000000u);
+            atomicMax(key + m, ((unsigned long long)ord << 32) | (unsigned)(0xFFFFFFFFu - (unsigned)bi[0]));
+        }
+        __threadfence();
+        if (atomicAdd(cnt + m, 1u) == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long k = atomicExch(key + m, 0ull);
+            out[m] = (int)(0xFFFFFFFFu - (unsigned)(k & 0xFFFFFFFFull));
+            cnt[m] = 0;
+        }
     }
 }
 
@@ -147,8 +167,7 @@ int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "attention: head_dim %d with %d query heads per kv head is not instantiated", HD, G);
     const size_t smem = attn_smem_bytes(HD, G);
     MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<dim3(grid, M), DNT, smem, ctx->stream>>>(P, l, pos0_dev, pos0, q_stride);
-    MI_CUDA(ctx, cudaGetLastError());
+    MI_CUDA(ctx, launch_k(ctx->pdl, kern, dim3(grid, M), dim3(DNT), smem, ctx->stream, P, l, pos0_dev, pos0, q_stride));
     return MI_OK;
 }
 
@@ -167,7 +186,8 @@ int ensure_bufs(mi_ctx* ctx, mi_model* m) {
         (st = dev_alloc(ctx, m, &b.logits, (size_t)M * m->V)) ||
         (st = dev_alloc(ctx, m, &b.tokens, (size_t)M + 1)) || (st = dev_alloc(ctx, m, &b.out, (size_t)M)) ||
         (st = dev_alloc(ctx, m, &b.attn_part, (size_t)M * m->NH * m->max_chunks * (m->HD + 2))) ||
-        (st = dev_alloc(ctx, m, &b.attn_cnt, (size_t)M * m->NH)))
+        (st = dev_alloc(ctx, m, &b.attn_cnt, (size_t)M * m->NH)) ||
+        (st = dev_alloc(ctx, m, &b.amax_key, (size_t)M)) || (st = dev_alloc(ctx, m, &b.amax_cnt, (size_t)M)))
         return st;
     b.pos0 = b.tokens + M;            // tokens and position travel in one copy
     b.cap = M;
@@ -188,29 +208,33 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
     const std::vector<LayerPtrs>& lp = m->layer_ptrs;
     const size_t nsm = (size_t)E * 4;
     int st;
+    // every launch of the pass may overlap its predecessor's tail (each kernel waits before touching shared data);
+    // MINFER_VERIFY_PDL=0 restores plain stream order
+    static const bool use_pdl = [] { const char* e = getenv("MINFER_VERIFY_PDL"); return !(e && atoi(e) == 0); }();
+    const bool pdl = use_pdl;
+    struct PdlScope { mi_ctx* c; bool old; ~PdlScope() { c->pdl = old; } } scope{ctx, ctx->pdl};
+    ctx->pdl = pdl;
     if (nsm > 48 * 1024) MI_CUDA(ctx, cudaFuncSetAttribute(vf_norm_quant, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)nsm));
     for (int l = 0; l < L; l++) {
         const mi_weight *wqkv = &m->views[4 * l], *wo = &m->views[4 * l + 1], *wgu = &m->views[4 * l + 2], *wdn = &m->views[4 * l + 3];
-        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, l == 0, b.X, l == 0 ? nullptr : b.Y, E, lp[l].attn_norm, b.xq, b.xd);
-        MI_CUDA(ctx, cudaGetLastError());
+        MI_CUDA(ctx, launch_k(pdl, vf_norm_quant, dim3(M), dim3(DNT), nsm, ctx->stream, P, (const int*)b.tokens, l == 0, b.X,
+                              (const float*)(l == 0 ? nullptr : b.Y), E, lp[l].attn_norm, b.xq, b.xd));
         // the GEMM packs its output at the matrix's own row count: y[m * rows + r]
         if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
-        vf_rope_kv<<<M, DNT, 0, ctx->stream>>>(P, l, b.pos0, b.qkv, (int)wqkv->rows);
-        MI_CUDA(ctx, cudaGetLastError());
+        MI_CUDA(ctx, launch_k(pdl, vf_rope_kv, dim3(M), dim3(DNT), 0, ctx->stream, P, l, (const int*)b.pos0, b.qkv, (int)wqkv->rows));
         if ((st = launch_attention<false>(ctx, P, m->HD, m->G, m->grid, M, l, b.pos0, 0, wqkv->rows))) return st;
         if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
-        vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, lp[l].ffn_norm, b.xq, b.xd);
-        MI_CUDA(ctx, cudaGetLastError());
+        MI_CUDA(ctx, launch_k(pdl, vf_norm_quant, dim3(M), dim3(DNT), nsm, ctx->stream, P, (const int*)b.tokens, false, b.X, (const float*)b.Y, E,
+                              lp[l].ffn_norm, b.xq, b.xd));
         if ((st = mi_gemm_q4_q8(ctx, wgu, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.Y))) return st;
-        vf_swiglu_quant<<<dim3((FF / 32 + DNW - 1) / DNW, M), DNT, 0, ctx->stream>>>(b.Y, FF, b.act_q, b.act_d);
-        MI_CUDA(ctx, cudaGetLastError());
+        MI_CUDA(ctx, launch_k(pdl, vf_swiglu_quant, dim3((FF / 32 + DNW - 1) / DNW, M), dim3(DNT), 0, ctx->stream, (const float*)b.Y, FF, b.act_q, b.act_d));
         if ((st = mi_gemm_q4_q8(ctx, wdn, b.act_q, reinterpret_cast<const uint16_t*>(b.act_d), M, nullptr, b.Y))) return st;
     }
-    vf_norm_quant<<<M, DNT, nsm, ctx->stream>>>(P, b.tokens, false, b.X, b.Y, E, m->P.out_norm, b.xq, b.xd);
-    MI_CUDA(ctx, cudaGetLastError());
+    MI_CUDA(ctx, launch_k(pdl, vf_norm_quant, dim3(M), dim3(DNT), nsm, ctx->stream, P, (const int*)b.tokens, false, b.X, (const float*)b.Y, E,
+                          m->P.out_norm, b.xq, b.xd));
     if ((st = mi_gemm_q4_q8(ctx, &m->views[4 * L], b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.logits))) return st;
-    vf_argmax<<<M, 1024, 0, ctx->stream>>>(b.logits, V, V, b.out);
-    MI_CUDA(ctx, cudaGetLastError());
+    MI_CUDA(ctx, launch_k(pdl, vf_argmax, dim3(kArgmaxSlices, M), dim3(512), 0, ctx->stream, (const float*)b.logits, (long long)V, V, b.out,
+                          b.amax_key, b.amax_cnt));
     return MI_OK;
 }
 
