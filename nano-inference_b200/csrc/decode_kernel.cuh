@@ -786,64 +786,67 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         prof_mark(P, tp, kProfStep);
         for (int ph = ph0; ph < ph1 && ok; ph++) {
             const int l = ph / 5, k = ph == nph - 1 ? 5 : ph % 5;
-            if (k == 0) {
-                // ---- QKV: h_in = (l == 0) ? embedding : h_mid + down-projection partials of layer l-1
-                if (l == 0) {
-                    const int tok = step < P.n_forced ? __ldg(P.in_tokens + step) : __ldcg(P.cur_token);
-                    stage_norm_q8(P, nullptr, tok, nullptr, 0, P.h_in, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
-                } else {
+            // One call site each for the norm prologue, the copy prologue and the CTA job: the four per-layer GEMV
+            // phases run the same instructions (they stay in the instruction cache from phase to phase) and differ
+            // only in pointers and in the few lines of their epilogue.
+            if (k == 0 || k == 3 || k == 5) {
+                // QKV : h_in  = (l == 0) ? embedding : h_mid + down-projection partials of layer l-1
+                // GU  : h_mid = h_in + O-projection partials
+                // LM  : final norm over h_mid + last down-projection partials
+                const float* src = nullptr; const double* part = nullptr; float* commit = nullptr; const float* nw = nullptr;
+                int tok = 0, pks = 0;
+                if (k == 0 && l == 0) {
+                    tok = step < P.n_forced ? __ldg(P.in_tokens + step) : __ldcg(P.cur_token);
+                    commit = P.h_in; nw = sm.lp[0].attn_norm;
+                } else if (k == 0) {
                     const Job& dj = sm.jobs[4 * (l - 1) + 3];
-                    stage_norm_q8(P, P.h_mid, 0, P.part + dj.part_off, dj.ks, P.h_in, sm.lp[l].attn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
+                    src = P.h_mid; part = P.part + dj.part_off; pks = dj.ks; commit = P.h_in; nw = sm.lp[l].attn_norm;
+                } else if (k == 3) {
+                    const Job& oj = sm.jobs[4 * l + 1];
+                    src = P.h_in; part = P.part + oj.part_off; pks = oj.ks; commit = P.h_mid; nw = sm.lp[l].ffn_norm;
+                } else {
+                    const Job& dj = sm.jobs[4 * (P.L - 1) + 3];
+                    src = P.h_mid; part = P.part + dj.part_off; pks = dj.ks; nw = P.out_norm;
                 }
-                prof_mark(P, tp, 0);
-                const float* bias = sm.lp[l].bqkv;
-                const int nq = P.NH * HD;
-                ok = run_cta_job(ws, P, sm, 4 * l + 0, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
-                    const int p = g * 32 + ln;
-                    const float v = __fadd_rn(v0, __ldg(bias + p));
-                    const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
-                    float out = v;
-                    if (p < nq + P.KVD) {                                  // q or k: rotate the (even, odd) lane pair
-                        const int within = (p < nq ? p : p - nq) % HD, i = within >> 1;
-                        const double c = sm.cs[i], s = sm.cs[HD / 2 + i];    // products are exact in double: one rounding each
-                        if ((within & 1) == 0) out = __double2float_rn(__dsub_rn(__dmul_rn((double)v, c), __dmul_rn((double)partner, s)));
-                        else out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c)));
-                    }
-                    if (p < nq + 2 * P.KVD) __stcg(P.qkv_out + p, out);
-                });
-            } else if (k == 1) {
+                stage_norm_q8(P, src, tok, part, pks, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s);
+                prof_mark(P, tp, 2 * k);
+            } else if (k == 2 || k == 4) {
+                if (k == 2) stage_copy_q8(P.att_q, P.att_d, P.E / 32, xq_s, xs_s);
+                else stage_copy_q8(P.act_q, P.act_d, P.FF / 32, xq_s, xs_s);
+                prof_mark(P, tp, 2 * k);
+            }
+            if (k == 1) {
                 if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G>(P, l, pos, sm.stage, tp);
                 else attention_phase<HD, G, G>(P, l, pos, sm.stage, tp);
-            } else if (k == 2) {
-                stage_copy_q8(P.att_q, P.att_d, P.E / 32, xq_s, xs_s);
-                prof_mark(P, tp, 4);
-                ok = run_cta_job(ws, P, sm, 4 * l + 1, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
-                    // unsplit: the "partial" is the whole sum; keep one path for the consumer
-                    __stcg(P.part + sm.jobs[4 * l + 1].part_off + (size_t)g * 32 + ln, (double)v0);
-                });
-            } else if (k == 3) {
-                // ---- gate/up: h_mid = h_in + O-projection partials
-                const Job& oj = sm.jobs[4 * l + 1];
-                stage_norm_q8(P, P.h_in, 0, P.part + oj.part_off, oj.ks, P.h_mid, sm.lp[l].ffn_norm, P.E, P.eps, sm.red, xq_s, xs_s);
-                prof_mark(P, tp, 6);
-                ok = run_cta_job(ws, P, sm, 4 * l + 2, lane, xq_s, xs_s, tp, [&](int g, int ln, float gate, float up) {
-                    const double gd = (double)gate;
-                    const float a = __double2float_rn(__dmul_rn(__ddiv_rn(gd, __dadd_rn(1.0, exp(-gd))), (double)up));
-                    const int r = g * 32 + ln;                            // FF is a multiple of 32: whole q8_0 block per warp
-                    const int qv = quant_block_warp(a, ln, nullptr, P.act_d + g);
-                    P.act_q[r] = (int8_t)qv;
-                });
-            } else if (k == 4) {
-                stage_copy_q8(P.act_q, P.act_d, P.FF / 32, xq_s, xs_s);
-                prof_mark(P, tp, 8);
-                ok = run_cta_job(ws, P, sm, 4 * l + 3, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float) {
-                    __stcg(P.part + sm.jobs[4 * l + 3].part_off + (size_t)g * 32 + ln, (double)v0);
+            } else if (k != 5) {
+                const int jn = 4 * l + (k == 0 ? 0 : k == 2 ? 1 : k == 3 ? 2 : 3);
+                const float* bias = sm.lp[l].bqkv;
+                const int nq = P.NH * HD, part_off = sm.jobs[jn].part_off;
+                ok = run_cta_job(ws, P, sm, jn, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float v1) {
+                    if (k == 0) {                                            // + bias, RoPE, packed q / k / v
+                        const int p = g * 32 + ln;
+                        const float v = __fadd_rn(v0, __ldg(bias + p));
+                        const float partner = __shfl_xor_sync(0xffffffffu, v, 1);
+                        float out = v;
+                        if (p < nq + P.KVD) {                                  // q or k: rotate the (even, odd) lane pair
+                            const int within = (p < nq ? p : p - nq) % HD, i = within >> 1;
+                            const double c = sm.cs[i], s = sm.cs[HD / 2 + i];    // products are exact in double: one rounding each
+                            if ((within & 1) == 0) out = __double2float_rn(__dsub_rn(__dmul_rn((double)v, c), __dmul_rn((double)partner, s)));
+                            else out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c)));
+                        }
+                        if (p < nq + 2 * P.KVD) __stcg(P.qkv_out + p, out);
+                    } else if (k == 3) {                                     // SwiGLU of (gate, up), one q8_0 block per warp
+                        const double gd = (double)v0;
+                        const float a = __double2float_rn(__dmul_rn(__ddiv_rn(gd, __dadd_rn(1.0, exp(-gd))), (double)v1));
+                        const int r = g * 32 + ln;                            // FF is a multiple of 32
+                        const int qv = quant_block_warp(a, ln, nullptr, P.act_d + g);
+                        P.act_q[r] = (int8_t)qv;
+                    } else {                                                 // O / down, unsplit: the "partial" is the whole sum; one path for the consumer
+                        __stcg(P.part + part_off + (size_t)g * 32 + ln, (double)v0);
+                    }
                 });
             } else {
-                // ---- final norm over h_mid + last down-projection partials, lm_head, greedy argmax (lowest index wins ties)
-                const Job& dj = sm.jobs[4 * (P.L - 1) + 3];
-                stage_norm_q8(P, P.h_mid, 0, P.part + dj.part_off, dj.ks, nullptr, P.out_norm, P.E, P.eps, sm.red, xq_s, xs_s);
-                prof_mark(P, tp, 10);
+                // ---- lm_head on the staged final norm, greedy argmax (lowest index wins ties)
                 float best = -INFINITY; int bidx = 0x7fffffff;
                 float* lg = P.logits ? P.logits + (long long)(step - step0) * P.logits_stride : nullptr;
                 ok = run_warp_job(ws, 4 * P.L, lane, xq_s, xs_s, [&](int g, int ln, float v0) {
