@@ -526,56 +526,63 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         {
             const int sub = lane >> 3, li = lane & 7;
             constexpr int KV4 = DPL * 2 / 16 > 0 ? DPL * 2 / 16 : 1;        // 16-byte loads per lane and position
-            uint4 kraw[8][KV4];
-            #pragma unroll
-            for (int sw = 0; sw < 8; sw++) {
-                if (sw * 4 >= np) continue;                                  // warp-uniform
-                const int pi = min(sw * 4 + sub, np - 1);
-                const __half* kr = kbase + (size_t)(b0 + pi) * P.KVD + li * DPL;
-                if constexpr (DPL >= 8) {
-                    #pragma unroll
-                    for (int c = 0; c < KV4; c++) kraw[sw][c] = __ldcg(reinterpret_cast<const uint4*>(kr) + c);
-                } else {
-                    const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(kr));
-                    kraw[sw][0] = make_uint4(k2.x, k2.y, 0u, 0u);
-                }
-            }
-            #pragma unroll
-            for (int sw = 0; sw < 8; sw++) {
-                if (sw * 4 < np) {                                           // warp-uniform
-                    const int pi = sw * 4 + sub;
-                    double kd[DPL];
-                    #pragma unroll
-                    for (int c = 0; c < KV4; c++) {
-                        const __half2* hh = reinterpret_cast<const __half2*>(&kraw[sw][c]);
+            // two rounds of four sweeps (16 positions): half the unrolled code of one round of eight; a round's K rows
+            // are all requested before the first one is used
+            #pragma unroll 1
+            for (int s0 = 0; s0 < 8 && s0 * 4 < np; s0 += 4) {
+                uint4 kraw[4][KV4];
+                #pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int sw = s0 + u;
+                    if (sw * 4 >= np) continue;                              // warp-uniform
+                    const int pi = min(sw * 4 + sub, np - 1);
+                    const __half* kr = kbase + (size_t)(b0 + pi) * P.KVD + li * DPL;
+                    if constexpr (DPL >= 8) {
                         #pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            if (c * 8 + 2 * e < DPL) {
-                                const float2 f = __half22float2(hh[e]);
-                                kd[c * 8 + 2 * e] = (double)f.x; kd[c * 8 + 2 * e + 1] = (double)f.y;
+                        for (int c = 0; c < KV4; c++) kraw[u][c] = __ldcg(reinterpret_cast<const uint4*>(kr) + c);
+                    } else {
+                        const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(kr));
+                        kraw[u][0] = make_uint4(k2.x, k2.y, 0u, 0u);
+                    }
+                }
+                #pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int sw = s0 + u;
+                    if (sw * 4 < np) {                                       // warp-uniform
+                        const int pi = sw * 4 + sub;
+                        double kd[DPL];
+                        #pragma unroll
+                        for (int c = 0; c < KV4; c++) {
+                            const __half2* hh = reinterpret_cast<const __half2*>(&kraw[u][c]);
+                            #pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                if (c * 8 + 2 * e < DPL) {
+                                    const float2 f = __half22float2(hh[e]);
+                                    kd[c * 8 + 2 * e] = (double)f.x; kd[c * 8 + 2 * e + 1] = (double)f.y;
+                                }
                             }
                         }
-                    }
-                    double d[G];
-                    #pragma unroll
-                    for (int j = 0; j < G; j++) {
-                        const double* qj = qs + (j * LPP + li) * QSTR;
-                        double acc = 0.0;
+                        double d[G];
                         #pragma unroll
-                        for (int e = 0; e < DPL; e += 2) {
-                            const double2 qq = *reinterpret_cast<const double2*>(qj + e);
-                            acc = __fma_rn(qq.x, kd[e], acc);
-                            acc = __fma_rn(qq.y, kd[e + 1], acc);
+                        for (int j = 0; j < G; j++) {
+                            const double* qj = qs + (j * LPP + li) * QSTR;
+                            double acc = 0.0;
+                            #pragma unroll
+                            for (int e = 0; e < DPL; e += 2) {
+                                const double2 qq = *reinterpret_cast<const double2*>(qj + e);
+                                acc = __fma_rn(qq.x, kd[e], acc);
+                                acc = __fma_rn(qq.y, kd[e + 1], acc);
+                            }
+                            d[j] = acc;
                         }
-                        d[j] = acc;
-                    }
-                    #pragma unroll
-                    for (int sft = 1; sft <= 4; sft <<= 1)
                         #pragma unroll
-                        for (int j = 0; j < G; j++) d[j] = __dadd_rn(d[j], __shfl_xor_sync(0xffffffffu, d[j], sft));
-                    if (li == 0 && pi < np) {
-                        #pragma unroll
-                        for (int j = 0; j < G; j++) wl[pi * G + j] = (double)__fmul_rn(__double2float_rn(d[j]), inv);
+                        for (int sft = 1; sft <= 4; sft <<= 1)
+                            #pragma unroll
+                            for (int j = 0; j < G; j++) d[j] = __dadd_rn(d[j], __shfl_xor_sync(0xffffffffu, d[j], sft));
+                        if (li == 0 && pi < np) {
+                            #pragma unroll
+                            for (int j = 0; j < G; j++) wl[pi * G + j] = (double)__fmul_rn(__double2float_rn(d[j]), inv);
+                        }
                     }
                 }
             }
