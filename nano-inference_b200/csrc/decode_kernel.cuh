@@ -360,20 +360,24 @@ __device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const flo
     for (int k = 0; k < NB; k++) {
         const int b = min(warp + k * DNW, nb - 1), e = b * 32 + lane;      // clamped: every address is valid
         wv[k] = __ldg(w + e);
-        if (src) x[k] = __ldcg(src + e);
-        else {                                                  // embedding: value (nibble - 8) * d (src/gguf.h:94-102)
-            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
-            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
-            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
-            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
-            x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
-        }
+        x[k] = src ? __ldcg(src + e) : 0.f;
         #pragma unroll
         for (int q = 0; q < 4; q++) pt[k][q] = 0.0;
         if (part) {
             const double* pp = part + (size_t)b * ks * 32 + lane;
             #pragma unroll
             for (int q = 0; q < 4; q++) if (q < ks) pt[k][q] = __ldcg(pp + q * 32);
+        }
+    }
+    if (!src) {                                                 // layer 0: the embedding row, value (nibble - 8) * d (src/gguf.h:94-102)
+        #pragma unroll
+        for (int k = 0; k < NB; k++) {
+            const int b = min(warp + k * DNW, nb - 1);
+            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
+            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
+            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
+            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
+            x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
         }
     }
     // pass B: fold the partials in split order (ks <= 4, enforced when the jobs are planned)
@@ -440,6 +444,7 @@ __device__ __forceinline__ void stage_norm_q8(const DecodeParams& P, const float
                                               const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
     const int per_warp = (E / 32 + DNW - 1) / DNW;
     if (per_warp <= 4) stage_norm_q8_t<4>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+    else if (per_warp <= 6) stage_norm_q8_t<6>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
     else if (per_warp <= 8) stage_norm_q8_t<8>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
     else stage_norm_q8_wide(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
 }
