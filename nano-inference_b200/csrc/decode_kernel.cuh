@@ -614,16 +614,18 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         }
         __syncwarp();
         // pass 2: o += w[p] * V[p]
-        for (int pp0 = 0; pp0 < np; pp0 += 8) {                              // 8 positions' V rows requested together
-            unsigned short vh[8][DPW];
+        constexpr int VB = G == 1 ? 16 : 8;                                  // V rows requested together (one head per CTA: registers to spare)
+        for (int pp0 = 0; pp0 < np; pp0 += VB) {
+            unsigned short vh[VB][DPW];
             #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < VB; u++) {
+                if (u >= 8 && pp0 + u >= np) continue;                       // warp-uniform: the second half of a round may be empty
                 const unsigned short* vp = reinterpret_cast<const unsigned short*>(vbase + (size_t)(b0 + min(pp0 + u, np - 1)) * P.KVD);
                 #pragma unroll
                 for (int i = 0; i < DPW; i++) vh[u][i] = __ldcg(vp + lane + 32 * i);
             }
             #pragma unroll
-            for (int u = 0; u < 8; u++) {
+            for (int u = 0; u < VB; u++) {
                 if (pp0 + u < np) {
                     double vd[DPW];
                     #pragma unroll
@@ -652,15 +654,13 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     // warp j folds head j's DNW warp states against their common maximum and publishes the chunk partial
     if (warp < G) {
         const int j = warp, head = h0 + j;
-        float mm = -INFINITY;
-        #pragma unroll
-        for (int w = 0; w < DNW; w++) mm = fmaxf(mm, (float)scr[(size_t)(w * G + j) * SW + HD]);
+        // lane w takes warp w's maximum: one exponential for all eight rescale factors, then broadcast
+        const float mw_l = lane < DNW ? (float)scr[(size_t)(lane * G + j) * SW + HD] : -INFINITY;
+        const float mm = warp_max_float(mw_l);
+        const double f_l = mw_l == -INFINITY ? 0.0 : exp_shared((double)mw_l - (double)mm);
         double f[DNW];
         #pragma unroll
-        for (int w = 0; w < DNW; w++) {
-            const float mw = (float)scr[(size_t)(w * G + j) * SW + HD];
-            f[w] = mw == -INFINITY ? 0.0 : exp_shared((double)mw - (double)mm);
-        }
+        for (int w = 0; w < DNW; w++) f[w] = __shfl_sync(0xffffffffu, f_l, w);
         double ob[DPW], ll = 0.0;
         #pragma unroll
         for (int i = 0; i < DPW; i++) ob[i] = 0.0;
