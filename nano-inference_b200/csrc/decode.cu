@@ -12,6 +12,8 @@
 
 using namespace mi;
 
+namespace mi { const void* decode_kernel_prof(int HD, int G); }
+
 namespace {
 
 struct Staging {       // one reusable device buffer for raw GGUF bytes
@@ -69,9 +71,13 @@ int plan_ks(int kind, int groups, int nt, int grid) {
 
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
     void (*kern)(DecodeParams, int, int, int, int) = nullptr;
-    #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
-    MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
-    #undef MI_PICK
+    if (P.prof) {                                   // the instrumented build (decode_prof.cu)
+        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_prof(m->HD, m->G)));
+    } else {
+        #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
+        MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
+        #undef MI_PICK
+    }
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: head_dim %d with %d query heads per kv head is not instantiated", m->HD, m->G);
     static const void* attr_done[16] = {nullptr};
     if (attr_done[ctx->device & 15] != (const void*)kern) {

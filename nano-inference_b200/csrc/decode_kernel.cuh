@@ -40,6 +40,19 @@
 #pragma once
 #include "gemv_core.cuh"
 
+// The kernel exists in two builds.  The default one carries no profiling code at all: the timer marks that the
+// in-kernel profiler needs cost 6 % of the step when merely compiled in (they sit between the hot instructions of every
+// phase).  A translation unit that defines MI_PROF 1 before including this file gets the instrumented build; the two live in
+// different inline namespaces, so both can be linked into one library and picked at launch time.
+#ifndef MI_PROF
+#define MI_PROF 0
+#endif
+#if MI_PROF
+#define MI_KVARIANT prof
+#else
+#define MI_KVARIANT fast
+#endif
+
 namespace mi {
 
 constexpr int DNW = 8;            // warps per CTA
@@ -107,6 +120,7 @@ __host__ __device__ inline int attn_chunks(int Lp, int max_chunks, int chunk = k
 }
 
 #ifdef __CUDACC__
+inline namespace MI_KVARIANT {
 
 struct DecodeSmem {
     uint8_t* ring; uint64_t* bars; Job* jobs; LayerPtrs* lp; float* cs; double* red; double* fold; uint8_t* stage;
@@ -128,9 +142,13 @@ __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, in
 // close the current profile interval: charge the time since t to slot k (CTA 0, thread 0 only).
 // The sums live in shared memory and are flushed once at kernel exit, so a mark costs a
 // timer read and a shared-memory add, not a global round trip on the critical path.
+#if MI_PROF
 __shared__ unsigned long long s_prof[kProfSlots];
+#endif
 __device__ __forceinline__ void prof_mark(const DecodeParams& P, unsigned long long& t, int k) {
+#if MI_PROF
     if (P.prof && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); s_prof[k] += n - t; t = n; }
+#endif
 }
 
 // ---- grid barrier: monotonic arrival counter, bounded wait -----------------------
@@ -390,7 +408,7 @@ __device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const flo
         pv[k] = s;
         if (warp + k * DNW >= nb) { x[k] = 0.f; pv[k] = 0.0; }         // a clamped duplicate: contributes nothing
     }
-    unsigned long long tq = gtime_ns();
+    unsigned long long tq = MI_PROF ? gtime_ns() : 0;
     double ss = 0.0;
     #pragma unroll
     for (int k = 0; k < NB; k++) {
@@ -766,7 +784,9 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     sm.fold = reinterpret_cast<double*>(after_jobs + 1024 + 256);
     sm.stage = after_jobs + 1024 + 256 + kFoldBytes;
     __shared__ int s_ok;
+#if MI_PROF
     if (tid < kProfSlots) s_prof[tid] = 0;
+#endif
 
     for (int i = tid; i < njobs * (int)(sizeof(Job) / 4); i += DNT)
         reinterpret_cast<int*>(sm.jobs)[i] = __ldg(reinterpret_cast<const int*>(P.jobs) + i);
@@ -801,7 +821,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     bool ok = true;
     const bool single = (step1 - step0 == 1) && (ph1 - ph0 == 1);
 
-    unsigned long long tp = P.prof ? gtime_ns() : 0;
+    unsigned long long tp = (MI_PROF && P.prof) ? gtime_ns() : 0;
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = P.pos0 + step;
         if (tid < HD / 2) {
@@ -918,15 +938,18 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             prof_mark(P, tp, kProfBarrier);
         }
     }
+#if MI_PROF
     if (P.prof && blockIdx.x == 0) {
         __syncthreads();
         if (tid < kProfSlots) P.prof[tid] += s_prof[tid];
     }
+#endif
     if (!ok) {
         if (lane == 0) atomicMax(P.err, MI_ERR_TIMEOUT);
         ws.drain();
     }
 }
 
+}  // inline namespace
 #endif  // __CUDACC__
 }  // namespace mi
