@@ -17,9 +17,9 @@ struct VerifyBufs {
     float* logits = nullptr;           // [M][V]
     int* tokens = nullptr; int* out = nullptr;          // [M]
     int* pos0 = nullptr;               // first position of the pass (device resident so that the launch sequence is position-free)
-    void* graph[17] = {};              // cudaGraphExec_t of the pass per M, and the scratch addresses each was built with
-    const void* graph_part[17] = {}; const void* graph_cnt[17] = {};
-    bool warm[17] = {};
+    void* graph[51] = {};              // cudaGraphExec_t of the pass per M, and the scratch addresses each was built with
+    const void* graph_part[51] = {}; const void* graph_cnt[51] = {};
+    bool warm[51] = {};                // index: M + 17 * attention regime (see verify.cu)
     double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
     unsigned long long* amax_key = nullptr; unsigned* amax_cnt = nullptr;   // [M] argmax scratch, self-clearing
 };

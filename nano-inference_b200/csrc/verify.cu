@@ -199,7 +199,10 @@ int ensure_bufs(mi_ctx* ctx, mi_model* m) {
 namespace {
 
 // enqueue one pass over the tokens in b.tokens at the position in b.pos0 (both already on the device)
-int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
+// regime: how many CTAs per query the attention launch needs - 0: every query sees <= 256 positions (one CTA per head),
+// 1: <= 1024 (up to four chunks per head), 2: beyond (the whole grid).  Launching the full grid for eight queries of a
+// short context means eight waves of CTAs that exit at once; the chunking of a query does not depend on the regime.
+int enqueue_pass(mi_ctx* ctx, mi_model* m, int M, int regime) {
     VerifyBufs& b = m->vb;
     const int E = m->E, FF = m->FF, L = m->L, V = m->V;
     DecodeParams P = m->P;
@@ -207,6 +210,7 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
     P.prof = nullptr;
     const std::vector<LayerPtrs>& lp = m->layer_ptrs;
     const size_t nsm = (size_t)E * 4;
+    const int attn_grid = regime == 0 ? std::min(m->grid, m->NH) : regime == 1 ? std::min(m->grid, m->NH * (kPerHeadAttnMax / 256)) : m->grid;
     int st;
     // every launch of the pass may overlap its predecessor's tail (each kernel waits before touching shared data);
     // MINFER_VERIFY_PDL=0 restores plain stream order
@@ -222,7 +226,7 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
         // the GEMM packs its output at the matrix's own row count: y[m * rows + r]
         if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
         MI_CUDA(ctx, launch_k(pdl, vf_rope_kv, dim3(M), dim3(DNT), 0, ctx->stream, P, l, (const int*)b.pos0, b.qkv, (int)wqkv->rows));
-        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, m->grid, M, l, b.pos0, 0, wqkv->rows))) return st;
+        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, attn_grid, M, l, b.pos0, 0, wqkv->rows))) return st;
         if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
         MI_CUDA(ctx, launch_k(pdl, vf_norm_quant, dim3(M), dim3(DNT), nsm, ctx->stream, P, (const int*)b.tokens, false, b.X, (const float*)b.Y, E,
                               lp[l].ffn_norm, b.xq, b.xd));
@@ -243,20 +247,21 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M) {
 // given M - the first one runs plainly and lets the GEMM grow its scratch - and rebuilt if
 // that scratch has moved since.  Streams that cannot capture (the legacy default stream) and
 // MINFER_VERIFY_GRAPH=0 run plainly.
-int run_pass(mi_ctx* ctx, mi_model* m, int M) {
+int run_pass(mi_ctx* ctx, mi_model* m, int M, int regime) {
     VerifyBufs& b = m->vb;
     static const bool use_graph = [] { const char* e = getenv("MINFER_VERIFY_GRAPH"); return !(e && atoi(e) == 0); }();
     const bool capturable = ctx->stream != nullptr && ctx->stream != cudaStreamLegacy && ctx->stream != cudaStreamPerThread;
-    if (!use_graph || !capturable) return enqueue_pass(ctx, m, M);
-    if (b.graph[M] && (b.graph_part[M] != (const void*)ctx->part || b.graph_cnt[M] != (const void*)ctx->counters)) {
-        cudaGraphExecDestroy((cudaGraphExec_t)b.graph[M]);        // the GEMM scratch it points into has been reallocated since
-        b.graph[M] = nullptr;
+    if (!use_graph || !capturable) return enqueue_pass(ctx, m, M, regime);
+    const int key = M + 17 * regime;
+    if (b.graph[key] && (b.graph_part[key] != (const void*)ctx->part || b.graph_cnt[key] != (const void*)ctx->counters)) {
+        cudaGraphExecDestroy((cudaGraphExec_t)b.graph[key]);      // the GEMM scratch it points into has been reallocated since
+        b.graph[key] = nullptr;
     }
-    if (!b.graph[M]) {
-        if (!b.warm[M]) { b.warm[M] = true; return enqueue_pass(ctx, m, M); }
+    if (!b.graph[key]) {
+        if (!b.warm[key]) { b.warm[key] = true; return enqueue_pass(ctx, m, M, regime); }
         cudaGraph_t g = nullptr;
         MI_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        const int st = enqueue_pass(ctx, m, M);
+        const int st = enqueue_pass(ctx, m, M, regime);
         const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
         if (st != MI_OK) { if (g) cudaGraphDestroy(g); return st; }
         if (e != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "verify: stream capture failed: %s", cudaGetErrorString(e));
@@ -264,9 +269,9 @@ int run_pass(mi_ctx* ctx, mi_model* m, int M) {
         const cudaError_t e2 = cudaGraphInstantiate(&ge, g, 0);
         cudaGraphDestroy(g);
         if (e2 != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "verify: graph instantiation failed: %s", cudaGetErrorString(e2));
-        b.graph[M] = ge; b.graph_part[M] = ctx->part; b.graph_cnt[M] = ctx->counters;
+        b.graph[key] = ge; b.graph_part[key] = ctx->part; b.graph_cnt[key] = ctx->counters;
     }
-    MI_CUDA(ctx, cudaGraphLaunch((cudaGraphExec_t)b.graph[M], ctx->stream));
+    MI_CUDA(ctx, cudaGraphLaunch((cudaGraphExec_t)b.graph[key], ctx->stream));
     return MI_OK;
 }
 
@@ -291,7 +296,8 @@ extern "C" int mi_verify(mi_ctx* ctx, mi_model* m, const int32_t* tokens_host, i
     head[VMAX] = pos0;
     MI_CUDA(ctx, cudaMemcpyAsync(b.tokens, head, sizeof(head), cudaMemcpyHostToDevice, ctx->stream));   // pageable source: staged before the call returns
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
-    if ((st = run_pass(ctx, m, M))) return st;
+    const int lp_max = pos0 + M, regime = lp_max <= 256 ? 0 : lp_max <= kPerHeadAttnMax ? 1 : 2;
+    if ((st = run_pass(ctx, m, M, regime))) return st;
     MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
     if (logits_dev) MI_CUDA(ctx, cudaMemcpyAsync(logits_dev, b.logits, (size_t)M * m->V * 4, cudaMemcpyDeviceToDevice, ctx->stream));
     if (out_tokens_host) MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, b.out, (size_t)M * 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -327,5 +333,8 @@ extern "C" int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* 
     P.att_q = reinterpret_cast<int8_t*>(ctx->part + part);
     P.att_d = reinterpret_cast<__half*>(reinterpret_cast<int8_t*>(ctx->part + part) + (size_t)M * NQ);
     P.err = ctx->d_err;
-    return launch_attention<true>(ctx, P, head_dim, G, grid, M, 0, nullptr, pos0, NQ);
+    // CTAs per query that the longest causal range of the call can use (the chunking of a query does not depend on it)
+    const int lp_max = pos0 + M;
+    const int agrid = lp_max <= 256 ? std::min(grid, n_head) : lp_max <= kPerHeadAttnMax ? std::min(grid, n_head * (kPerHeadAttnMax / 256)) : grid;
+    return launch_attention<true>(ctx, P, head_dim, G, agrid, M, 0, nullptr, pos0, NQ);
 }

@@ -139,15 +139,22 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         if (mi_model_state_ptr(model, MI_STATE_PROFILE, &p, &nb) == MI_OK && p) {
             unsigned long long pr[32];
             mi_memcpy_to_host(ctx, pr, p, sizeof pr);
+            // slots (csrc/decode_kernel.cuh): 2k = prologue of phase kind k, 2k+1 = its tail after the unit loop, 12 = grid
+            // barrier, 13 = step prologue, 14..16 = attention (q staging, scan, fold + merge), 18 / 19 = tile loops and
+            // fold + epilogue of the per-layer GEMV phases
             const char* ph[6] = {"P1 QKV", "P2 attention", "P3 Wo", "P4 gate/up", "P5 down", "lm_head"};
             const double steps = (double)(P + n_gen - 1 + env_int("WARMUP", 2));
+            auto us = [&](int k) { return pr[k] / 1e3 / steps; };
             double tot = 0;
             for (int k = 0; k < 6; k++) {
-                fprintf(stderr, "  %-13s %8.1f %8.1f us/token (staging, work)\n", ph[k], pr[2 * k] / 1e3 / steps, pr[2 * k + 1] / 1e3 / steps);
-                tot += (pr[2 * k] + pr[2 * k + 1]) / 1e3 / steps;
+                const double stage = k == 1 ? us(14) : us(2 * k), work = k == 1 ? us(15) + us(16) + us(3) : us(2 * k + 1);
+                fprintf(stderr, "  %-13s %8.1f %8.1f us/token (prologue, %s)\n", ph[k], stage, work, k == 1 ? "scan + fold" : k == 5 ? "lm_head rows + argmax" : "tail");
+                tot += stage + work;
             }
-            fprintf(stderr, "  %-13s %8.1f us/token; step prologue %.1f; total %.1f us/position on CTA 0\n", "grid barrier", pr[12] / 1e3 / steps,
-                    pr[13] / 1e3 / steps, tot + (pr[12] + pr[13]) / 1e3 / steps);
+            fprintf(stderr, "  %-13s %8.1f %8.1f us/token (tile loops, fold + epilogue of P1 / P3 / P4 / P5)\n", "GEMV units", us(18), us(19));
+            tot += us(18) + us(19);
+            fprintf(stderr, "  %-13s %8.1f us/token; step prologue %.1f; total %.1f us/position on CTA 0\n", "grid barrier", us(12), us(13),
+                    tot + us(12) + us(13));
         }
     }
     mi_model_free(ctx, model);
