@@ -1,12 +1,16 @@
 #!/usr/bin/env python
 """Benchmark of the B200-native quantized decode path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|gemv]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload decode|gemv|gemm|verify|attn|setup]
 
 Prints ONE JSON line on rank 0.  For N > 1 it is launched by torch.distributed.run
-(one rank per GPU).  DESIGN.md, "Measurement", says what each field means.
+(one rank per GPU).  Fields: `value` = device-timed throughput of the whole job with inputs
+resident in HBM; `e2e` = the same metric through the host-buffer API call, copies included;
+`roofline` = algorithmic bytes per launch / CUDA-event time against the measured HBM peak;
+`cpu_baseline` = the reference's own CPU program on a bounded sample of the workload.
 
-Workload "decode" (default; config 2 of BASELINE.json): Qwen2.5-1.5B-shape all-q4_0
+Workload "decode" (default; the 1.5B-shape batch-1 configuration): Qwen2.5-1.5B-shape all-q4_0
 model with seeded random weights (written by the package's gguf_synth), fp16 KV cache
 for 4096 positions, a 64-token seeded prompt, then batch-1 greedy decode.  A step is
 one generated token; K steps run inside one launch of the persistent decode kernel.

@@ -66,7 +66,7 @@ def test_streams_against_reference_cpu_infer_golden(ctx, pkg, cases):
     """cpu_infer multiplies fp32 activations; this engine quantizes them to q8_0 (as the
     reference's GPU engines do), so agreement is exact only while no near-tie flips:
     the two milder models must match in full; on the liveliest one (weights std 0.3, near-ties
-    everywhere) only the first token is required, and the q8 oracle is the judge instead."""
+    everywhere) only the first token is required; there the q8 oracle decides."""
     for path, c in cases:
         m = pkg.Model(ctx, path, max_seq=len(c["prompt"]) + c["n_gen"])
         got, _ = m.generate(c["prompt"], c["n_gen"])
