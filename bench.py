@@ -608,8 +608,8 @@ def run_ours(args, rank, world, local_rank):
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
         L = cfg.n_layer
         launches = K * (5 * L + 1 + 1)
-        engine = f"kernel sequence, one launch per phase; {4 * L + 1} NCCL collectives per token issued by the host"
-        parallelism = f"tp{world}: rows of every matrix sharded over {world} GPUs, attention replicated"
+        engine = f"kernel sequence, one launch per phase; {2 * L + 1} NCCL collectives per token issued by the host"
+        parallelism = f"tp{world}: rows of gate/up, down and lm_head sharded over {world} GPUs; QKV, attention and O replicated"
     clocks = sampler.stop() if sampler else None
     (ms, e2e_ms), _ = reduce_max_sum([ms, e2e_ms], [0.0])
     model.free()

@@ -254,16 +254,17 @@ MI_API int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* kcac
 /* ---- tensor parallelism (one process per GPU) --------------------------------- */
 
 /* The reference is single-GPU (README.md:54); this part has no counterpart in it.
- * Every GEMV job of the decode step is sharded by rows: GPU `rank` of `world` owns a
- * contiguous range of each matrix's 32-row groups (mi_tp_partition) and streams only
- * those rows.  What a sharded phase produces lands in a buffer that all GPUs lay out
- * identically, with the entries a GPU does not own left at zero; an all-reduce (sum)
- * of that buffer between the phases - NCCL, issued by the host program - therefore
- * reproduces, bit for bit, what one GPU computes (x + 0 is exact for every type).
- * Attention is replicated.  Per token and layer: all-reduce after the QKV phase
- * (MI_TP_QKV), the O phase (MI_TP_PART_O), the gate/up phase (MI_TP_ACT) and the down
- * phase (MI_TP_PART_DOWN); after the lm_head each GPU holds the best logit of its rows
- * (MI_TP_BEST: {float value, int32 token}); gather those and call mi_tp_pick. */
+ * The gate/up, down and lm_head jobs of the decode step (nine tenths of the weight bytes) are
+ * sharded by rows: GPU `rank` of `world` owns a contiguous range of each matrix's 32-row groups
+ * (mi_tp_partition) and streams only those rows.  What a sharded phase produces lands in a
+ * buffer that all GPUs lay out identically, with the entries a GPU does not own left at zero;
+ * an all-reduce (sum) of that buffer after the phase - NCCL, issued by the host program -
+ * therefore reproduces, bit for bit, what one GPU computes (x + 0 is exact for every type).
+ * The QKV and O projections and attention are computed in full by every GPU (no exchange).
+ * Per token and layer: all-reduce after the gate/up phase (MI_TP_ACT) and after the down phase
+ * (MI_TP_PART_DOWN); after the lm_head each GPU holds the best logit of its rows
+ * (MI_TP_BEST: {float value, int32 token}); gather those and call mi_tp_pick.  MI_TP_QKV and
+ * MI_TP_PART_O name buffers that need no exchange; they stay addressable for inspection. */
 enum { MI_TP_QKV = 0, MI_TP_PART_O = 1, MI_TP_ACT = 2, MI_TP_PART_DOWN = 3, MI_TP_BEST = 4 };
 
 /* Range [begin, end) of `groups` row groups owned by `rank`.  Pure arithmetic, no GPU needed. */

@@ -220,11 +220,14 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         // tensor parallelism: this GPU owns a contiguous range of the job's unit groups (rows); every GPU holds the
         // whole matrix but streams only its rows.  The K-split is planned from the largest share so that all GPUs
         // lay the partial sums out identically.
-        int g0, g1;
-        mi_tp_partition(groups, tp_rank, tp_world, &g0, &g1);
+        // The QKV and O projections (a tenth of a layer's bytes) are the exception: every GPU computes all their rows,
+        // so that attention and the O projection need no exchange at all.
+        const bool replicated = kind == JOB_QKV || kind == JOB_O;
+        int g0 = 0, g1 = groups;
+        if (!replicated) mi_tp_partition(groups, tp_rank, tp_world, &g0, &g1);
         jb.g_off = g0; jb.groups = g1 - g0;
         jb.base = base + (size_t)g0 * nacc * jb.nt * tile_bytes(jb.kb);
-        jb.ks = plan_ks(kind, (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
+        jb.ks = plan_ks(kind, replicated ? groups : (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
         const char* force = kind == JOB_O ? getenv("MINFER_KS_O") : kind == JOB_DOWN ? getenv("MINFER_KS_DOWN") : nullptr;   // tuning knobs
         if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
         jb.n_units = jb.groups * jb.ks;
@@ -550,9 +553,7 @@ extern "C" int mi_decode_launch(mi_ctx* ctx, mi_model* m, int pos, int phase_beg
             // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce
             const int l = ph / 5, k = ph % 5;
             void* p = nullptr; int64_t nb = 0;
-            if (k == 0) mi_model_tp_region(m, MI_TP_QKV, l, &p, &nb);
-            else if (k == 2) mi_model_tp_region(m, MI_TP_PART_O, l, &p, &nb);
-            else if (k == 3) mi_model_tp_region(m, MI_TP_ACT, l, &p, &nb);
+            if (k == 3) mi_model_tp_region(m, MI_TP_ACT, l, &p, &nb);               // QKV and O are computed in full by every GPU
             else if (k == 4) mi_model_tp_region(m, MI_TP_PART_DOWN, l, &p, &nb);
             if (p) MI_CUDA(ctx, cudaMemsetAsync(p, 0, (size_t)nb, ctx->stream));
         }

@@ -1,8 +1,9 @@
 """Tensor-parallel decode, one process per GPU: the host side of the exchange.
 
-Each rank owns a contiguous range of every matrix's 32-row groups and runs the
-decode phases through the C ABI (mi_decode_launch, asynchronous); between phases it
-all-reduces the buffer the phase wrote (NCCL through torch.distributed, on the same
+Each rank owns a contiguous range of the 32-row groups of the gate/up, down and lm_head
+matrices (nine tenths of the bytes; QKV and O are computed in full by every rank, so
+attention needs no exchange) and runs the decode phases through the C ABI
+(mi_decode_launch, asynchronous); after a sharded phase it all-reduces the buffer the phase wrote (NCCL through torch.distributed, on the same
 stream).  Entries a rank does not own are zero before the reduction, so the sum
 reproduces the single-GPU values bit for bit - the buffers are reduced as raw bytes,
 which is valid for every element type because x + 0 never carries.
@@ -28,9 +29,7 @@ class TPDecoder:
         self.L = model.config.n_layer
         self.torch = torch
         if self.world > 1:
-            self.r_qkv = model.tp_region(pkg.TP_QKV)
             self.r_act = model.tp_region(pkg.TP_ACT)
-            self.r_o = [model.tp_region(pkg.TP_PART_O, l) for l in range(self.L)]
             self.r_down = [model.tp_region(pkg.TP_PART_DOWN, l) for l in range(self.L)]
             self.r_best = model.tp_region(pkg.TP_BEST)
             self.gathered = torch.zeros(8 * self.world, dtype=torch.uint8, device="cuda")
@@ -45,9 +44,9 @@ class TPDecoder:
             m.launch(pos, 0, 5 * L + 1)
             return
         for l in range(L):
-            m.launch(pos, 5 * l, 5 * l + 1); self._allreduce(self.r_qkv)
-            m.launch(pos, 5 * l + 1, 5 * l + 3); self._allreduce(self.r_o[l])
-            m.launch(pos, 5 * l + 3, 5 * l + 4); self._allreduce(self.r_act)
+            # QKV, attention and the O projection are computed in full by every rank; the two large projections
+            # are sharded: one all-reduce after gate/up (the quantized activations), one after down (its partial sums)
+            m.launch(pos, 5 * l, 5 * l + 4); self._allreduce(self.r_act)
             m.launch(pos, 5 * l + 4, 5 * l + 5); self._allreduce(self.r_down[l])
         m.launch(pos, 5 * L, 5 * L + 1)
         self.dist.all_gather_into_tensor(self.gathered, self.r_best, group=self.group)
