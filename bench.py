@@ -582,17 +582,26 @@ def run_ours(args, rank, world, local_rank):
         engine = "persistent kernel (one cooperative launch for all timed steps)"
         parallelism = "single GPU"
     else:
-        # tensor parallel: every GEMV job row-sharded over the ranks, NCCL all-reduce of the (zero-padded) phase
-        # outputs after the QKV, O, gate/up and down phases of every layer, attention replicated
+        # tensor parallel: the large GEMV jobs row-sharded over the ranks, NCCL all-reduce of the (zero-padded) phase
+        # outputs after the gate/up and down phases of every layer; QKV, attention and O replicated.  One step (phase
+        # launches + collectives) is captured into a CUDA graph once and replayed per token (MINFER_TP_GRAPH=0: plain).
         tpmod = ge.load_submodule("tp")
         dec = tpmod.TPDecoder(pkg, model, dist)
+        use_graph = os.environ.get("MINFER_TP_GRAPH", "1") != "0"
+        if use_graph:
+            dec.capture()
         warm = dec.decode(ids, PROMPT_LEN + warmup)            # untimed: prompt, then W greedy steps
         sampler = ClockSampler(local_rank) if rank == 0 else None
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if use_graph:
+            model.set_pos(pos0)
         e0.record()
         for s in range(K):
-            dec.step(pos0 + s)
+            if use_graph:
+                dec.graph.replay()
+            else:
+                dec.step(pos0 + s)
         e1.record()
         barrier()
         ctx.sync()
@@ -602,14 +611,19 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         t0 = time.perf_counter()
         for s in range(e2e_steps):                              # host reads the token back after every step
-            dec.step(pos0 + K + s)
+            if use_graph:
+                dec.graph.replay()
+            else:
+                dec.step(pos0 + K + s)
             model.get_token()
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
         L = cfg.n_layer
         launches = K * (5 * L + 1 + 1)
-        engine = f"kernel sequence, one launch per phase; {2 * L + 1} NCCL collectives per token issued by the host"
+        engine = (f"kernel sequence, one launch per phase; {2 * L + 1} NCCL collectives per token; "
+                  + ("one CUDA graph per token (launches + collectives)" if use_graph else "issued by the host"))
         parallelism = f"tp{world}: rows of gate/up, down and lm_head sharded over {world} GPUs; QKV, attention and O replicated"
+        dec.release()                       # the captured graph must be gone before the process group is destroyed
     clocks = sampler.stop() if sampler else None
     (ms, e2e_ms), _ = reduce_max_sum([ms, e2e_ms], [0.0])
     model.free()

@@ -277,6 +277,13 @@ MI_API int mi_model_tp_region(const mi_model* model, int which, int layer, void*
  * waiting; the input token is the model's device-resident current token.  On a sharded model the
  * buffer a phase writes is zeroed first.  The caller interleaves its all-reduces on the same stream. */
 MI_API int mi_decode_launch(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
+/* Position argument of mi_decode_launch that means "the model's device-resident position": a launch sequence
+ * enqueued with it does not depend on the step and can be captured once into a CUDA graph by the host program
+ * (tensor-parallel steps: the phase launches and the NCCL all-reduces between them) and replayed per token. */
+#define MI_POS_DEVICE (-1)
+/* Set / add to (both asynchronously) the device-resident position. */
+MI_API int mi_model_set_pos(mi_ctx* ctx, mi_model* model, int pos);
+MI_API int mi_model_advance_pos(mi_ctx* ctx, mi_model* model, int delta);
 /* Set (asynchronously) / read back (synchronously) the model's current token. */
 MI_API int mi_model_set_token(mi_ctx* ctx, mi_model* model, int32_t token);
 MI_API int mi_model_get_token(mi_ctx* ctx, mi_model* model, int32_t* token, float* best_val);

@@ -70,12 +70,15 @@ SIGNATURES = {
     "mi_model_tp_region": (_i32, [_vp, _i32, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
     "mi_decode_launch": (_i32, [_vp, _vp, _i32, _i32, _i32]),
     "mi_model_set_token": (_i32, [_vp, _vp, _i32]),
+    "mi_model_set_pos": (_i32, [_vp, _vp, _i32]),
+    "mi_model_advance_pos": (_i32, [_vp, _vp, _i32]),
     "mi_model_get_token": (_i32, [_vp, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "mi_tp_pick": (_i32, [_vp, _vp, _vp, _i32]),
 }
 TP_QKV, TP_PART_O, TP_ACT, TP_PART_DOWN, TP_BEST = range(5)
 
 DECODE_PERSISTENT, DECODE_PER_PHASE = 0, 1
+POS_DEVICE = -1          # mi_decode_launch: use the model's device-resident position
 STATE = {"h": 0, "q": 1, "att": 2, "kcache": 3, "vcache": 4, "act_q": 5, "act_d": 6, "profile": 7, "h_mid": 8}
 
 
@@ -276,6 +279,12 @@ class Model:
 
     def launch(self, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_launch(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch")
+
+    def set_pos(self, pos):
+        self.ctx.check(self.ctx.lib.mi_model_set_pos(self.ctx.h, self.h, int(pos)), "mi_model_set_pos")
+
+    def advance_pos(self, delta=1):
+        self.ctx.check(self.ctx.lib.mi_model_advance_pos(self.ctx.h, self.h, int(delta)), "mi_model_advance_pos")
 
     def set_token(self, tok):
         self.ctx.check(self.ctx.lib.mi_model_set_token(self.ctx.h, self.h, int(tok)), "mi_model_set_token")

@@ -361,7 +361,8 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NH)) ||
         (st = dev_alloc(ctx, m, &P.part, part_off)) ||
         (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
-        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) || (st = dev_alloc(ctx, m, &P.bar, 64)))
+        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) || (st = dev_alloc(ctx, m, &P.bar, 64)) ||
+        (st = dev_alloc(ctx, m, &m->d_pos, 1)))
         return st;
     P.act_q = reinterpret_cast<int8_t*>(m->act_buf); P.act_d = reinterpret_cast<__half*>(m->act_buf + FF);   // one run: exchanged as one piece
     P.best_val = m->best_buf; P.cur_token = reinterpret_cast<int*>(m->best_buf + 1);                        // {value, token}: exchanged as one piece
@@ -477,6 +478,7 @@ extern "C" int mi_decode_phases(mi_ctx* ctx, mi_model* m, int32_t token, int pos
 
 namespace {
 __global__ void set_token_kernel(int* dst, int tok) { *dst = tok; }
+__global__ void add_int_kernel(int* dst, int delta) { *dst += delta; }
 // gathered: [world] x {float best value, int token}; the largest value wins, the lowest token id on ties
 // (the rule of src/cpu_infer.cpp:153-154 applied across the GPUs' row ranges)
 __global__ void tp_pick_kernel(const float* gathered, int world, float* best_val, int* cur_token) {
@@ -515,6 +517,23 @@ extern "C" int mi_model_set_token(mi_ctx* ctx, mi_model* m, int32_t token) {
     return MI_OK;
 }
 
+extern "C" int mi_model_set_pos(mi_ctx* ctx, mi_model* m, int pos) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "set_pos: null model");
+    if (pos < 0 || pos >= m->max_seq) return set_error(ctx, MI_ERR_LIMIT, "set_pos: position %d outside the KV cache of %d", pos, m->max_seq);
+    set_token_kernel<<<1, 1, 0, ctx->stream>>>(m->d_pos, pos);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
+extern "C" int mi_model_advance_pos(mi_ctx* ctx, mi_model* m, int delta) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m) return set_error(ctx, MI_ERR_INVALID, "advance_pos: null model");
+    add_int_kernel<<<1, 1, 0, ctx->stream>>>(m->d_pos, delta);
+    MI_CUDA(ctx, cudaGetLastError());
+    return MI_OK;
+}
+
 extern "C" int mi_model_get_token(mi_ctx* ctx, mi_model* m, int32_t* token, float* best_val) {
     if (!ctx) return MI_ERR_INVALID;
     if (!m) return set_error(ctx, MI_ERR_INVALID, "get_token: null model");
@@ -540,14 +559,18 @@ extern "C" int mi_decode_launch(mi_ctx* ctx, mi_model* m, int pos, int phase_beg
     if (!m) return set_error(ctx, MI_ERR_INVALID, "decode_launch: null model");
     const int nph = 5 * m->L + 1;
     if (phase_begin < 0 || phase_end > nph || phase_begin > phase_end) return set_error(ctx, MI_ERR_INVALID, "decode_launch: bad phase range");
-    if (pos < 0 || pos >= m->max_seq) return set_error(ctx, MI_ERR_LIMIT, "decode_launch: position %d outside the KV cache of %d", pos, m->max_seq);
+    // pos == MI_POS_DEVICE: the position is the model's device-resident one (mi_model_set_pos / mi_model_advance_pos); the
+    // caller keeps it inside the KV cache
+    const bool dev_pos = pos == MI_POS_DEVICE;
+    if (!dev_pos && (pos < 0 || pos >= m->max_seq)) return set_error(ctx, MI_ERR_LIMIT, "decode_launch: position %d outside the KV cache of %d", pos, m->max_seq);
     int st;
     if (m->out_capacity < 1) {
         if ((st = dev_alloc(ctx, m, &m->d_out_tokens, 16))) return st;
         m->out_capacity = 16;
     }
     DecodeParams P = m->P;
-    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = pos; P.logits = nullptr; P.logits_stride = m->V;
+    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = dev_pos ? 0 : pos; P.logits = nullptr; P.logits_stride = m->V;
+    P.pos_dev = dev_pos ? m->d_pos : nullptr;
     for (int ph = phase_begin; ph < phase_end; ph++) {
         if (m->tp_world > 1 && ph < nph - 1) {
             // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce

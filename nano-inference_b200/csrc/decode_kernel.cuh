@@ -109,6 +109,7 @@ struct DecodeParams {
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
     float* logits; long long logits_stride;    // optional [n_steps][stride]
     int pos0;
+    const int* pos_dev;              // optional: first position read from device memory instead (a captured launch sequence stays position-free)
     unsigned* bar; int* err;
     unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA 0 (see kProf*)
 };
@@ -823,7 +824,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
 
     unsigned long long tp = (MI_PROF && P.prof) ? gtime_ns() : 0;
     for (int step = step0; step < step1 && ok; step++) {
-        const int pos = P.pos0 + step;
+        const int pos = (P.pos_dev ? __ldcg(P.pos_dev) : P.pos0) + step;
         if (tid < HD / 2) {
             const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + tid));    // fp32 angle, as src/cpu_infer.cpp:54
             sm.cs[tid] = __double2float_rn(cos(th)); sm.cs[HD / 2 + tid] = __double2float_rn(sin(th));

@@ -45,6 +45,7 @@ struct mi_model {
     uint8_t* act_buf = nullptr;          // [act_q | act_d]
     float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
     int qkv_rows = 0;
+    int* d_pos = nullptr;                 // device-resident position for position-free launch sequences
     std::vector<mi_weight> views;         // [4L+1] whole matrices in job order (QKV, O, gate/up, down per layer; lm_head), for the M-token step
     std::vector<mi::LayerPtrs> layer_ptrs;    // host copy of the per-layer norm / bias pointers
     mi::VerifyBufs vb;                    // buffers of the M-token step, allocated on first use

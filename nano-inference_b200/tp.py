@@ -34,6 +34,39 @@ class TPDecoder:
             self.r_best = model.tp_region(pkg.TP_BEST)
             self.gathered = torch.zeros(8 * self.world, dtype=torch.uint8, device="cuda")
 
+        self.graph = None
+
+    def capture(self):
+        """Capture one step - the phase launches and the all-reduces between them - into a CUDA graph that reads the
+        position from device memory and advances it; decode() replays it per token.  One plain step runs first (it
+        lets the library make its lazy allocations and NCCL open its channels); the KV cache entry it writes at the
+        model's last position is never read before it is overwritten."""
+        torch, m = self.torch, self.model
+        m.set_pos(m.config.max_seq - 1)
+        self.step(self.pkg.POS_DEVICE)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            m.ctx.use_torch_stream()
+            with torch.cuda.graph(g, stream=side):
+                self.step(self.pkg.POS_DEVICE)
+                m.advance_pos(1)
+        torch.cuda.current_stream().wait_stream(side)
+        m.ctx.use_torch_stream()
+        torch.cuda.synchronize()
+        self.graph = g
+
+    def release(self):
+        """Drop the captured graph.  It holds NCCL work alive: the process group cannot be destroyed before it is gone
+        (destroy_process_group waits forever otherwise)."""
+        if self.graph is not None:
+            import gc
+            self.graph = None
+            gc.collect()
+            self.torch.cuda.synchronize()
+
     def _allreduce(self, t):
         self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM, group=self.group)
 
@@ -55,9 +88,14 @@ class TPDecoder:
     def decode(self, in_tokens, n_steps, pos0=0):
         """Like Model.decode: forced tokens first, then greedy; returns the greedy token after every step."""
         out = []
+        if self.graph is not None:
+            self.model.set_pos(pos0)
         for s in range(n_steps):
             if s < len(in_tokens):
                 self.model.set_token(in_tokens[s])
-            self.step(pos0 + s)
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.step(pos0 + s)
             out.append(self.model.get_token()[0])
         return out
