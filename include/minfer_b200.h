@@ -277,6 +277,9 @@ MI_API int mi_model_tp_region(const mi_model* model, int which, int layer, void*
  * waiting; the input token is the model's device-resident current token.  On a sharded model the
  * buffer a phase writes is zeroed first.  The caller interleaves its all-reduces on the same stream. */
 MI_API int mi_decode_launch(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
+/* The same range as ONE cooperative launch (grid barriers between the phases, as in the persistent loop): for a run of
+ * phases with no exchange between them - on a sharded model QKV, attention, O and gate/up of a layer. */
+MI_API int mi_decode_launch_fused(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
 /* Position argument of mi_decode_launch that means "the model's device-resident position": a launch sequence
  * enqueued with it does not depend on the step and can be captured once into a CUDA graph by the host program
  * (tensor-parallel steps: the phase launches and the NCCL all-reduces between them) and replayed per token. */

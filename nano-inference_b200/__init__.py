@@ -69,6 +69,7 @@ SIGNATURES = {
     "mi_model_load_gguf_tp": (_i32, [_vp, C.c_char_p, _i32, _i32, _i32, C.POINTER(_vp)]),
     "mi_model_tp_region": (_i32, [_vp, _i32, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
     "mi_decode_launch": (_i32, [_vp, _vp, _i32, _i32, _i32]),
+    "mi_decode_launch_fused": (_i32, [_vp, _vp, _i32, _i32, _i32]),
     "mi_model_set_token": (_i32, [_vp, _vp, _i32]),
     "mi_model_set_pos": (_i32, [_vp, _vp, _i32]),
     "mi_model_advance_pos": (_i32, [_vp, _vp, _i32]),
@@ -279,6 +280,9 @@ class Model:
 
     def launch(self, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_launch(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch")
+
+    def launch_fused(self, pos, ph0, ph1):
+        self.ctx.check(self.ctx.lib.mi_decode_launch_fused(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch_fused")
 
     def set_pos(self, pos):
         self.ctx.check(self.ctx.lib.mi_model_set_pos(self.ctx.h, self.h, int(pos)), "mi_model_set_pos")

@@ -554,7 +554,17 @@ extern "C" int mi_tp_pick(mi_ctx* ctx, mi_model* m, const void* gathered_dev, in
     return MI_OK;
 }
 
+static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int phase_end, bool fused);
+
 extern "C" int mi_decode_launch(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int phase_end) {
+    return launch_phases(ctx, m, pos, phase_begin, phase_end, false);
+}
+
+extern "C" int mi_decode_launch_fused(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int phase_end) {
+    return launch_phases(ctx, m, pos, phase_begin, phase_end, true);
+}
+
+static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int phase_end, bool fused) {
     if (!ctx) return MI_ERR_INVALID;
     if (!m) return set_error(ctx, MI_ERR_INVALID, "decode_launch: null model");
     const int nph = 5 * m->L + 1;
@@ -574,13 +584,20 @@ extern "C" int mi_decode_launch(mi_ctx* ctx, mi_model* m, int pos, int phase_beg
     for (int ph = phase_begin; ph < phase_end; ph++) {
         if (m->tp_world > 1 && ph < nph - 1) {
             // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce
+            // (no phase of a fused range reads a buffer that a later phase of the range writes)
             const int l = ph / 5, k = ph % 5;
             void* p = nullptr; int64_t nb = 0;
             if (k == 3) mi_model_tp_region(m, MI_TP_ACT, l, &p, &nb);               // QKV and O are computed in full by every GPU
             else if (k == 4) mi_model_tp_region(m, MI_TP_PART_DOWN, l, &p, &nb);
             if (p) MI_CUDA(ctx, cudaMemsetAsync(p, 0, (size_t)nb, ctx->stream));
         }
-        if ((st = dispatch_launch(ctx, m, P, 0, 1, ph, ph + 1, false))) return st;
+        if (!fused && (st = dispatch_launch(ctx, m, P, 0, 1, ph, ph + 1, false))) return st;
+    }
+    if (fused && phase_end > phase_begin) {
+        // one cooperative launch for the range: grid barriers between its phases, the weight ring running ahead across them
+        const bool coop = phase_end - phase_begin > 1;
+        if (coop) MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 64 * sizeof(unsigned), ctx->stream));
+        if ((st = dispatch_launch(ctx, m, P, 0, 1, phase_begin, phase_end, coop))) return st;
     }
     return MI_OK;
 }

@@ -74,12 +74,12 @@ class TPDecoder:
         """One decode step at position pos from the model's current token; leaves the next token current."""
         m, L = self.model, self.L
         if self.world == 1:
-            m.launch(pos, 0, 5 * L + 1)
+            m.launch_fused(pos, 0, 5 * L + 1)
             return
         for l in range(L):
             # QKV, attention and the O projection are computed in full by every rank; the two large projections
             # are sharded: one all-reduce after gate/up (the quantized activations), one after down (its partial sums)
-            m.launch(pos, 5 * l, 5 * l + 4); self._allreduce(self.r_act)
+            m.launch_fused(pos, 5 * l, 5 * l + 4); self._allreduce(self.r_act)       # one cooperative launch for the four phases
             m.launch(pos, 5 * l + 4, 5 * l + 5); self._allreduce(self.r_down[l])
         m.launch(pos, 5 * L, 5 * L + 1)
         self.dist.all_gather_into_tensor(self.gathered, self.r_best, group=self.group)
