@@ -46,3 +46,31 @@ def test_fullsize_decode_matches_q8_oracle(ctx, pkg, tmp_path, preset, n_prompt,
             worst = max(worst, rel_err(logits[s].cpu().numpy(), lo))
     assert worst < 1e-3, f"logits deviate {worst:.2e}"
     m.free(); m2.free()
+
+
+@pytest.mark.parametrize("preset", ["1.5b", "3b"])
+def test_fullsize_engines_and_m_token_step_agree_bit_for_bit(ctx, pkg, tmp_path, preset):
+    """The 1.5B shape and the 3B shape (36 layers, hidden 2048, 16 / 2 heads, FFN 11008: the batched configuration's
+    model at batch 1): persistent kernel == kernel sequence == M-token step (8 and 16 tokens per weight pass) on the
+    logits of every position, as bits.  No oracle here - the CPU side would take minutes at this size."""
+    import torch
+    path = gu.make_synthetic(tmp_path / "m.gguf", preset, seed=77)
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    n = 24
+    seq = [int(t) for t in np.random.default_rng(77).integers(0, V, n)]
+    m = pkg.Model(ctx, path, n + 1)
+    ref = torch.zeros((n, V), dtype=torch.float32, device="cuda")
+    tok_ref, _ = m.decode(seq, n, 0, ref, pkg.DECODE_PERSISTENT)
+    lg = torch.zeros_like(ref)
+    tok, _ = m.decode(seq, n, 0, lg, pkg.DECODE_PER_PHASE)
+    assert tok == tok_ref and torch.equal(lg.view(torch.int32), ref.view(torch.int32)), "kernel sequence differs from the persistent kernel"
+    for M in (8, 16):
+        lg.zero_()
+        tok = []
+        for i in range(0, n, M):
+            part = seq[i:i + M]
+            o, _ = m.verify(part, i, lg[i:i + len(part)])
+            tok += o
+        assert tok == tok_ref and torch.equal(lg.view(torch.int32), ref.view(torch.int32)), f"M-token step (M={M}) differs from the decode"
+    m.free()
