@@ -588,6 +588,9 @@ def run_ours(args, rank, world, local_rank):
         tpmod = ge.load_submodule("tp")
         dec = tpmod.TPDecoder(pkg, model, dist)
         use_graph = os.environ.get("MINFER_TP_GRAPH", "1") != "0"
+        use_peer = os.environ.get("MINFER_TP_PEER", "1") != "0"
+        if use_peer:
+            dec.enable_peer_exchange()           # exchanges through peer memory (own kernel over NVLink) instead of NCCL
         if use_graph:
             dec.capture()
         warm = dec.decode(ids, PROMPT_LEN + warmup)            # untimed: prompt, then W greedy steps
@@ -620,8 +623,9 @@ def run_ours(args, rank, world, local_rank):
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
         L = cfg.n_layer
         launches = K * (5 * L + 1 + 1)
-        engine = (f"kernel sequence, one launch per phase; {2 * L + 1} NCCL collectives per token; "
-                  + ("one CUDA graph per token (launches + collectives)" if use_graph else "issued by the host"))
+        engine = (f"per layer one cooperative launch (QKV, attention, O, gate/up) and one launch (down); {2 * L + 1} exchanges per token "
+                  + ("through peer memory over NVLink (own kernel: push owned slice, flag, bounded wait)" if use_peer else "as NCCL all-reduces")
+                  + ("; one CUDA graph per token" if use_graph else "; issued by the host"))
         parallelism = f"tp{world}: rows of gate/up, down and lm_head sharded over {world} GPUs; QKV, attention and O replicated"
         dec.release()                       # the captured graph must be gone before the process group is destroyed
     clocks = sampler.stop() if sampler else None

@@ -280,6 +280,15 @@ MI_API int mi_decode_launch(mi_ctx* ctx, mi_model* model, int pos, int phase_beg
 /* The same range as ONE cooperative launch (grid barriers between the phases, as in the persistent loop): for a run of
  * phases with no exchange between them - on a sharded model QKV, attention, O and gate/up of a layer. */
 MI_API int mi_decode_launch_fused(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
+/* Exchange through peer memory instead of a collective library: every process calls mi_tp_ipc_handles (192 bytes out:
+ * CUDA IPC handles of its activation buffer, partial-sum buffer and flag block), the host program gathers the handles of all
+ * ranks ([world][192 bytes], rank order) and passes them to mi_tp_ipc_open.  From then on mi_tp_exchange(which, layer) - one
+ * small kernel - stores this GPU's slice of MI_TP_ACT / MI_TP_PART_DOWN / MI_TP_BEST into every peer's buffer over NVLink,
+ * flags the peers and waits (bounded; MI_ERR_TIMEOUT through mi_ctx_sync) for theirs; after MI_TP_BEST it also makes the
+ * overall greedy token current.  Every GPU issues the same sequence of exchanges.  Same bits as the all-reduce path. */
+MI_API int mi_tp_ipc_handles(mi_ctx* ctx, mi_model* model, void* out_host);
+MI_API int mi_tp_ipc_open(mi_ctx* ctx, mi_model* model, const void* all_host);
+MI_API int mi_tp_exchange(mi_ctx* ctx, mi_model* model, int which, int layer);
 /* Position argument of mi_decode_launch that means "the model's device-resident position": a launch sequence
  * enqueued with it does not depend on the step and can be captured once into a CUDA graph by the host program
  * (tensor-parallel steps: the phase launches and the NCCL all-reduces between them) and replayed per token. */

@@ -75,6 +75,9 @@ SIGNATURES = {
     "mi_model_advance_pos": (_i32, [_vp, _vp, _i32]),
     "mi_model_get_token": (_i32, [_vp, _vp, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     "mi_tp_pick": (_i32, [_vp, _vp, _vp, _i32]),
+    "mi_tp_ipc_handles": (_i32, [_vp, _vp, _vp]),
+    "mi_tp_ipc_open": (_i32, [_vp, _vp, _vp]),
+    "mi_tp_exchange": (_i32, [_vp, _vp, _i32, _i32]),
 }
 TP_QKV, TP_PART_O, TP_ACT, TP_PART_DOWN, TP_BEST = range(5)
 
@@ -280,6 +283,20 @@ class Model:
 
     def launch(self, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_launch(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch")
+
+    def tp_ipc_handles(self):
+        """192 bytes: CUDA IPC handles of this rank's exchanged buffers (numpy uint8)."""
+        import numpy as np
+        out = np.zeros(192, dtype=np.uint8)
+        self.ctx.check(self.ctx.lib.mi_tp_ipc_handles(self.ctx.h, self.h, _ptr(out)), "mi_tp_ipc_handles")
+        return out
+
+    def tp_ipc_open(self, all_handles):
+        """all_handles: numpy uint8 [world * 192], every rank's handles in rank order."""
+        self.ctx.check(self.ctx.lib.mi_tp_ipc_open(self.ctx.h, self.h, _ptr(all_handles)), "mi_tp_ipc_open")
+
+    def tp_exchange(self, which, layer=0):
+        self.ctx.check(self.ctx.lib.mi_tp_exchange(self.ctx.h, self.h, which, layer), "mi_tp_exchange")
 
     def launch_fused(self, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_launch_fused(self.ctx.h, self.h, pos, ph0, ph1), "mi_decode_launch_fused")

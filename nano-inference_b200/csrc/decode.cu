@@ -101,6 +101,7 @@ extern "C" int mi_model_free(mi_ctx* ctx, mi_model* m) {
     if (!m) return MI_OK;
     cudaSetDevice(m->device);
     cudaDeviceSynchronize();
+    for (void* p : m->ipc_opened) cudaIpcCloseMemHandle(p);
     for (void* p : m->allocs) cudaFree(p);
     for (void* g : m->vb.graph) if (g) cudaGraphExecDestroy((cudaGraphExec_t)g);
     if (m->ev0) cudaEventDestroy(m->ev0);
@@ -582,7 +583,7 @@ static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int
     P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = dev_pos ? 0 : pos; P.logits = nullptr; P.logits_stride = m->V;
     P.pos_dev = dev_pos ? m->d_pos : nullptr;
     for (int ph = phase_begin; ph < phase_end; ph++) {
-        if (m->tp_world > 1 && ph < nph - 1) {
+        if (m->tp_world > 1 && ph < nph - 1 && !m->tp_peer_on) {          // (peer exchange: every GPU writes only what it owns, nothing is summed)
             // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce
             // (no phase of a fused range reads a buffer that a later phase of the range writes)
             const int l = ph / 5, k = ph % 5;

@@ -45,6 +45,10 @@ struct mi_model {
     uint8_t* act_buf = nullptr;          // [act_q | act_d]
     float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
     int qkv_rows = 0;
+    int* tp_flags = nullptr;              // peer exchange: flags, epoch, gathered argmax candidates (see tp_peer.cu)
+    void* tp_peer[8][3] = {};             // per rank: activations, partial sums, flag block (own entries = local pointers)
+    bool tp_peer_on = false;
+    std::vector<void*> ipc_opened;        // peer mappings to close
     int* d_pos = nullptr;                 // device-resident position for position-free launch sequences
     std::vector<mi_weight> views;         // [4L+1] whole matrices in job order (QKV, O, gate/up, down per layer; lm_head), for the M-token step
     std::vector<mi::LayerPtrs> layer_ptrs;    // host copy of the per-layer norm / bias pointers

@@ -35,6 +35,19 @@ class TPDecoder:
             self.gathered = torch.zeros(8 * self.world, dtype=torch.uint8, device="cuda")
 
         self.graph = None
+        self.peer = False
+
+    def enable_peer_exchange(self):
+        """Exchange through peer memory (the library's own kernel over NVLink) instead of NCCL all-reduces: gathers every
+        rank's CUDA IPC handles once (the only collective used), then every exchange is one small kernel."""
+        import numpy as np
+        torch, m = self.torch, self.model
+        mine = torch.from_numpy(m.tp_ipc_handles()).cuda()
+        allh = torch.zeros(192 * self.world, dtype=torch.uint8, device="cuda")
+        self.dist.all_gather_into_tensor(allh, mine, group=self.group)
+        m.tp_ipc_open(np.ascontiguousarray(allh.cpu().numpy()))
+        self.dist.barrier(group=self.group)          # every rank has mapped every buffer before the first push
+        self.peer = True
 
     def capture(self):
         """Capture one step - the phase launches and the all-reduces between them - into a CUDA graph that reads the
@@ -75,6 +88,13 @@ class TPDecoder:
         m, L = self.model, self.L
         if self.world == 1:
             m.launch_fused(pos, 0, 5 * L + 1)
+            return
+        if self.peer:
+            for l in range(L):
+                m.launch_fused(pos, 5 * l, 5 * l + 4); m.tp_exchange(self.pkg.TP_ACT)
+                m.launch(pos, 5 * l + 4, 5 * l + 5); m.tp_exchange(self.pkg.TP_PART_DOWN, l)
+            m.launch(pos, 5 * L, 5 * L + 1)
+            m.tp_exchange(self.pkg.TP_BEST)              # also picks the overall greedy token
             return
         for l in range(L):
             # QKV, attention and the O projection are computed in full by every rank; the two large projections
