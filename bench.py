@@ -589,8 +589,33 @@ def run_ours(args, rank, world, local_rank):
         dec = tpmod.TPDecoder(pkg, model, dist)
         use_graph = os.environ.get("MINFER_TP_GRAPH", "1") != "0"
         use_peer = os.environ.get("MINFER_TP_PEER", "1") != "0"
+        fused = use_peer and os.environ.get("MINFER_TP_FUSED", "1") != "0"
         if use_peer:
             dec.enable_peer_exchange()           # exchanges through peer memory (own kernel over NVLink) instead of NCCL
+    if world > 1 and fused:
+        # the persistent kernel on every GPU, the exchange with the other GPUs inside it (CTA 0, between two grid barriers):
+        # one cooperative launch per GPU for all timed steps, exactly the single-GPU measurement
+        pre, _ = dec.decode_persistent(ids, PROMPT_LEN, 0)
+        warm, _ = dec.decode_persistent([pre[-1]], warmup, PROMPT_LEN)
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        barrier()
+        gen, ms = dec.decode_persistent([warm[-1]], K, pos0)
+        barrier()
+        e2e_steps = min(K, 64)
+        tok = warm[-1]
+        barrier()
+        t0 = time.perf_counter()
+        for s in range(e2e_steps):                              # host token in, host token out, every step, on every rank
+            out, _ = dec.decode_persistent([tok], 1, pos0 + s)
+            tok = out[0]
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+        L = cfg.n_layer
+        launches = 1
+        engine = (f"persistent kernel on every GPU (one cooperative launch for all timed steps); {2 * L + 1} exchanges per token inside "
+                  "the kernel: CTA 0 stores the owned slice into every peer's buffer over NVLink, flags, waits (bounded)")
+        parallelism = f"tp{world}: rows of gate/up, down and lm_head sharded over {world} GPUs; QKV, attention and O replicated"
+    elif world > 1:
         if use_graph:
             dec.capture()
         warm = dec.decode(ids, PROMPT_LEN + warmup)            # untimed: prompt, then W greedy steps
@@ -628,6 +653,7 @@ def run_ours(args, rank, world, local_rank):
                   + ("; one CUDA graph per token" if use_graph else "; issued by the host"))
         parallelism = f"tp{world}: rows of gate/up, down and lm_head sharded over {world} GPUs; QKV, attention and O replicated"
         dec.release()                       # the captured graph must be gone before the process group is destroyed
+    per_token_call = world == 1 or fused
     clocks = sampler.stop() if sampler else None
     (ms, e2e_ms), _ = reduce_max_sum([ms, e2e_ms], [0.0])
     model.free()
@@ -664,8 +690,8 @@ def run_ours(args, rank, world, local_rank):
         "gemv_roofline": gemv_roofline(stacks, kern_ms, peak, peak_kind),
         "kernel_sequence_engine_tok_s": round(1e3 / ms_seq, 1) if ms_seq else None,
         "cpu_baseline": {"value": round(cpu_v, 4), "unit": "tok/s", "cores": cpu_threads, "kind": cpu_kind, "sample": cpu_desc},
-        "e2e": {"value": round(1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 if world == 1 else 0, "d2h_bytes_per_step": 4 if world == 1 else 8,
-                "api": "mi_decode(n_steps=1) per token: host token id in, host token id out, one launch and one sync per step" if world == 1
+        "e2e": {"value": round(1e3 / e2e_ms, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 if per_token_call else 0, "d2h_bytes_per_step": 4 if per_token_call else 8,
+                "api": "mi_decode(n_steps=1) per token (on every GPU): host token id in, host token id out, one launch and one sync per step" if per_token_call
                        else "TPDecoder.step + mi_model_get_token per token: the greedy token is read back to the host after every step"},
         "gpu_launches": launches, "clocks": clocks, "first_tokens": gen[:8],
     }

@@ -434,6 +434,22 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
     }
     if (n_forced) MI_CUDA(ctx, cudaMemcpyAsync(m->d_in_tokens, in_tokens_host, (size_t)n_forced * 4, cudaMemcpyHostToDevice, ctx->stream));
     DecodeParams P = m->P;
+    if (m->tp_world > 1) {
+        // a sharded model decodes through this entry point only with the exchange inside the kernel (peer memory mapped,
+        // persistent engine); every GPU must make the same call
+        if (!m->tp_peer_on || mode != MI_DECODE_PERSISTENT)
+            return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: a sharded model needs mi_tp_ipc_open and the persistent engine here (or mi_decode_launch + exchanges)");
+        TpPeerParams& T = P.tp;
+        T.on = 1; T.rank = m->tp_rank; T.world = m->tp_world;
+        mi_tp_partition(m->FF / 32, m->tp_rank, m->tp_world, &T.ff_g0, &T.ff_g1);
+        mi_tp_partition((m->E + 31) / 32, m->tp_rank, m->tp_world, &T.e_g0, &T.e_g1);
+        for (int r = 0; r < m->tp_world; r++) {
+            T.act_peer[r] = reinterpret_cast<uint8_t*>(m->tp_peer[r][0]);
+            T.part_peer[r] = reinterpret_cast<double*>(m->tp_peer[r][1]);
+            T.flags_peer[r] = reinterpret_cast<int*>(m->tp_peer[r][2]);
+        }
+        T.flags_local = m->tp_flags;
+    }
     P.in_tokens = m->d_in_tokens; P.n_forced = n_forced; P.out_tokens = m->d_out_tokens; P.pos0 = pos0;
     P.logits = logits_dev; P.logits_stride = m->V;
     const int nph = 5 * m->L + 1;

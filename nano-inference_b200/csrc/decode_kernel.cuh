@@ -82,6 +82,17 @@ struct Job {
 
 struct LayerPtrs { const float* attn_norm; const float* ffn_norm; const float* bqkv; };
 
+// Tensor parallelism inside the persistent kernel: peer pointers (CUDA IPC mappings of the other GPUs' buffers) for the
+// exchange that follows the gate/up, down and lm_head phases.  on == 0: single GPU, or exchanges done by the host program.
+struct TpPeerParams {
+    int on, rank, world;
+    int ff_g0, ff_g1, e_g0, e_g1;          // this GPU's row groups of the gate/up (FF/32 groups) and down (E/32 groups) jobs
+    uint8_t* act_peer[8];                  // [act_q | act_d] on every GPU
+    double* part_peer[8];                  // partial-sum buffer on every GPU
+    int* flags_peer[8];                    // flag block on every GPU: [8] flags by source, [8] epoch, [16..] candidates {float, int} by rank
+    int* flags_local;
+};
+
 struct DecodeParams {
     int L, E, FF, NH, NKV, HD, KVD, V;
     float eps;
@@ -112,6 +123,7 @@ struct DecodeParams {
     const int* pos_dev;              // optional: first position read from device memory instead (a captured launch sequence stays position-free)
     unsigned* bar; int* err;
     unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA 0 (see kProf*)
+    TpPeerParams tp;
 };
 
 // number of KV chunks for a causal range of Lp positions (host and device agree)
@@ -766,6 +778,73 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     }
 }
 
+// ---- exchange with the other GPUs (CTA 0, between two grid barriers) --------------------
+// Store what this GPU owns of the buffer the phase wrote into every peer's copy, publish the epoch number in every
+// peer's flag slot, wait (bounded) for the peers' numbers.  kind 3: gate/up activations, 4: down partial sums of layer
+// l, 5: argmax candidates, followed by the pick of the overall greedy token.  Returns false if a wait gave up.
+__device__ __forceinline__ bool tp_peer_exchange(const DecodeParams& P, const DecodeSmem& sm, int kind, int l, int step, int* ok_s) {
+    const TpPeerParams& T = P.tp;
+    const int tid = threadIdx.x;
+    int* epoch_p = T.flags_local + 8;
+    const int epoch = *reinterpret_cast<volatile int*>(epoch_p) + 1;
+    float* cand_local = reinterpret_cast<float*>(T.flags_local + 16);
+    if (kind == 5 && tid == 0) {                               // this GPU's candidate into its own slot first
+        cand_local[2 * T.rank] = __ldcg(P.best_val);
+        reinterpret_cast<int*>(cand_local)[2 * T.rank + 1] = __ldcg(P.cur_token);
+    }
+    __syncthreads();
+    for (int p = 0; p < T.world; p++) {
+        if (p == T.rank) continue;
+        if (kind == 3) {
+            const int4* s = reinterpret_cast<const int4*>(P.act_q + (size_t)T.ff_g0 * 32);
+            int4* d = reinterpret_cast<int4*>(T.act_peer[p] + (size_t)T.ff_g0 * 32);
+            for (int i = tid; i < (T.ff_g1 - T.ff_g0) * 2; i += DNT) d[i] = __ldcg(s + i);
+            const unsigned short* s2 = reinterpret_cast<const unsigned short*>(P.act_d) + T.ff_g0;
+            unsigned short* d2 = reinterpret_cast<unsigned short*>(T.act_peer[p] + P.FF) + T.ff_g0;
+            for (int i = tid; i < T.ff_g1 - T.ff_g0; i += DNT) d2[i] = __ldcg(s2 + i);
+        } else if (kind == 4) {
+            const Job& jb = sm.jobs[4 * l + 3];
+            const size_t off = (size_t)jb.part_off + (size_t)T.e_g0 * jb.ks * 32, cnt = (size_t)(T.e_g1 - T.e_g0) * jb.ks * 32;
+            const double2* s = reinterpret_cast<const double2*>(P.part + off);
+            double2* d = reinterpret_cast<double2*>(T.part_peer[p] + off);
+            for (size_t i = tid; i < cnt / 2; i += DNT) d[i] = __ldcg(s + i);
+        } else if (tid == 0) {
+            float* cp = reinterpret_cast<float*>(T.flags_peer[p] + 16);
+            cp[2 * T.rank] = cand_local[2 * T.rank];
+            reinterpret_cast<int*>(cp)[2 * T.rank + 1] = reinterpret_cast<int*>(cand_local)[2 * T.rank + 1];
+        }
+    }
+    __threadfence_system();                                    // this thread's peer stores are performed before the flag below
+    __syncthreads();
+    if (tid == 0) *ok_s = 1;
+    __syncthreads();
+    if (tid < T.world && tid != T.rank) {
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(T.flags_peer[tid] + T.rank), "r"(epoch) : "memory");
+        const unsigned long long t0 = gtime_ns();
+        int v;
+        for (unsigned it = 0;; it++) {
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(T.flags_local + tid) : "memory");
+            if (v - epoch >= 0) break;
+            if ((it & 63u) == 63u && gtime_ns() - t0 > kWaitBudgetNs) { *ok_s = 0; break; }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        *epoch_p = epoch;
+        if (kind == 5 && *ok_s) {                              // the overall greedy token: largest value, lowest id on ties
+            float b = __ldcg(cand_local); int t = __ldcg(reinterpret_cast<int*>(cand_local) + 1);
+            for (int r = 1; r < T.world; r++) {
+                const float v = __ldcg(cand_local + 2 * r); const int ix = __ldcg(reinterpret_cast<int*>(cand_local) + 2 * r + 1);
+                if (v > b || (v == b && ix < t)) { b = v; t = ix; }
+            }
+            __stcg(P.cur_token, t); __stcg(P.best_val, b);
+            P.out_tokens[step] = t;
+        }
+    }
+    __syncthreads();
+    return *ok_s != 0;
+}
+
 // ---- the kernel ---------------------------------------------------------------------
 template <int HD, int G>
 __global__ void __launch_bounds__(DNT, 1)
@@ -935,7 +1014,17 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             prof_mark(P, tp, 2 * k + 1);
             if (!ok) break;
             const bool last = (step == step1 - 1) && (ph == ph1 - 1);
-            if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
+            if (P.tp.on && k >= 3) {
+                // sharded phase: all CTAs' rows are in local memory -> CTA 0 exchanges with the other GPUs -> everybody goes on
+                ok = grid_barrier(P.bar, bar_gen, &s_ok);
+                if (ok && blockIdx.x == 0) {
+                    __shared__ int s_xok;
+                    ok = tp_peer_exchange(P, sm, k, l, step, &s_xok);
+                }
+                ok = __syncthreads_and(ok ? 1 : 0) != 0;
+                if (!ok) break;
+                if (!last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
+            } else if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
             prof_mark(P, tp, kProfBarrier);
         }
     }

@@ -105,6 +105,12 @@ class TPDecoder:
         self.dist.all_gather_into_tensor(self.gathered, self.r_best, group=self.group)
         m.tp_pick(self.gathered, self.world)
 
+    def decode_persistent(self, in_tokens, n_steps, pos0=0):
+        """All steps in ONE cooperative launch per GPU, the exchanges done inside the kernel over peer memory
+        (enable_peer_exchange first; every rank makes the same call).  Returns (greedy tokens, device milliseconds)."""
+        assert self.world == 1 or self.peer, "enable_peer_exchange() first"
+        return self.model.decode(in_tokens, n_steps, pos0, None, self.pkg.DECODE_PERSISTENT)
+
     def decode(self, in_tokens, n_steps, pos0=0):
         """Like Model.decode: forced tokens first, then greedy; returns the greedy token after every step."""
         out = []

@@ -38,13 +38,14 @@ def main():
     dec.capture()
     got_peer_graph = dec.decode(prompt, n_steps)
     dec.release()                                # before the process group goes away
+    got_fused, _ = dec.decode_persistent(prompt, n_steps)   # one launch per GPU, the exchange inside the kernel
     h_tp = m.state("h_mid", np.float32, m.config.n_embd)
     ok = True
     if rank == 0:
         ref = pkg.Model(ctx, path, n_steps + 2)
         want, _ = ref.decode(prompt, n_steps, 0, None, pkg.DECODE_PER_PHASE)
         h_ref = ref.state("h_mid", np.float32, ref.config.n_embd)
-        ok = got == want and got_graph == want and got_peer == want and got_peer_graph == want and np.array_equal(h_tp, h_ref)
+        ok = got == want and got_graph == want and got_peer == want and got_peer_graph == want and got_fused == want and np.array_equal(h_tp, h_ref)
         print("TP_PARITY", "OK" if ok else f"MISMATCH got={got} want={want}", f"world={world} steps={n_steps}", flush=True)
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
