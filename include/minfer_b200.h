@@ -285,7 +285,10 @@ MI_API int mi_decode_launch_fused(mi_ctx* ctx, mi_model* model, int pos, int pha
  * ranks ([world][192 bytes], rank order) and passes them to mi_tp_ipc_open.  From then on mi_tp_exchange(which, layer) - one
  * small kernel - stores this GPU's slice of MI_TP_ACT / MI_TP_PART_DOWN / MI_TP_BEST into every peer's buffer over NVLink,
  * flags the peers and waits (bounded; MI_ERR_TIMEOUT through mi_ctx_sync) for theirs; after MI_TP_BEST it also makes the
- * overall greedy token current.  Every GPU issues the same sequence of exchanges.  Same bits as the all-reduce path. */
+ * overall greedy token current.  Every GPU issues the same sequence of exchanges.  Same bits as the all-reduce path.
+ * Once mi_tp_ipc_open has run, mi_decode(..., MI_DECODE_PERSISTENT, ...) works on the sharded model too - called with the
+ * same arguments on every GPU, it runs the whole generation as one cooperative launch per GPU and does these exchanges
+ * inside the kernel (CTA 0, between two grid barriers, bounded waits). */
 MI_API int mi_tp_ipc_handles(mi_ctx* ctx, mi_model* model, void* out_host);
 MI_API int mi_tp_ipc_open(mi_ctx* ctx, mi_model* model, const void* all_host);
 MI_API int mi_tp_exchange(mi_ctx* ctx, mi_model* model, int which, int layer);
