@@ -12,7 +12,7 @@
 
 using namespace mi;
 
-namespace mi { const void* decode_kernel_prof(int HD, int G); }
+namespace mi { const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); }
 
 namespace {
 
@@ -71,7 +71,9 @@ int plan_ks(int kind, int groups, int nt, int grid) {
 
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
     void (*kern)(DecodeParams, int, int, int, int) = nullptr;
-    if (P.prof) {                                   // the instrumented build (decode_prof.cu)
+    if (P.tp.on) {                                  // the build with the exchange between GPUs inside (decode_tp.cu)
+        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_tp(m->HD, m->G)));
+    } else if (P.prof) {                            // the instrumented build (decode_prof.cu)
         kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_prof(m->HD, m->G)));
     } else {
         #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;

@@ -47,8 +47,15 @@
 #ifndef MI_PROF
 #define MI_PROF 0
 #endif
+// A third build (MI_TP 1) adds the exchange with the other GPUs inside the kernel; the single-GPU build does not carry
+// that code either.
+#ifndef MI_TP
+#define MI_TP 0
+#endif
 #if MI_PROF
 #define MI_KVARIANT prof
+#elif MI_TP
+#define MI_KVARIANT tpx
 #else
 #define MI_KVARIANT fast
 #endif
@@ -778,6 +785,7 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
     }
 }
 
+#if MI_TP
 // ---- exchange with the other GPUs (CTA 0, between two grid barriers) --------------------
 // Store what this GPU owns of the buffer the phase wrote into every peer's copy, publish the epoch number in every
 // peer's flag slot, wait (bounded) for the peers' numbers.  kind 3: gate/up activations, 4: down partial sums of layer
@@ -844,6 +852,7 @@ __device__ __forceinline__ bool tp_peer_exchange(const DecodeParams& P, const De
     __syncthreads();
     return *ok_s != 0;
 }
+#endif  // MI_TP
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int HD, int G>
@@ -1014,6 +1023,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             prof_mark(P, tp, 2 * k + 1);
             if (!ok) break;
             const bool last = (step == step1 - 1) && (ph == ph1 - 1);
+#if MI_TP
             if (P.tp.on && k >= 3) {
                 // sharded phase: all CTAs' rows are in local memory -> CTA 0 exchanges with the other GPUs -> everybody goes on
                 ok = grid_barrier(P.bar, bar_gen, &s_ok);
@@ -1024,7 +1034,9 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 ok = __syncthreads_and(ok ? 1 : 0) != 0;
                 if (!ok) break;
                 if (!last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
-            } else if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
+            } else
+#endif
+            if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
             prof_mark(P, tp, kProfBarrier);
         }
     }
