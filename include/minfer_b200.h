@@ -72,6 +72,12 @@ MI_API int mi_ctx_set_stream(mi_ctx* ctx, void* cuda_stream);
  * bounded wait gave up) and clear it. */
 MI_API int mi_ctx_sync(mi_ctx* ctx);
 MI_API const char* mi_last_error(const mi_ctx* ctx);
+/* Time budget, in nanoseconds of the GPU's global timer, of every device-side wait of the
+ * decode kernel (a consumer polling for another CTA's or another GPU's tagged words); default
+ * 2 s.  When a wait runs out the kernel stops, drains its outstanding bulk copies and records
+ * MI_ERR_TIMEOUT; mi_ctx_sync reports it and the next call starts clean.  The reference spins
+ * without a bound (src/mega.cu:126-134); a bounded wait with a status has no counterpart there. */
+MI_API int mi_ctx_set_wait_budget_ns(mi_ctx* ctx, unsigned long long ns);
 /* Number of SMs the context sizes its grids for. */
 MI_API int mi_ctx_sm_count(const mi_ctx* ctx);
 
@@ -221,6 +227,11 @@ MI_API int mi_model_state_ptr(const mi_model* model, int which, void** ptr, int6
  * src/cuda_infer.cu:1031-1201 and the mega kernel of src/mega.cu:597-903. */
 MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
                      int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms);
+/* Test hook for the time-out path: from now on the producers of phase `phase` (5 * layer + kind;
+ * 5 * n_layer = lm_head) compute but publish nothing, so the waits of that phase's consumers run
+ * out after the context's wait budget and the call returns MI_ERR_TIMEOUT - nothing hangs or
+ * faults.  -1 restores normal operation.  No counterpart in the reference. */
+MI_API int mi_model_debug_drop_phase(mi_model* model, int phase);
 /* Run phases [phase_begin, phase_end) of one step (5 per layer: QKV, attention, O,
  * gate/up, down; then the lm_head) one launch each, leaving the state buffers for
  * inspection.  For per-phase parity checks. */

@@ -40,6 +40,8 @@ SIGNATURES = {
     "mi_ctx_set_stream": (_i32, [_vp, _vp]),
     "mi_ctx_sync": (_i32, [_vp]),
     "mi_last_error": (C.c_char_p, [_vp]),
+    "mi_ctx_set_wait_budget_ns": (_i32, [_vp, C.c_uint64]),
+    "mi_model_debug_drop_phase": (_i32, [_vp, _i32]),
     "mi_ctx_sm_count": (_i32, [_vp]),
     "mi_device_malloc": (_i32, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "mi_device_free": (_i32, [_vp, _vp]),
@@ -164,6 +166,10 @@ class Context:
 
     def sync(self):
         self.check(self.lib.mi_ctx_sync(self.h), "mi_ctx_sync")
+
+    def set_wait_budget_ns(self, ns):
+        """Time budget of the decode kernel's device-side waits (default 2 s)."""
+        self.check(self.lib.mi_ctx_set_wait_budget_ns(self.h, int(ns)), "mi_ctx_set_wait_budget_ns")
 
     # ---- weights
     def upload_q4_0(self, raw_host, rows, cols, count=1):
@@ -317,6 +323,10 @@ class Model:
 
     def tp_pick(self, gathered, world):
         self.ctx.check(self.ctx.lib.mi_tp_pick(self.ctx.h, self.h, _ptr(gathered), world), "mi_tp_pick")
+
+    def debug_drop_phase(self, phase):
+        """Test hook: the producers of `phase` publish nothing (its consumers' waits then run out); -1 = normal."""
+        self.ctx.check(self.ctx.lib.mi_model_debug_drop_phase(self.h, int(phase)), "mi_model_debug_drop_phase")
 
     def run_phases(self, token, pos, ph0, ph1):
         self.ctx.check(self.ctx.lib.mi_decode_phases(self.ctx.h, self.h, token, pos, ph0, ph1), "mi_decode_phases")

@@ -131,10 +131,20 @@ extern "C" int mi_ctx_sync(mi_ctx* ctx) {
     int err = 0;
     MI_CUDA(ctx, cudaMemcpy(&err, ctx->d_err, sizeof(int), cudaMemcpyDeviceToHost));
     if (err != 0) {
+        // a kernel that gave up may have left the self-resetting arrival counters of the split-K GEMV partly counted
+        ctx->errors_reported++;
         MI_CUDA(ctx, cudaMemset(ctx->d_err, 0, sizeof(int)));
+        if (ctx->counters) MI_CUDA(ctx, cudaMemset(ctx->counters, 0, ctx->n_counters * sizeof(unsigned)));
         MI_CUDA(ctx, cudaStreamSynchronize(cudaStreamLegacy));
         return set_error(ctx, err, "device reported: %s", mi_strerror(err));
     }
+    return MI_OK;
+}
+
+extern "C" int mi_ctx_set_wait_budget_ns(mi_ctx* ctx, unsigned long long ns) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (ns == 0) return set_error(ctx, MI_ERR_INVALID, "wait budget must be positive");
+    ctx->wait_ns = ns;
     return MI_OK;
 }
 

@@ -12,7 +12,10 @@
 
 using namespace mi;
 
-namespace mi { const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); }
+namespace mi {
+const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G);
+int reset_after_error(mi_ctx* ctx, mi_model* m);
+}
 
 namespace {
 
@@ -60,13 +63,15 @@ int alloc_tiled(mi_ctx* ctx, mi_model* m, int64_t rows, int64_t cols, uint8_t** 
 }
 
 // Cross-CTA K-split of a per-layer job.  A job whose result feeds an in-phase epilogue
-// (QKV: bias + RoPE + stores; gate/up: SwiGLU + q8_0) is never split across CTAs: its
-// eight warps already share every unit.  The O and down projections only emit partial
-// sums for the next prologue, so they are split until every CTA has a unit.
+// (QKV: bias + RoPE; gate/up: SwiGLU + q8_0) is never split across CTAs: its eight warps
+// already share every unit, and so is the O projection (measured: 6 tiles per row group, one
+// per warp, gains nothing from a split).  The down projection (35 tiles per row group at the
+// 1.5B shape, 48 row groups for 148 CTAs) is split until every CTA has a unit; the CTA of
+// split 0 collects the other splits' partial sums (see run_cta_job).
 int plan_ks(int kind, int groups, int nt, int grid) {
-    if (kind != JOB_DOWN) return 1;      // measured: the O projection (6 tiles per row group: one per warp) gains nothing from a split
+    if (kind != JOB_DOWN) return 1;
     int ks = grid / std::max(groups, 1);
-    return std::max(1, std::min(std::min(ks, nt), 4));     // the consumer prologue folds at most four partials per row
+    return std::max(1, std::min(std::min(ks, nt), kMaxKSplit));
 }
 
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
@@ -81,18 +86,18 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
         #undef MI_PICK
     }
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: head_dim %d with %d query heads per kv head is not instantiated", m->HD, m->G);
-    static const void* attr_done[16] = {nullptr};
-    if (attr_done[ctx->device & 15] != (const void*)kern) {
+    // the opt-in shared-memory size is a property of (device, kernel): raise it whenever this model needs more than any before
+    static const void* attr_kern[16] = {nullptr};
+    static size_t attr_smem[16] = {0};
+    if (attr_kern[ctx->device & 15] != (const void*)kern || attr_smem[ctx->device & 15] < m->smem) {
         MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem));
-        attr_done[ctx->device & 15] = (const void*)kern;
+        attr_kern[ctx->device & 15] = (const void*)kern; attr_smem[ctx->device & 15] = m->smem;
     }
-    if (coop) {
-        void* args[] = {(void*)&P, &step0, &step1, &ph0, &ph1};
-        MI_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)kern, dim3(m->grid), dim3(DNT), args, m->smem, ctx->stream));
-    } else {
-        kern<<<m->grid, DNT, m->smem, ctx->stream>>>(P, step0, step1, ph0, ph1);
-        MI_CUDA(ctx, cudaGetLastError());
-    }
+    // Always a cooperative launch: CTAs wait for one another's tagged words inside every phase range (the K-split fold
+    // of the down projection, the greedy pick over all CTAs' candidates), so all of them must be resident together.
+    (void)coop;
+    void* args[] = {(void*)&P, &step0, &step1, &ph0, &ph1};
+    MI_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)kern, dim3(m->grid), dim3(DNT), args, m->smem, ctx->stream));
     return MI_OK;
 }
 
@@ -152,7 +157,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         return set_error(ctx, MI_ERR_FORMAT, "model: missing qwen2.* metadata or tokenizer.ggml.tokens");
     if (m->E % m->NH || m->NH % m->NKV) return set_error(ctx, MI_ERR_FORMAT, "model: head counts do not divide");
     m->HD = m->E / m->NH; m->KVD = m->NKV * m->HD; m->G = m->NH / m->NKV;
-    if (m->E % 32 || m->FF % 32 || m->HD % 32 || m->G > DNW || m->L > 64 || m->E > 16384 || m->FF > 32768)
+    if (m->E % 32 || m->FF % 32 || m->HD % 32 || m->HD > 128 || m->G > DNW || m->L > 64 || m->E > 8192 || m->FF > 32768)
         return set_error(ctx, MI_ERR_UNSUPPORTED, "model: shape outside this path (E, FF, head_dim multiples of 32; <= 8 query heads per kv head)");
     m->max_seq = max_seq;
     m->grid = ctx->sm_count;
@@ -216,7 +221,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     std::vector<LayerPtrs> lp(L);
     const int qkv_rows = NQ + 2 * KVD, W = m->grid * DNW;
     m->qkv_rows = qkv_rows;
-    int rot = 0, wrot = 0; size_t part_off = 0;
+    int rot = 0, wrot = 0;
     auto add_job = [&](const uint8_t* base, int groups, int cols, int nacc, int kind, int layer) {
         Job jb{}; jb.nb = cols / 32; jb.kb = choose_kb(jb.nb); jb.nt = jb.nb / jb.kb;
         jb.nacc = nacc; jb.kind = kind; jb.layer = layer;
@@ -231,11 +236,10 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         jb.g_off = g0; jb.groups = g1 - g0;
         jb.base = base + (size_t)g0 * nacc * jb.nt * tile_bytes(jb.kb);
         jb.ks = plan_ks(kind, replicated ? groups : (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
-        const char* force = kind == JOB_O ? getenv("MINFER_KS_O") : kind == JOB_DOWN ? getenv("MINFER_KS_DOWN") : nullptr;   // tuning knobs
-        if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), 4));
+        const char* force = kind == JOB_DOWN ? getenv("MINFER_KS_DOWN") : nullptr;   // tuning knob
+        if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), kMaxKSplit));
+        if (jb.ks >= m->grid) jb.ks = std::max(1, m->grid - 1);       // the CTAs of a row group's splits must be distinct
         jb.n_units = jb.groups * jb.ks;
-        jb.part_off = (int)part_off;
-        if (kind == JOB_O || kind == JOB_DOWN) part_off += (size_t)groups * jb.ks * 32;
         if (kind == JOB_LM) { jb.rot = 0; jb.wrot = 0; }
         else {
             // successive jobs start where the previous one stopped, over CTAs and over the warps of a CTA
@@ -356,19 +360,37 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     P.rope_freq = d_freq;
 
     // ---- state
-    m->part_count = part_off;
-    if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.qkv_out, (size_t)(qkv_rows + 31) / 32 * 32)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
-        (st = dev_alloc(ctx, m, &P.att_q, NQ)) || (st = dev_alloc(ctx, m, &P.att_d, NQ / 32)) ||
-        (st = dev_alloc(ctx, m, &m->act_buf, (size_t)FF + (size_t)FF / 32 * 2)) ||
+    // the exchange block: every vector one CTA hands to another, as tagged 8-byte words (layout: XwLayout)
+    {
+        XwLayout& x = P.xo;
+        int off = 0;
+        auto take = [&](int words) { const int o = off; off += (words + 1) / 2 * 2; return o; };     // every vector 16-byte aligned
+        x.qkv = take((qkv_rows + 31) / 32 * 32);
+        x.att = take(q8_words(NQ));
+        x.o = take((E + 31) / 32 * 32);
+        x.act = take(q8_words(FF));
+        x.down = take((E + 31) / 32 * 32);
+        x.dpart = take((E + 31) / 32 * (kMaxKSplit - 1) * 64);
+        x.cand = take(kMaxWorldTP * m->grid * 2);
+        x.total = off;
+    }
+    if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
+        (st = dev_alloc(ctx, m, &P.xw, (size_t)P.xo.total)) ||
         (st = dev_alloc(ctx, m, &P.kc, (size_t)L * max_seq * KVD)) || (st = dev_alloc(ctx, m, &P.vc, (size_t)L * max_seq * KVD)) ||
         (st = dev_alloc(ctx, m, &P.attn_part, (size_t)m->NH * m->max_chunks * (HD + 2))) || (st = dev_alloc(ctx, m, &P.attn_cnt, m->NH)) ||
-        (st = dev_alloc(ctx, m, &P.part, part_off)) ||
-        (st = dev_alloc(ctx, m, &P.cand_val, m->grid)) || (st = dev_alloc(ctx, m, &P.cand_idx, m->grid)) ||
-        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &P.cand_cnt, 1)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) || (st = dev_alloc(ctx, m, &P.bar, 64)) ||
-        (st = dev_alloc(ctx, m, &m->d_pos, 1)))
+        (st = dev_alloc(ctx, m, &P.prof, kProfSlots)) || (st = dev_alloc(ctx, m, &m->best_buf, 2)) ||
+        (st = dev_alloc(ctx, m, &m->d_pos, 2)))
         return st;
-    P.act_q = reinterpret_cast<int8_t*>(m->act_buf); P.act_d = reinterpret_cast<__half*>(m->act_buf + FF);   // one run: exchanged as one piece
     P.best_val = m->best_buf; P.cur_token = reinterpret_cast<int*>(m->best_buf + 1);                        // {value, token}: exchanged as one piece
+    // the tag counter lives on the device and the kernel advances it itself (a launch that completes a step leaves it
+    // past every tag it used): replayed launch sequences and calls after a failed one always get fresh tags.
+    // Words start as zero, so the counter starts at 1.
+    {
+        const int init[2] = {0, 1};
+        MI_CUDA(ctx, cudaMemcpy(m->d_pos, init, sizeof(init), cudaMemcpyHostToDevice));
+    }
+    P.epoch_dev = reinterpret_cast<unsigned*>(m->d_pos + 1);
+    P.drop_phase = -1;
     P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
     m->prof_buf = P.prof;
     if (!getenv("MINFER_PROFILE")) P.prof = nullptr;         // the buffer exists either way; kernels only write it when asked
@@ -400,12 +422,12 @@ extern "C" int mi_model_state_ptr(const mi_model* m, int which, void** ptr, int6
     switch (which) {
         case MI_STATE_H: *ptr = P.h_in; if (bytes) *bytes = (int64_t)m->E * 4; break;
         case MI_STATE_H_MID: *ptr = P.h_mid; if (bytes) *bytes = (int64_t)m->E * 4; break;
-        case MI_STATE_Q: *ptr = P.qkv_out; if (bytes) *bytes = (int64_t)(NQ + 2 * m->KVD) * 4; break;
+        case MI_STATE_Q: *ptr = P.xw + P.xo.qkv; if (bytes) *bytes = (int64_t)(NQ + 2 * m->KVD) * 8; break;
         case MI_STATE_ATT: *ptr = P.att; if (bytes) *bytes = (int64_t)NQ * 4; break;
         case MI_STATE_KCACHE: *ptr = P.kc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
         case MI_STATE_VCACHE: *ptr = P.vc; if (bytes) *bytes = (int64_t)m->L * m->max_seq * m->KVD * 2; break;
-        case MI_STATE_ACT_Q: *ptr = P.act_q; if (bytes) *bytes = (int64_t)m->FF; break;
-        case MI_STATE_ACT_D: *ptr = P.act_d; if (bytes) *bytes = (int64_t)m->FF / 32 * 2; break;
+        case MI_STATE_ACT_Q: *ptr = P.xw + P.xo.act; if (bytes) *bytes = (int64_t)m->FF / 4 * 8; break;
+        case MI_STATE_ACT_D: *ptr = P.xw + P.xo.act + m->FF / 4; if (bytes) *bytes = (int64_t)m->FF / 32 * 8; break;
         case MI_STATE_PROFILE: *ptr = m->prof_buf; if (bytes) *bytes = (int64_t)kProfSlots * 8; break;
         default: return MI_ERR_INVALID;
     }
@@ -420,7 +442,7 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
     if (n_steps == 0) { if (elapsed_ms) *elapsed_ms = 0.f; return MI_OK; }
     if (n_forced > n_steps) n_forced = n_steps;
     if (n_forced > 0 && !in_tokens_host) return set_error(ctx, MI_ERR_INVALID, "decode: null input tokens");
-    if (pos0 + n_steps > m->max_seq)
+    if ((long long)pos0 + n_steps > m->max_seq)
         return set_error(ctx, MI_ERR_LIMIT, "decode: positions %d..%d exceed the KV cache of %d", pos0, pos0 + n_steps - 1, m->max_seq);
     for (int i = 0; i < n_forced; i++)
         if (in_tokens_host[i] < 0 || in_tokens_host[i] >= m->V) return set_error(ctx, MI_ERR_INVALID, "decode: token id %d out of range", in_tokens_host[i]);
@@ -443,21 +465,15 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
             return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: a sharded model needs mi_tp_ipc_open and the persistent engine here (or mi_decode_launch + exchanges)");
         TpPeerParams& T = P.tp;
         T.on = 1; T.rank = m->tp_rank; T.world = m->tp_world;
-        mi_tp_partition(m->FF / 32, m->tp_rank, m->tp_world, &T.ff_g0, &T.ff_g1);
-        mi_tp_partition((m->E + 31) / 32, m->tp_rank, m->tp_world, &T.e_g0, &T.e_g1);
-        for (int r = 0; r < m->tp_world; r++) {
-            T.act_peer[r] = reinterpret_cast<uint8_t*>(m->tp_peer[r][0]);
-            T.part_peer[r] = reinterpret_cast<double*>(m->tp_peer[r][1]);
-            T.flags_peer[r] = reinterpret_cast<int*>(m->tp_peer[r][2]);
-        }
-        T.flags_local = m->tp_flags;
+        for (int r = 0; r < m->tp_world; r++) T.xw_peer[r] = reinterpret_cast<unsigned long long*>(m->tp_peer[r][0]);
     }
+    P.wait_ns = ctx->wait_ns;
+    if ((st = mi::reset_after_error(ctx, m))) return st;
     P.in_tokens = m->d_in_tokens; P.n_forced = n_forced; P.out_tokens = m->d_out_tokens; P.pos0 = pos0;
     P.logits = logits_dev; P.logits_stride = m->V;
     const int nph = 5 * m->L + 1;
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
     if (mode == MI_DECODE_PERSISTENT) {
-        MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 64 * sizeof(unsigned), ctx->stream));
         if ((st = dispatch_launch(ctx, m, P, 0, n_steps, 0, nph, true))) return st;
     } else if (mode == MI_DECODE_PER_PHASE) {
         for (int s = 0; s < n_steps; s++) {
@@ -498,6 +514,10 @@ extern "C" int mi_decode_phases(mi_ctx* ctx, mi_model* m, int32_t token, int pos
 namespace {
 __global__ void set_token_kernel(int* dst, int tok) { *dst = tok; }
 __global__ void add_int_kernel(int* dst, int delta) { *dst += delta; }
+__global__ void reset_counters_kernel(unsigned* a, int na, unsigned* b, int nb) {
+    for (int i = threadIdx.x; i < na; i += blockDim.x) a[i] = 0;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) b[i] = 0;
+}
 // gathered: [world] x {float best value, int token}; the largest value wins, the lowest token id on ties
 // (the rule of src/cpu_infer.cpp:153-154 applied across the GPUs' row ranges)
 __global__ void tp_pick_kernel(const float* gathered, int world, float* best_val, int* cur_token) {
@@ -514,15 +534,12 @@ extern "C" int mi_model_tp_region(const mi_model* m, int which, int layer, void*
     if (!m || !ptr || !bytes) return MI_ERR_INVALID;
     const DecodeParams& P = m->P;
     switch (which) {
-        case MI_TP_QKV: *ptr = P.qkv_out; *bytes = (int64_t)(m->qkv_rows + 31) / 32 * 32 * 4; return MI_OK;
-        case MI_TP_ACT: *ptr = m->act_buf; *bytes = (int64_t)m->FF + (int64_t)m->FF / 32 * 2; return MI_OK;
+        case MI_TP_QKV: *ptr = P.xw + P.xo.qkv; *bytes = (int64_t)(m->qkv_rows + 31) / 32 * 32 * 8; return MI_OK;
+        case MI_TP_ACT: *ptr = P.xw + P.xo.act; *bytes = (int64_t)q8_words(m->FF) * 8; return MI_OK;
         case MI_TP_BEST: *ptr = m->best_buf; *bytes = 8; return MI_OK;
-        case MI_TP_PART_O: case MI_TP_PART_DOWN: {
+        case MI_TP_PART_O: case MI_TP_PART_DOWN:
             if (layer < 0 || layer >= m->L) return MI_ERR_INVALID;
-            const Job& jb = m->jobs[4 * layer + (which == MI_TP_PART_O ? 1 : 3)];
-            const int total_groups = (m->E + 31) / 32;
-            *ptr = P.part + jb.part_off; *bytes = (int64_t)total_groups * jb.ks * 32 * 8; return MI_OK;
-        }
+            *ptr = P.xw + (which == MI_TP_PART_O ? P.xo.o : P.xo.down); *bytes = (int64_t)(m->E + 31) / 32 * 32 * 8; return MI_OK;
         default: return MI_ERR_INVALID;
     }
 }
@@ -600,6 +617,8 @@ static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int
     DecodeParams P = m->P;
     P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = dev_pos ? 0 : pos; P.logits = nullptr; P.logits_stride = m->V;
     P.pos_dev = dev_pos ? m->d_pos : nullptr;
+    P.wait_ns = ctx->wait_ns;
+    if ((st = mi::reset_after_error(ctx, m))) return st;
     for (int ph = phase_begin; ph < phase_end; ph++) {
         if (m->tp_world > 1 && ph < nph - 1 && !m->tp_peer_on) {          // (peer exchange: every GPU writes only what it owns, nothing is summed)
             // entries of the exchanged buffer that this GPU does not own must read zero before the all-reduce
@@ -613,10 +632,31 @@ static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int
         if (!fused && (st = dispatch_launch(ctx, m, P, 0, 1, ph, ph + 1, false))) return st;
     }
     if (fused && phase_end > phase_begin) {
-        // one cooperative launch for the range: grid barriers between its phases, the weight ring running ahead across them
-        const bool coop = phase_end - phase_begin > 1;
-        if (coop) MI_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 64 * sizeof(unsigned), ctx->stream));
-        if ((st = dispatch_launch(ctx, m, P, 0, 1, phase_begin, phase_end, coop))) return st;
+        // one cooperative launch for the range, the weight ring running ahead across its phases
+        if ((st = dispatch_launch(ctx, m, P, 0, 1, phase_begin, phase_end, true))) return st;
     }
+    return MI_OK;
+}
+
+// A kernel that gave up on a wait may have left the self-resetting arrival counters of the attention merge (decode loop
+// and M-token step) partly counted.  mi_ctx_sync counts the errors it reports; the first launch on a model after a new
+// one clears that model's counters.
+int mi::reset_after_error(mi_ctx* ctx, mi_model* m) {
+    if (m->errors_seen == ctx->errors_reported) return MI_OK;
+    m->errors_seen = ctx->errors_reported;
+    reset_counters_kernel<<<1, 256, 0, ctx->stream>>>(m->P.attn_cnt, m->NH, m->vb.attn_cnt, m->vb.attn_cnt ? 16 * m->NH : 0);
+    MI_CUDA(ctx, cudaGetLastError());
+    if (m->vb.amax_cnt) {
+        MI_CUDA(ctx, cudaMemsetAsync(m->vb.amax_cnt, 0, 16 * sizeof(unsigned), ctx->stream));
+        MI_CUDA(ctx, cudaMemsetAsync(m->vb.amax_key, 0, 16 * sizeof(unsigned long long), ctx->stream));
+    }
+    return MI_OK;
+}
+
+// Test hook: the producers of one phase (index 5 * layer + kind, or the lm_head phase 5 * n_layer) publish nothing from
+// now on, so that the waits of its consumers run out; -1 restores normal operation.
+extern "C" int mi_model_debug_drop_phase(mi_model* m, int phase) {
+    if (!m) return MI_ERR_INVALID;
+    m->P.drop_phase = phase;
     return MI_OK;
 }

@@ -1,31 +1,52 @@
 // The fused decode step for sm_100a: one persistent kernel that runs any range of
 // the per-token phases
-//     per layer:  QKV  (residual fold -> rmsnorm -> q8 -> GEMV -> +bias, RoPE, q / fp16 KV store)
+//     per layer:  QKV  (residual add -> rmsnorm -> q8 -> GEMV -> +bias, RoPE, q / k / v)
 //                 ATTN (split-KV attention over the fp16 cache, merge, -> q8)
-//                 O    (GEMV -> partial sums)
-//                 GU   (residual fold -> rmsnorm -> q8 -> gate & up GEMV -> SwiGLU -> q8)
-//                 DOWN (GEMV -> partial sums)
-//     finally:    LM   (residual fold -> rmsnorm -> q8 -> lm_head GEMV -> argmax)
+//                 O    (GEMV)
+//                 GU   (residual add -> rmsnorm -> q8 -> gate & up GEMV -> SwiGLU -> q8)
+//                 DOWN (GEMV, K-split over CTAs, folded by the split-0 CTA)
+//     finally:    LM   (residual add -> rmsnorm -> q8 -> lm_head GEMV -> argmax)
 // for any range of steps.  Launched with one phase per launch it is a plain
-// kernel sequence; launched cooperatively over all phases and steps it is the
-// persistent decode loop, phases separated by a bounded-wait grid barrier.
+// kernel sequence; launched cooperatively (all CTAs resident) over all phases and
+// steps it is the persistent decode loop.
+//
+// No grid barrier.  The reference's persistent kernel separates its phases by a
+// grid-wide barrier (src/mega.cu:123-134, five per layer).  Here every value that
+// one CTA hands to another travels as a TAGGED WORD: 8 bytes = {32-bit payload,
+// 32-bit tag}, written and read as one naturally aligned 64-bit access (single-copy
+// atomic).  The tag numbers the (step, phase) that produced the value.  A consumer
+// simply loads the words it needs and looks at their tags; words that are not there
+// yet are polled (bounded by a time budget).  There is no separate flag, hence no
+// release fence before it and no second round trip after it: a phase boundary costs
+// one store-to-load hop through the L2 instead of arrive + poll + reload, and a CTA
+// waits only for the values it actually consumes.  Buffers are reused every layer;
+// a word can only be overwritten after every reader has passed on, because the
+// writer's own inputs descend from outputs of those readers (each layer has phases
+// in which every CTA produces something that every CTA consumes).  A reader that
+// nevertheless fell behind would see a wrong tag and time out - never wrong data.
+// The same words, stored additionally into the other GPUs' copies of the buffers
+// over NVLink (plain 8-byte peer stores), are the whole tensor-parallel exchange.
+//
+// The residual stream lives in shared memory: every CTA adds the same projection
+// outputs to its own copy (the arithmetic is deterministic, all copies hold the
+// same bits), so it never travels.  CTA 0 also writes it to global memory for
+// launches that start in the middle of a step, and for inspection.
 //
 // Work split.  Every GEMV phase is a "job" over a tiled q4_0 matrix.  For the
 // per-layer matrices a unit is (32-row group [gate/up: a pair of groups], K-split)
 // and belongs to a CTA: its eight warps take the unit's tiles round-robin and
-// fold their double partial sums through shared memory, so no fence or atomic
-// sits on the critical path.  Where a job has fewer row groups than the grid has
-// CTAs (O and down projections) the K dimension is additionally split across
-// CTAs; those partial sums go to global scratch as doubles and are added by the
-// NEXT phase's prologue, behind the grid barrier that separates the phases
-// anyway.  The lm_head has thousands of row groups: there a unit is a row group
-// and belongs to one warp.
+// fold their double partial sums through shared memory.  The down projection has
+// fewer row groups than the grid has CTAs, so its K dimension is additionally split
+// across CTAs; splits 1.. hand their double partial sums (two tagged words each) to
+// the CTA of split 0, which adds them in split order and publishes the fp32 row.
+// The lm_head has thousands of row groups: there a unit is a row group and belongs
+// to one warp.
 //
 // Weight streaming.  The whole tile sequence of a warp - across phases, layers
 // and steps - follows from shapes and indices alone, so lane 0 of every warp
 // keeps a private shared-memory ring full with bulk copies that run ahead of
-// the barriers: weights are immutable, the HBM stream never waits for a phase
-// boundary, only for ring space.
+// the phase boundaries: weights are immutable, the HBM stream never waits for a
+// phase, only for ring space.
 //
 // Numerics follow the reference (paths relative to its root): quantizer
 // src/cuda_infer.cu:80-89; block dot src/mega.cu:151-165; RMSNorm / RoPE / SwiGLU /
@@ -35,20 +56,21 @@
 // values) is carried in double and rounded to fp32 once; exp, cos and sin come
 // from the double math library.  A q8_0 quantizer is discontinuous, so this is
 // what lets two engines (or two split / step / shard configurations of this one)
-// agree bit for bit: the fp32 value of a double-carried sum does not depend on
-// the order of its terms.  Each token is processed exactly as if it were alone.
+// agree bit for bit: every term of a GEMV sum is a multiple of 2^-48 (fp16 x fp16 x
+// integer), so while a sum stays below 2^5 in magnitude the double additions are
+// exact and the fp32 value cannot depend on their order; beyond that it has been
+// observed, not proved.  Each token is processed exactly as if it were alone.
 #pragma once
 #include "gemv_core.cuh"
 
-// The kernel exists in two builds.  The default one carries no profiling code at all: the timer marks that the
-// in-kernel profiler needs cost 6 % of the step when merely compiled in (they sit between the hot instructions of every
-// phase).  A translation unit that defines MI_PROF 1 before including this file gets the instrumented build; the two live in
-// different inline namespaces, so both can be linked into one library and picked at launch time.
+// The kernel exists in three builds.  The default one carries no profiling code and no peer stores.  A translation unit
+// that defines MI_PROF 1 before including this file gets the instrumented build (timer marks between the hot instructions
+// cost a few percent when merely compiled in); MI_TP 1 gives the tensor-parallel build, whose publishing stores also go to
+// the other GPUs.  The three live in different inline namespaces, so all can be linked into one library and picked at
+// launch time.
 #ifndef MI_PROF
 #define MI_PROF 0
 #endif
-// A third build (MI_TP 1) adds the exchange with the other GPUs inside the kernel; the single-GPU build does not carry
-// that code either.
 #ifndef MI_TP
 #define MI_TP 0
 #endif
@@ -68,9 +90,11 @@ constexpr int DS = 3;             // ring slots per warp
 constexpr int DSLOT = 4608;       // bytes per slot: the largest tile (8 blocks)
 constexpr int kAttnChunk = 64;    // smallest KV range worth its own CTA
 constexpr int kPerHeadAttnMax = 1024;   // up to this many cached positions a CTA handles one query head, beyond it a whole GQA group
+constexpr int kMaxKSplit = 4;     // cross-CTA K-splits of the down projection
+constexpr int kMaxWorldTP = 8;
 
-// profile slots: 2*k = staging of phase kind k, 2*k+1 = its main work; 12 = barrier, 13 = step prologue
-enum { kProfBarrier = 12, kProfStep = 13, kProfSlots = 32 };
+// profile slots: 2*k = staging of phase kind k, 2*k+1 = its main work; 12 = time spent waiting for tagged words, 13 = step prologue
+enum { kProfWait = 12, kProfStep = 13, kProfSlots = 32 };
 
 enum JobKind { JOB_QKV = 0, JOB_O = 1, JOB_GU = 2, JOB_DOWN = 3, JOB_LM = 4 };
 
@@ -81,7 +105,7 @@ struct Job {
     int n_units;           // groups * ks
     int rot;               // CTA (per-layer jobs) or warp slot (lm_head) that gets unit 0
     int wrot;              // warp that gets tile 0 of a CTA unit
-    int part_off;          // offset (in doubles) of this job's cross-CTA partials: [all groups][ks][32]
+    int pad0_;
     int layer;
     int g_off;             // first unit group this GPU owns (tensor parallelism; base points at it, groups counts the owned ones)
     int pad_;
@@ -89,15 +113,24 @@ struct Job {
 
 struct LayerPtrs { const float* attn_norm; const float* ffn_norm; const float* bqkv; };
 
-// Tensor parallelism inside the persistent kernel: peer pointers (CUDA IPC mappings of the other GPUs' buffers) for the
-// exchange that follows the gate/up, down and lm_head phases.  on == 0: single GPU, or exchanges done by the host program.
+// Tensor parallelism inside the kernel: the other GPUs' exchange blocks (CUDA IPC mappings).  on == 0: single GPU, or
+// exchanges done by the host program between launches.
 struct TpPeerParams {
-    int on, rank, world;
-    int ff_g0, ff_g1, e_g0, e_g1;          // this GPU's row groups of the gate/up (FF/32 groups) and down (E/32 groups) jobs
-    uint8_t* act_peer[8];                  // [act_q | act_d] on every GPU
-    double* part_peer[8];                  // partial-sum buffer on every GPU
-    int* flags_peer[8];                    // flag block on every GPU: [8] flags by source, [8] epoch, [16..] candidates {float, int} by rank
-    int* flags_local;
+    int on, rank, world, pad_;
+    unsigned long long* xw_peer[kMaxWorldTP];     // exchange block on every GPU (own entry = local block)
+};
+
+// Offsets (in 8-byte words) of the tagged vectors inside the exchange block.  q8_0 vectors are stored as
+// [n/4] words of four int8 values followed by [n/32 (+1 if odd)] words of {fp16 scale bits | int16 sum of the block's values << 16}.
+struct XwLayout {
+    int qkv;        // [qkv rows, padded to 32]   fp32 bits: q | k | v after bias and RoPE, packed (pair-adjacent) order
+    int att;        // q8_0 of the merged attention output [NH*HD]
+    int o;          // [E] fp32 bits: O projection
+    int act;        // q8_0 of SwiGLU(gate, up) [FF]                                     (pushed to the other GPUs)
+    int down;       // [E] fp32 bits: down projection                                    (pushed)
+    int dpart;      // [E/32][kMaxKSplit-1][32][2]: double partial sums (lo, hi) of the down K-splits 1..
+    int cand;       // [kMaxWorldTP][grid][2]: argmax candidates {fp32 value bits}, {index}   (pushed)
+    int total;
 };
 
 struct DecodeParams {
@@ -112,23 +145,30 @@ struct DecodeParams {
     const float* rope_freq;          // [HD/2]: base^(-2i/HD), computed on the host with powf
     const uint8_t* emb_base;         // tiled token embedding (may alias the lm_head)
     int emb_nt, emb_kb;
-    // state (global, written and read across CTAs: always accessed through L2)
-    float* h_in;                     // residual stream at the input of the current layer
-    float* h_mid;                    // residual stream after the attention block
-    float* qkv_out;                  // [q | k | v] of the current token after bias and RoPE, packed (pair-adjacent) row order
-    float* att;
-    int8_t* att_q; __half* att_d;    // q8_0 of the merged attention output
-    int8_t* act_q; __half* act_d;    // q8_0 of SwiGLU(gate, up)
+    // residual stream as committed by CTA 0: read by a launch that starts in the middle of a step, and by tests
+    float* h_in;                     // at the input of the current layer
+    float* h_mid;                    // after the attention block
+    // the exchange block: every vector one CTA hands to another, as tagged words
+    unsigned long long* xw; XwLayout xo;
+    // Tag of (step s of the launch, phase p) = epoch + s * (5L+1) + p + 1.  The epoch lives in device memory and the kernel
+    // advances it itself: a launch whose phase range ends a step leaves it past every tag the launch used (a launch that
+    // gave up on a wait: further still).  Replayed launch sequences and calls after a failure therefore never meet a stale
+    // word with a matching tag; launches that continue a step (phase range not starting at 0) share its epoch.
+    unsigned* epoch_dev;
+    unsigned long long wait_ns;      // time budget of every device-side wait
+    int drop_phase;                  // test hook: the producers of this phase publish nothing (-1: none), so that its consumers' waits run out
+    // plain (untagged) vectors: inputs / outputs of the attention code when it runs as a kernel of its own (M-token step)
+    float* qkv_out;
+    float* att;                      // merged attention output, fp32 (also written by the decode loop, for inspection)
+    int8_t* att_q; __half* att_d;
     __half* kc; __half* vc; int max_seq;       // [L][max_seq][KVD]
     double* attn_part; unsigned* attn_cnt; int max_chunks;  // [NH][max_chunks][HD+2], [NKV]
-    double* part;                              // cross-CTA partial sums of the O / down projections
-    float* cand_val; int* cand_idx; unsigned* cand_cnt;     // per-CTA argmax candidates
-    float* best_val;                 // value of this GPU's best logit (tensor parallelism: compared across GPUs)
+    float* best_val;                 // value of the best logit (tensor parallelism with host-side exchange: this GPU's rows only)
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
     float* logits; long long logits_stride;    // optional [n_steps][stride]
     int pos0;
     const int* pos_dev;              // optional: first position read from device memory instead (a captured launch sequence stays position-free)
-    unsigned* bar; int* err;
+    int* err;
     unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA 0 (see kProf*)
     TpPeerParams tp;
 };
@@ -138,12 +178,13 @@ __host__ __device__ inline int attn_chunks(int Lp, int max_chunks, int chunk = k
     int n = (Lp + chunk - 1) / chunk;
     return n < 1 ? 1 : (n > max_chunks ? max_chunks : n);
 }
+__host__ __device__ inline int q8_words(int n) { return n / 4 + (n / 32 + 1) / 2 * 2; }     // tagged words of a q8_0 vector of n values
 
 #ifdef __CUDACC__
 inline namespace MI_KVARIANT {
 
 struct DecodeSmem {
-    uint8_t* ring; uint64_t* bars; Job* jobs; LayerPtrs* lp; float* cs; double* red; double* fold; uint8_t* stage;
+    uint8_t* ring; uint64_t* bars; Job* jobs; LayerPtrs* lp; float* cs; double* red; double* fold; float* h; uint8_t* stage;
 };
 
 constexpr int kFoldBytes = 2 * DNW * 2 * 32 * 8;      // two buffers of [warp][acc][lane] doubles
@@ -156,7 +197,7 @@ __host__ __device__ inline size_t decode_stage_bytes(int E, int FF, int HD, int 
 }
 __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, int HD, int G) {
     return (size_t)DNW * DS * DSLOT + 256 + ((size_t)njobs * sizeof(Job) + 127) / 128 * 128 + 64 * sizeof(LayerPtrs) + 1024 + 256 + kFoldBytes +
-           decode_stage_bytes(E, FF, HD, G);
+           ((size_t)E * 4 + 127) / 128 * 128 + decode_stage_bytes(E, FF, HD, G);
 }
 
 // close the current profile interval: charge the time since t to slot k (CTA 0, thread 0 only).
@@ -171,30 +212,75 @@ __device__ __forceinline__ void prof_mark(const DecodeParams& P, unsigned long l
 #endif
 }
 
-// ---- grid barrier: monotonic arrival counter, bounded wait -----------------------
-// The release on the arrival orders this CTA's earlier writes (made visible to thread 0
-// by the __syncthreads) before it; the acquire on the poll orders later reads after it.
-__device__ __forceinline__ bool grid_barrier(unsigned* bar, unsigned& target, int* ok_s) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        target += gridDim.x;
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bar) : "memory");
-        bool ok = true;
-        unsigned v;
-        unsigned long long t0 = 0;
-        for (unsigned it = 0;; it++) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
-            if ((int)(v - target) >= 0) break;
-            if ((it & 1023u) == 1023u) {
-                const unsigned long long now = gtime_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > kWaitBudgetNs) { ok = false; break; }
-            }
+// ---- tagged words ---------------------------------------------------------------------
+// One 64-bit access carries value and tag together, so there is nothing to order between them.
+// The accesses are volatile: they are performed at the L2 (the point where all SMs of this GPU,
+// and peers storing over NVLink, meet), once each, in program order.
+__device__ __forceinline__ unsigned long long tw_ld(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void tw_ld2(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {   // 16-byte aligned pair; each word is checked on its own
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void tw_st(unsigned long long* p, unsigned tag, unsigned payload) {
+    asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(((unsigned long long)tag << 32) | payload) : "memory");
+}
+__device__ __forceinline__ bool tw_is(unsigned long long w, unsigned tag) { return (unsigned)(w >> 32) == tag; }
+
+// Where a phase publishes: locally, and (tensor-parallel build, shared vectors) into every other GPU's block.
+struct Pub {
+    unsigned long long* xw; unsigned tag; bool mute;
+#if MI_TP
+    const TpPeerParams* tp;
+#endif
+    __device__ __forceinline__ void local(int off, unsigned payload) const { if (!mute) tw_st(xw + off, tag, payload); }
+    __device__ __forceinline__ void shared(int off, unsigned payload) const {
+        if (mute) return;
+        tw_st(xw + off, tag, payload);
+#if MI_TP
+        if (tp->on) {
+            for (int p = 0; p < tp->world; p++) if (p != tp->rank) tw_st(tp->xw_peer[p] + off, tag, payload);
         }
-        *ok_s = ok ? 1 : 0;
+#endif
     }
-    __syncthreads();
-    return *ok_s != 0;
+};
+
+// Poll one word until it carries `tag`.  Gives up (false) when the time budget has run out or another CTA has reported
+// an error; the caller then leaves the kernel through its error path.
+static __device__ __noinline__ bool tw_spin(const unsigned long long* p, unsigned tag, unsigned long long budget_ns, const int* err) {
+    unsigned long long t0 = 0;
+    for (unsigned it = 1;; it++) {
+        if (tw_is(tw_ld(p), tag)) return true;
+        if ((it & 31u) == 0) {
+            const unsigned long long now = gtime_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget_ns || *reinterpret_cast<const volatile int*>(err) != 0) return false;
+        }
+    }
+}
+
+// Load the N words addr(k) (k with bit k of `valid` set) and return their payloads once all carry `tag`.  All loads are
+// issued before any is looked at; if some word is not there yet, the thread polls the first such word and then fetches
+// every missing word again (they were produced together, most have landed meanwhile).
+template <int N, class AddrFn>
+__device__ __forceinline__ bool tw_poll(const DecodeParams& P, unsigned tag, unsigned valid, AddrFn addr, unsigned (&out)[N]) {
+    unsigned long long w[N];
+    #pragma unroll
+    for (int k = 0; k < N; k++) w[k] = (valid >> k & 1u) ? tw_ld(addr(k)) : ((unsigned long long)tag << 32);
+    for (;;) {
+        const unsigned long long* miss = nullptr;
+        #pragma unroll
+        for (int k = N - 1; k >= 0; k--) if (!tw_is(w[k], tag)) miss = addr(k);
+        if (!miss) break;
+        if (!tw_spin(miss, tag, P.wait_ns, P.err)) return false;
+        #pragma unroll
+        for (int k = 0; k < N; k++) if (!tw_is(w[k], tag)) w[k] = tw_ld(addr(k));
+    }
+    #pragma unroll
+    for (int k = 0; k < N; k++) out[k] = (unsigned)w[k];
+    return true;
 }
 
 // ---- the per-warp weight stream -----------------------------------------------
@@ -299,14 +385,37 @@ __device__ __forceinline__ double tile_consume(WarpStream& ws, int lane, int kb,
     return acc;
 }
 
+// q8_0 of one 32-element block held one element per lane; returns the int8 value, and through
+// d_out / s_out (all lanes) the fp16 scale and the integer sum of the block's values.
+__device__ __forceinline__ int quant_block_warp2(float v, __half& d_out, int& s_out) {
+    const float a = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v))));
+    const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+    const int q = __float2int_rn(__fmul_rn(v, inv));
+    s_out = __reduce_add_sync(0xffffffffu, q);
+    d_out = __float2half_rn(__fdiv_rn(a, 127.f));
+    return q;
+}
+// Publish one q8_0 block (lane = element) as tagged words: lanes 0, 4, 8, .. store four int8 values each, lane 0
+// also the scale word.  qoff / soff: word offsets of the vector's value and scale parts; b: block index.
+template <bool SHARED>
+__device__ __forceinline__ void publish_q8_block(const Pub& pub, int qoff, int soff, int b, int lane, int q, __half d, int s) {
+    unsigned v = (unsigned)q & 0xffu;
+    v |= __shfl_down_sync(0xffffffffu, v, 1) << 8;
+    v |= __shfl_down_sync(0xffffffffu, v, 2) << 16;
+    const unsigned sw = (unsigned)__half_as_ushort(d) | ((unsigned)s << 16);
+    if ((lane & 3) == 0) { if (SHARED) pub.shared(qoff + b * 8 + (lane >> 2), v); else pub.local(qoff + b * 8 + (lane >> 2), v); }
+    if (lane == 0) { if (SHARED) pub.shared(soff + b, sw); else pub.local(soff + b, sw); }
+}
+
 // Per-layer job: this CTA's units, tiles split over its warps, partial sums folded in
-// shared memory in warp order by warp 0.
-//   ks == 1 : epi(g, lane, v0, v1) with the complete sums (fp32 of the double sum);
-//   ks  > 1 : the double partial of (g, sp) goes to P.part for the next prologue.
+// shared memory in warp order by warp 0, which then calls epi(g, lane, v0, v1) with the
+// complete sums rounded to fp32.  A job that is K-split across CTAs (ks > 1; down projection)
+// adds one hop: the CTAs of splits 1.. publish their double partial sums as tagged word pairs,
+// the CTA of split 0 waits for them, adds them to its own in split order and calls epi.
 // Every warp passes the same number of __syncthreads, also after a wait gave up.
 template <class Epi>
 __device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& P, const DecodeSmem& sm, int j, int lane,
-                                            const int8_t* xq_s, const float2* xs_s, unsigned long long& tp, Epi epi) {
+                                            const int8_t* xq_s, const float2* xs_s, const Pub& pub, unsigned long long& tp, Epi epi) {
     const Job jb = ws.jobs[j];                          // registers: the fields are used many times
     bool ok = true;
     int uidx = 0;
@@ -327,8 +436,28 @@ __device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& 
             double v0 = fb[lane], v1 = fb[32 + lane];
             #pragma unroll
             for (int w = 1; w < DNW; w++) { v0 = __dadd_rn(v0, fb[(w * 2) * 32 + lane]); v1 = __dadd_rn(v1, fb[(w * 2 + 1) * 32 + lane]); }
-            if (jb.ks == 1) epi(s.g + jb.g_off, lane, __double2float_rn(v0), __double2float_rn(v1));
-            else __stcg(P.part + jb.part_off + ((size_t)(s.g + jb.g_off) * jb.ks + s.sp) * 32 + lane, v0);
+            const int gg = s.g + jb.g_off;
+            if (jb.ks > 1) {
+                const int slot = P.xo.dpart + ((gg * (kMaxKSplit - 1)) * 32 + lane) * 2;
+                if (s.sp != 0) {
+                    const unsigned long long bits = (unsigned long long)__double_as_longlong(v0);
+                    pub.local(slot + (s.sp - 1) * 64, (unsigned)bits);
+                    pub.local(slot + (s.sp - 1) * 64 + 1, (unsigned)(bits >> 32));
+                } else {
+                    unsigned pw[2 * (kMaxKSplit - 1)];
+                    const unsigned long long* base = P.xw + slot;
+                    if (ok) ok = tw_poll(P, pub.tag, (1u << (2 * (jb.ks - 1))) - 1u, [&](int k) { return base + (k >> 1) * 64 + (k & 1); }, pw);
+                    ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+                    if (ok) {
+                        #pragma unroll
+                        for (int q = 0; q < kMaxKSplit - 1; q++)
+                            if (q < jb.ks - 1) v0 = __dadd_rn(v0, __longlong_as_double((long long)(((unsigned long long)pw[2 * q + 1] << 32) | pw[2 * q])));
+                        epi(gg, lane, __double2float_rn(v0), 0.f);
+                    }
+                }
+            } else {
+                epi(gg, lane, __double2float_rn(v0), __double2float_rn(v1));
+            }
         }
         prof_mark(P, tp, 19);
     }
@@ -348,7 +477,7 @@ __device__ __forceinline__ bool run_warp_job(WarpStream& ws, int j, int lane, co
     return ok;
 }
 
-// ---- activation staging (whole CTA; ends with __syncthreads) -----------------------
+// ---- activation staging (whole CTA; returns a CTA-uniform ok) -----------------------
 
 // Warp-wide maximum of non-negative floats and warp-wide integer sum as single redux
 // instructions (the bit pattern of a non-negative float orders like an unsigned integer);
@@ -363,7 +492,7 @@ __device__ __forceinline__ float warp_max_float(float a) {
 }
 
 // q8_0 of one 32-element block held one element per lane; returns the int8 value,
-// writes {fp32 of fp16(a/127), float(8*sum q)} through lane 0.
+// writes the fp16 scale through lane 0 (plain stores: the attention kernel of the M-token step).
 __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_out, __half* xd_out) {
     const float a = warp_max_nonneg(fabsf(v));
     const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
@@ -377,37 +506,31 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
     return q;
 }
 
-// Residual fold + RMSNorm + q8_0 staging:
-//   x = src (global fp32) or the embedding row of `token` (src == null)
-//       + fp32(sum of the ks cross-CTA partials of the previous projection)   [if part]
-//   CTA 0 publishes x to commit (the residual stream other phases read later);
+// Residual add + RMSNorm + q8_0 staging:
+//   x = h (this CTA's copy of the residual stream in shared memory; or gsrc, the copy CTA 0 committed to global memory,
+//       when the launch starts here; or the embedding row of `token`)
+//       + the projection output published as tagged fp32 words at addw   [if addw]
+//   h = x;  CTA 0 also commits x to global memory;
 //   xq_s / xs_s = q8_0( x * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
 // Warp w owns the 32-element blocks w, w+8, ...; lane = element, so a thread holds at most
-// NB values and everything stays in registers.  All loads (vector, partials, norm weights)
+// NB values and everything stays in registers.  All loads (vector, tagged words, norm weights)
 // are requested before anything waits on them, and the NB quantizer chains of a warp are
-// interleaved so their shuffle latencies overlap.  Sum of squares in double (every x*x is
-// exact there).
+// interleaved so their latencies overlap.  Sum of squares in double (every x*x is exact there).
 template <int NB>
-__device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const float* src, int token, const double* part, int ks,
-                                                float* commit, const float* __restrict__ w, int E, float eps, double* red,
-                                                int8_t* xq_s, float2* xs_s) {
+__device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token,
+                                                const unsigned long long* addw, unsigned tag, float* commit, const float* __restrict__ w,
+                                                int E, float eps, double* red, int8_t* xq_s, float2* xs_s, unsigned long long& tpf) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nb = E / 32;
-    // pass A: request everything (vector, norm weights, up to 4 partials per element); no use of any value
-    float x[NB], wv[NB]; double pt[NB][4];
+    float x[NB], wv[NB];
+    unsigned valid = 0;
     #pragma unroll
     for (int k = 0; k < NB; k++) {
         const int b = min(warp + k * DNW, nb - 1), e = b * 32 + lane;      // clamped: every address is valid
+        if (warp + k * DNW < nb) valid |= 1u << k;
         wv[k] = __ldg(w + e);
-        x[k] = src ? __ldcg(src + e) : 0.f;
-        #pragma unroll
-        for (int q = 0; q < 4; q++) pt[k][q] = 0.0;
-        if (part) {
-            const double* pp = part + (size_t)b * ks * 32 + lane;
-            #pragma unroll
-            for (int q = 0; q < 4; q++) if (q < ks) pt[k][q] = __ldcg(pp + q * 32);
-        }
+        x[k] = embed ? 0.f : (gsrc ? __ldcg(gsrc + e) : h_s[e]);
     }
-    if (!src) {                                                 // layer 0: the embedding row, value (nibble - 8) * d (src/gguf.h:94-102)
+    if (embed) {                                                 // layer 0: the embedding row, value (nibble - 8) * d (src/gguf.h:94-102)
         #pragma unroll
         for (int k = 0; k < NB; k++) {
             const int b = min(warp + k * DNW, nb - 1);
@@ -418,31 +541,32 @@ __device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const flo
             x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
         }
     }
-    // pass B: fold the partials in split order (ks <= 4, enforced when the jobs are planned)
-    double pv[NB];
-    #pragma unroll
-    for (int k = 0; k < NB; k++) {
-        double s = pt[k][0];
+    bool ok = true;
+    if (addw) {
+        unsigned aw[NB];
+        prof_mark(P, tpf, 23);
+        ok = tw_poll(P, tag, valid, [&](int k) { return addw + (size_t)(warp + k * DNW) * 32 + lane; }, aw);
+        prof_mark(P, tpf, kProfWait);
         #pragma unroll
-        for (int q = 1; q < 4; q++) if (q < ks) s = __dadd_rn(s, pt[k][q]);
-        pv[k] = s;
-        if (warp + k * DNW >= nb) { x[k] = 0.f; pv[k] = 0.0; }         // a clamped duplicate: contributes nothing
+        for (int k = 0; k < NB; k++) if (valid >> k & 1u) x[k] = __fadd_rn(x[k], __uint_as_float(aw[k]));
     }
-    unsigned long long tq = MI_PROF ? gtime_ns() : 0;
     double ss = 0.0;
     #pragma unroll
     for (int k = 0; k < NB; k++) {
-        if (part) x[k] = __fadd_rn(x[k], __double2float_rn(pv[k]));
-        const int b = warp + k * DNW;
-        if (b < nb && commit && blockIdx.x == 0) __stcg(commit + b * 32 + lane, x[k]);
+        if (!(valid >> k & 1u)) x[k] = 0.f;                      // a clamped duplicate: contributes nothing
+        else {
+            const int e = (warp + k * DNW) * 32 + lane;
+            h_s[e] = x[k];
+            if (commit && blockIdx.x == 0) __stcg(commit + e, x[k]);
+        }
         const double xd = x[k]; ss = __fma_rn(xd, xd, ss);
     }
     #pragma unroll
     for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
     if (lane == 0) red[warp] = ss;
-    prof_mark(P, tq, 23);
-    __syncthreads();
-    prof_mark(P, tq, 24);
+    prof_mark(P, tpf, 23);
+    if (!__syncthreads_and(ok ? 1 : 0)) return false;
+    prof_mark(P, tpf, 24);
     double tot = 0.0;
     #pragma unroll
     for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
@@ -468,37 +592,88 @@ __device__ __forceinline__ void stage_norm_q8_t(const DecodeParams& P, const flo
             if (lane == 0) xs_s[b] = make_float2(__half2float(__float2half_rn(__fdiv_rn(a[k], 127.f))), __int2float_rn(8 * sq[k]));
         }
     }
-    prof_mark(P, tq, 25);
+    prof_mark(P, tpf, 25);
     __syncthreads();
-    prof_mark(P, tq, 26);
+    prof_mark(P, tpf, 26);
+    return true;
 }
 
-static __device__ __noinline__ void stage_norm_q8_wide(const DecodeParams& P, const float* src, int token, const double* part, int ks, float* commit,
-                                                const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
-    if ((E / 32 + DNW - 1) / DNW <= 16) stage_norm_q8_t<16>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
-    else stage_norm_q8_t<64>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+#define MI_NORM_ARGS const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token, const unsigned long long* addw, unsigned tag, \
+                     float* commit, const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s, unsigned long long& tpf
+#define MI_NORM_PASS P, h_s, gsrc, embed, token, addw, tag, commit, w, E, eps, red, xq_s, xs_s, tpf
+static __device__ __noinline__ bool stage_norm_q8_wide(MI_NORM_ARGS) {
+    if ((E / 32 + DNW - 1) / DNW <= 16) return stage_norm_q8_t<16>(MI_NORM_PASS);
+    return stage_norm_q8_t<32>(MI_NORM_PASS);
 }
-__device__ __forceinline__ void stage_norm_q8(const DecodeParams& P, const float* src, int token, const double* part, int ks, float* commit,
-                                              const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
+__device__ __forceinline__ bool stage_norm_q8(MI_NORM_ARGS) {
     const int per_warp = (E / 32 + DNW - 1) / DNW;
-    if (per_warp <= 4) stage_norm_q8_t<4>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
-    else if (per_warp <= 6) stage_norm_q8_t<6>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
-    else if (per_warp <= 8) stage_norm_q8_t<8>(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
-    else stage_norm_q8_wide(P, src, token, part, ks, commit, w, E, eps, red, xq_s, xs_s);
+    if (per_warp <= 4) return stage_norm_q8_t<4>(MI_NORM_PASS);
+    if (per_warp <= 6) return stage_norm_q8_t<6>(MI_NORM_PASS);
+    if (per_warp <= 8) return stage_norm_q8_t<8>(MI_NORM_PASS);
+    return stage_norm_q8_wide(MI_NORM_PASS);
 }
 
-// q8_0 vector already in global memory (written by another CTA): copy through L2.
-__device__ __forceinline__ void stage_copy_q8(const int8_t* xq, const __half* xd, int nb, int8_t* xq_s, float2* xs_s) {
-    const int tid = threadIdx.x;
-    const int4* src = reinterpret_cast<const int4*>(xq);
-    int4* dst = reinterpret_cast<int4*>(xq_s);
-    for (int b = tid; b < nb; b += DNT) {
-        const int4 xa = __ldcg(src + 2 * b), xc = __ldcg(src + 2 * b + 1);
-        dst[2 * b] = xa; dst[2 * b + 1] = xc;
-        const __half d = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(xd) + b));
-        xs_s[b] = make_float2(__half2float(d), __int2float_rn(8 * sum_x_block(xa, xc)));
+// A q8_0 vector published as tagged words by other CTAs -> shared memory: int8 values, and per block {fp32 of the fp16
+// scale, float(8 * sum of the block's values)}.  Thread t takes the 16-byte word pairs t, t + 256, ...; all of a
+// thread's loads are in flight together.
+template <int NP>
+__device__ __forceinline__ bool stage_poll_q8_t(const DecodeParams& P, const unsigned long long* vw, int n, unsigned tag, int8_t* xq_s, float2* xs_s) {
+    const int tid = threadIdx.x, nq2 = n / 8, tot2 = nq2 + (n / 32 + 1) / 2, nbk = n / 32;     // pairs of value words, all pairs, blocks
+    unsigned long long w[NP][2];
+    #pragma unroll
+    for (int k = 0; k < NP; k++) {
+        const int pr = tid + k * DNT;
+        if (pr < tot2) tw_ld2(vw + 2 * pr, w[k][0], w[k][1]);
+        else w[k][0] = w[k][1] = (unsigned long long)tag << 32;
+        if (pr == tot2 - 1 && (nbk & 1)) w[k][1] = (unsigned long long)tag << 32;      // odd block count: the pad word is never written
     }
-    __syncthreads();
+    bool ok = true;
+    for (;;) {
+        const unsigned long long* miss = nullptr;
+        #pragma unroll
+        for (int k = NP - 1; k >= 0; k--) {
+            if (!tw_is(w[k][1], tag)) miss = vw + 2 * (tid + k * DNT) + 1;
+            if (!tw_is(w[k][0], tag)) miss = vw + 2 * (tid + k * DNT);
+        }
+        if (!miss) break;
+        if (!tw_spin(miss, tag, P.wait_ns, P.err)) { ok = false; break; }
+        #pragma unroll
+        for (int k = 0; k < NP; k++) {
+            if (!tw_is(w[k][0], tag) || !tw_is(w[k][1], tag)) {
+                const int pr = tid + k * DNT;
+                tw_ld2(vw + 2 * pr, w[k][0], w[k][1]);
+                if (pr == tot2 - 1 && (nbk & 1)) w[k][1] = (unsigned long long)tag << 32;
+            }
+        }
+    }
+    #pragma unroll
+    for (int k = 0; k < NP; k++) {
+        const int pr = tid + k * DNT;
+        if (pr < nq2) {
+            reinterpret_cast<uint2*>(xq_s)[pr] = make_uint2((unsigned)w[k][0], (unsigned)w[k][1]);
+        } else if (pr < tot2) {
+            #pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int b = 2 * (pr - nq2) + h;
+                if (b < nbk) {
+                    const unsigned sw = (unsigned)w[k][h];
+                    xs_s[b] = make_float2(__half2float(__ushort_as_half((unsigned short)(sw & 0xffffu))), __int2float_rn(8 * (int)(short)(sw >> 16)));
+                }
+            }
+        }
+    }
+    return __syncthreads_and(ok ? 1 : 0) != 0;
+}
+static __device__ __noinline__ bool stage_poll_q8_rare(const DecodeParams& P, const unsigned long long* vw, int n, unsigned tag, int8_t* xq_s, float2* xs_s) {
+    const int np = (q8_words(n) / 2 + DNT - 1) / DNT;
+    if (np <= 8) return stage_poll_q8_t<8>(P, vw, n, tag, xq_s, xs_s);
+    return stage_poll_q8_t<18>(P, vw, n, tag, xq_s, xs_s);
+}
+__device__ __forceinline__ bool stage_poll_q8(const DecodeParams& P, const unsigned long long* vw, int n, unsigned tag, int8_t* xq_s, float2* xs_s) {
+    const int np = (q8_words(n) / 2 + DNT - 1) / DNT;
+    if (np <= 1) return stage_poll_q8_t<1>(P, vw, n, tag, xq_s, xs_s);
+    if (np <= 5) return stage_poll_q8_t<5>(P, vw, n, tag, xq_s, xs_s);
+    return stage_poll_q8_rare(P, vw, n, tag, xq_s, xs_s);
 }
 
 // ---- attention --------------------------------------------------------------------
@@ -519,35 +694,68 @@ __device__ __forceinline__ void stage_copy_q8(const int8_t* xq, const __half* xd
 // STORE_KV: the CTA whose range ends at the new position writes that position's K and V from the packed QKV
 // vector (the decode loop); callers that stored them beforehand pass false.  QNAT: q is in natural dimension
 // order (the stand-alone entry point) instead of the packed pair-adjacent order of the fused QKV projection.
-template <int HD, int G, int GQ, bool STORE_KV = true, bool QNAT = false>
-__device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp) {
+// TG: inputs (q, and k / v of the new position) and the q8_0 output travel as tagged words (the decode loop); otherwise they
+// are plain arrays (the attention kernel of the M-token step).  Returns false if a wait gave up (CTA-uniform).
+template <int HD, int G, int GQ, bool STORE_KV = true, bool QNAT = false, bool TG = false>
+__device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp,
+                                                unsigned tag_in = 0, const Pub* pub = nullptr) {
     constexpr int DPW = HD / 32;           // dims per lane in pass 2 and while folding (dim = lane + 32*i)
     constexpr int SW = HD + 2;             // doubles per (head) state: o[HD], m, l
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ngrp = P.NH / G;
     // one head per CTA: 256 positions are one 32-position batch per warp, and a single chunk needs no cross-CTA merge
     const int Lp = pos + 1, nch = attn_chunks(Lp, min(P.max_chunks, (int)gridDim.x / ngrp), G == 1 ? 256 : kAttnChunk);
-    if ((int)blockIdx.x >= ngrp * nch) return;
+    if ((int)blockIdx.x >= ngrp * nch) return true;
     const int grp = blockIdx.x / nch, ch = blockIdx.x % nch, h0 = grp * G, kvh = h0 / GQ;
     const int p0 = (int)((long long)ch * Lp / nch), p1 = (int)((long long)(ch + 1) * Lp / nch);
     double* scr = reinterpret_cast<double*>(stage);                        // [warp][G][SW]
     double* wts = scr + DNW * G * SW;                                       // [warp][32][G]
     constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2;                   // lanes per position in pass 1, dims per lane, padded stride
     double* qs = wts + DNW * 32 * G;                                        // [G][LPP][QSTR]: 16-byte skew per lane, conflict-free
-    // q of this kv head's G query heads, from the packed QKV vector: dim d of a head sits at 2d (d < HD/2) or 2(d-HD/2)+1
-    for (int i = tid; i < G * HD; i += DNT) {
-        const int j = i / HD, d = i % HD, pk = QNAT ? d : (d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1);
-        qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(h0 + j) * HD + pk);
-    }
-    if (STORE_KV && ch == nch - 1) {      // this CTA's range ends at the new position: store its K and V (fp16); CTAs that share a kv head store the same bits
+    const bool store_kv = STORE_KV && ch == nch - 1;     // this CTA's range ends at the new position: it stores that position's K and V (fp16); CTAs that share a kv head store the same bits
+    if constexpr (TG) {
+        // q of this CTA's G query heads, and k / v of the new position, from the tagged QKV vector (packed order: dim d of a
+        // head sits at 2d (d < HD/2) or 2(d-HD/2)+1); one poll for all of a thread's words
+        constexpr int QN = (G * HD + DNT - 1) / DNT;
         const int nq = P.NH * HD;
-        for (int d = tid; d < HD; d += DNT) {
-            const int pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
-            P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + (size_t)kvh * HD + pk));
-            P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + P.KVD + (size_t)kvh * HD + d));
+        unsigned qw[QN + 2], valid = 0;
+        #pragma unroll
+        for (int k = 0; k < QN; k++) if (tid + k * DNT < G * HD) valid |= 1u << k;
+        if (store_kv && tid < HD) valid |= 3u << QN;
+        const unsigned long long* qv = P.xw + P.xo.qkv;
+        const int dk = tid < HD / 2 ? 2 * tid : 2 * (tid - HD / 2) + 1;           // packed slot of dim `tid` (threads below HD)
+        bool okq = tw_poll(P, tag_in, valid, [&](int k) -> const unsigned long long* {
+            if (k < QN) {
+                const int i = tid + k * DNT, j = i / HD, d = i % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+                return qv + (size_t)(h0 + j) * HD + pk;
+            }
+            return k == QN ? qv + nq + (size_t)kvh * HD + dk : qv + nq + P.KVD + (size_t)kvh * HD + tid;
+        }, qw);
+        #pragma unroll
+        for (int k = 0; k < QN; k++) {
+            const int i = tid + k * DNT;
+            if (i < G * HD) { const int j = i / HD, d = i % HD; qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__uint_as_float(qw[k]); }
         }
+        if (store_kv && tid < HD) {
+            P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__uint_as_float(qw[QN]));
+            P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__uint_as_float(qw[QN + 1]));
+        }
+        if (!__syncthreads_and(okq ? 1 : 0)) return false;
+    } else {
+        for (int i = tid; i < G * HD; i += DNT) {
+            const int j = i / HD, d = i % HD, pk = QNAT ? d : (d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1);
+            qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__ldcg(P.qkv_out + (size_t)(h0 + j) * HD + pk);
+        }
+        if (store_kv) {
+            const int nq = P.NH * HD;
+            for (int d = tid; d < HD; d += DNT) {
+                const int pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+                P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + (size_t)kvh * HD + pk));
+                P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + d] = __float2half_rn(__ldcg(P.qkv_out + nq + P.KVD + (size_t)kvh * HD + d));
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
     prof_mark(P, tp, 14);
     const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
     const int n = p1 - p0, a0 = p0 + (int)((long long)n * warp / DNW), a1 = p0 + (int)((long long)n * (warp + 1) / DNW);
@@ -688,6 +896,9 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         for (int i = 0; i < DPW; i++) sw[lane + 32 * i] = o[j][i];
         if (lane == 0) { sw[HD] = (double)m[j]; sw[HD + 1] = ls[j]; }
     }
+    // the new position's K / V rows (plain stores above) are performed before anything this CTA publishes from here on:
+    // a CTA that reads them in a later step has consumed words that descend from this CTA's output
+    if (TG && store_kv && tid < HD) __threadfence();
     __syncthreads();
     // warp j folds head j's DNW warp states against their common maximum and publishes the chunk partial
     if (warp < G) {
@@ -715,7 +926,13 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
                 const float v = __double2float_rn(__ddiv_rn(ob[i], ll));
                 const int e = head * HD + 32 * i + lane;
                 __stcg(P.att + e, v);
-                P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
+                if constexpr (TG) {
+                    __half dq; int sq;
+                    const int qv8 = quant_block_warp2(v, dq, sq);
+                    publish_q8_block<false>(*pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+                } else {
+                    P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
+                }
             }
         } else {
             double* gp = P.attn_part + ((size_t)head * P.max_chunks + ch) * SW;
@@ -725,13 +942,13 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
         }
     }
     prof_mark(P, tp, 16);
-    if (nch == 1) return;
+    if (nch == 1) return true;
     __threadfence();
     __syncthreads();
     __shared__ unsigned s_prev;
     if (tid == 0) s_prev = atomicAdd(P.attn_cnt + grp, 1u);
     __syncthreads();
-    if (s_prev != (unsigned)nch - 1) return;
+    if (s_prev != (unsigned)nch - 1) return true;
     // last chunk of this kv head: fold the chunk partials against their common maximum, normalise, emit fp32 + q8_0
     __threadfence();
     if (tid == 0) P.attn_cnt[grp] = 0;
@@ -780,79 +997,17 @@ __device__ __forceinline__ void attention_phase(const DecodeParams& P, int l, in
             const float v = __double2float_rn(__ddiv_rn(ob[i], ll));
             const int e = head * HD + 32 * i + lane;
             __stcg(P.att + e, v);
-            P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
-        }
-    }
-}
-
-#if MI_TP
-// ---- exchange with the other GPUs (CTA 0, between two grid barriers) --------------------
-// Store what this GPU owns of the buffer the phase wrote into every peer's copy, publish the epoch number in every
-// peer's flag slot, wait (bounded) for the peers' numbers.  kind 3: gate/up activations, 4: down partial sums of layer
-// l, 5: argmax candidates, followed by the pick of the overall greedy token.  Returns false if a wait gave up.
-__device__ __forceinline__ bool tp_peer_exchange(const DecodeParams& P, const DecodeSmem& sm, int kind, int l, int step, int* ok_s) {
-    const TpPeerParams& T = P.tp;
-    const int tid = threadIdx.x;
-    int* epoch_p = T.flags_local + 8;
-    const int epoch = *reinterpret_cast<volatile int*>(epoch_p) + 1;
-    float* cand_local = reinterpret_cast<float*>(T.flags_local + 16);
-    if (kind == 5 && tid == 0) {                               // this GPU's candidate into its own slot first
-        cand_local[2 * T.rank] = __ldcg(P.best_val);
-        reinterpret_cast<int*>(cand_local)[2 * T.rank + 1] = __ldcg(P.cur_token);
-    }
-    __syncthreads();
-    for (int p = 0; p < T.world; p++) {
-        if (p == T.rank) continue;
-        if (kind == 3) {
-            const int4* s = reinterpret_cast<const int4*>(P.act_q + (size_t)T.ff_g0 * 32);
-            int4* d = reinterpret_cast<int4*>(T.act_peer[p] + (size_t)T.ff_g0 * 32);
-            for (int i = tid; i < (T.ff_g1 - T.ff_g0) * 2; i += DNT) d[i] = __ldcg(s + i);
-            const unsigned short* s2 = reinterpret_cast<const unsigned short*>(P.act_d) + T.ff_g0;
-            unsigned short* d2 = reinterpret_cast<unsigned short*>(T.act_peer[p] + P.FF) + T.ff_g0;
-            for (int i = tid; i < T.ff_g1 - T.ff_g0; i += DNT) d2[i] = __ldcg(s2 + i);
-        } else if (kind == 4) {
-            const Job& jb = sm.jobs[4 * l + 3];
-            const size_t off = (size_t)jb.part_off + (size_t)T.e_g0 * jb.ks * 32, cnt = (size_t)(T.e_g1 - T.e_g0) * jb.ks * 32;
-            const double2* s = reinterpret_cast<const double2*>(P.part + off);
-            double2* d = reinterpret_cast<double2*>(T.part_peer[p] + off);
-            for (size_t i = tid; i < cnt / 2; i += DNT) d[i] = __ldcg(s + i);
-        } else if (tid == 0) {
-            float* cp = reinterpret_cast<float*>(T.flags_peer[p] + 16);
-            cp[2 * T.rank] = cand_local[2 * T.rank];
-            reinterpret_cast<int*>(cp)[2 * T.rank + 1] = reinterpret_cast<int*>(cand_local)[2 * T.rank + 1];
-        }
-    }
-    __threadfence_system();                                    // this thread's peer stores are performed before the flag below
-    __syncthreads();
-    if (tid == 0) *ok_s = 1;
-    __syncthreads();
-    if (tid < T.world && tid != T.rank) {
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(T.flags_peer[tid] + T.rank), "r"(epoch) : "memory");
-        const unsigned long long t0 = gtime_ns();
-        int v;
-        for (unsigned it = 0;; it++) {
-            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(T.flags_local + tid) : "memory");
-            if (v - epoch >= 0) break;
-            if ((it & 63u) == 63u && gtime_ns() - t0 > kWaitBudgetNs) { *ok_s = 0; break; }
-        }
-    }
-    __syncthreads();
-    if (tid == 0) {
-        *epoch_p = epoch;
-        if (kind == 5 && *ok_s) {                              // the overall greedy token: largest value, lowest id on ties
-            float b = __ldcg(cand_local); int t = __ldcg(reinterpret_cast<int*>(cand_local) + 1);
-            for (int r = 1; r < T.world; r++) {
-                const float v = __ldcg(cand_local + 2 * r); const int ix = __ldcg(reinterpret_cast<int*>(cand_local) + 2 * r + 1);
-                if (v > b || (v == b && ix < t)) { b = v; t = ix; }
+            if constexpr (TG) {
+                __half dq; int sq;
+                const int qv8 = quant_block_warp2(v, dq, sq);
+                publish_q8_block<false>(*pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+            } else {
+                P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
             }
-            __stcg(P.cur_token, t); __stcg(P.best_val, b);
-            P.out_tokens[step] = t;
         }
     }
-    __syncthreads();
-    return *ok_s != 0;
+    return true;
 }
-#endif  // MI_TP
 
 // ---- the kernel ---------------------------------------------------------------------
 template <int HD, int G>
@@ -871,8 +1026,9 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     sm.cs = reinterpret_cast<float*>(after_jobs);                 // [HD]: cos then sin
     sm.red = reinterpret_cast<double*>(after_jobs + 1024);         // 32 doubles
     sm.fold = reinterpret_cast<double*>(after_jobs + 1024 + 256);
-    sm.stage = after_jobs + 1024 + 256 + kFoldBytes;
-    __shared__ int s_ok;
+    sm.h = reinterpret_cast<float*>(after_jobs + 1024 + 256 + kFoldBytes);
+    sm.stage = after_jobs + 1024 + 256 + kFoldBytes + ((size_t)P.E * 4 + 127) / 128 * 128;
+    __shared__ int s_tok;
 #if MI_PROF
     if (tid < kProfSlots) s_prof[tid] = 0;
 #endif
@@ -906,58 +1062,79 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     const int maxin = P.E > P.FF ? P.E : P.FF;
     int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage);
     float2* xs_s = reinterpret_cast<float2*>(sm.stage + maxin);
-    unsigned bar_gen = 0;
-    bool ok = true;
-    const bool single = (step1 - step0 == 1) && (ph1 - ph0 == 1);
+    bool ok = true, h_valid = false;                   // h_valid: this CTA's shared-memory copy of the residual stream is current
+    int err_code = MI_ERR_TIMEOUT;
+    const unsigned epoch = __ldcg(P.epoch_dev);
+    const int pos_base = P.pos_dev ? __ldcg(P.pos_dev) : P.pos0;
+    // candidates of the greedy pick: one {value, index} pair of words per CTA (and per GPU when the exchange runs in here)
+    const int cand_world = P.tp.on ? P.tp.world : 1, n_cand = cand_world * (int)gridDim.x;
+    const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * (int)gridDim.x + (int)blockIdx.x) * 2;
 
-    unsigned long long tp = (MI_PROF && P.prof) ? gtime_ns() : 0;
-    for (int step = step0; step < step1 && ok; step++) {
-        const int pos = (P.pos_dev ? __ldcg(P.pos_dev) : P.pos0) + step;
+    auto rope_table = [&](int pos) {                   // cos / sin of this position's angles, fp32 angle as src/cpu_infer.cpp:54
         if (tid < HD / 2) {
-            const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + tid));    // fp32 angle, as src/cpu_infer.cpp:54
+            const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + tid));
             sm.cs[tid] = __double2float_rn(cos(th)); sm.cs[HD / 2 + tid] = __double2float_rn(sin(th));
         }
-        __syncthreads();
+    };
+
+    unsigned long long tp = (MI_PROF && P.prof) ? gtime_ns() : 0;
+    if (step0 < step1) rope_table(pos_base + step0);
+    __syncthreads();
+    for (int step = step0; step < step1 && ok; step++) {
+        const int pos = pos_base + step;
+        if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
+        const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;        // tag of (step, phase 0)
+        if (step > step0 && ph1 != nph) { rope_table(pos); __syncthreads(); }     // (otherwise the previous step's lm_head phase has made the table)
         prof_mark(P, tp, kProfStep);
         for (int ph = ph0; ph < ph1 && ok; ph++) {
             const int l = ph / 5, k = ph == nph - 1 ? 5 : ph % 5;
-            // One call site each for the norm prologue, the copy prologue and the CTA job: the four per-layer GEMV
+            Pub pub;
+            pub.xw = P.xw; pub.tag = tag0 + (unsigned)ph; pub.mute = ph == P.drop_phase;
+#if MI_TP
+            pub.tp = &P.tp;
+#endif
+            // One call site each for the norm prologue, the q8 prologue and the CTA job: the four per-layer GEMV
             // phases run the same instructions (they stay in the instruction cache from phase to phase) and differ
             // only in pointers and in the few lines of their epilogue.
             if (k == 0 || k == 3 || k == 5) {
-                // QKV : h_in  = (l == 0) ? embedding : h_mid + down-projection partials of layer l-1
-                // GU  : h_mid = h_in + O-projection partials
-                // LM  : final norm over h_mid + last down-projection partials
-                const float* src = nullptr; const double* part = nullptr; float* commit = nullptr; const float* nw = nullptr;
-                int tok = 0, pks = 0;
+                // QKV : h = (l == 0) ? embedding : h + down projection of layer l-1        (committed as h_in)
+                // GU  : h = h + O projection                                                 (committed as h_mid)
+                // LM  : final norm over h + last down projection
+                const float* gsrc = nullptr; const unsigned long long* addw = nullptr; float* commit = nullptr; const float* nw = nullptr;
+                int tok = 0; bool embed = false;
                 if (k == 0 && l == 0) {
-                    tok = step < P.n_forced ? __ldg(P.in_tokens + step) : __ldcg(P.cur_token);
+                    embed = true;
+                    tok = step < P.n_forced ? __ldg(P.in_tokens + step) : (step == step0 ? __ldcg(P.cur_token) : s_tok);
+                    tok = min(max(tok, 0), P.V - 1);
                     commit = P.h_in; nw = sm.lp[0].attn_norm;
                 } else if (k == 0) {
-                    const Job& dj = sm.jobs[4 * (l - 1) + 3];
-                    src = P.h_mid; part = P.part + dj.part_off; pks = dj.ks; commit = P.h_in; nw = sm.lp[l].attn_norm;
+                    gsrc = h_valid ? nullptr : P.h_mid; addw = P.xw + P.xo.down; commit = P.h_in; nw = sm.lp[l].attn_norm;
                 } else if (k == 3) {
-                    const Job& oj = sm.jobs[4 * l + 1];
-                    src = P.h_in; part = P.part + oj.part_off; pks = oj.ks; commit = P.h_mid; nw = sm.lp[l].ffn_norm;
+                    gsrc = h_valid ? nullptr : P.h_in; addw = P.xw + P.xo.o; commit = P.h_mid; nw = sm.lp[l].ffn_norm;
                 } else {
-                    const Job& dj = sm.jobs[4 * (P.L - 1) + 3];
-                    src = P.h_mid; part = P.part + dj.part_off; pks = dj.ks; nw = P.out_norm;
+                    gsrc = h_valid ? nullptr : P.h_mid; addw = P.xw + P.xo.down; nw = P.out_norm;
                 }
-                stage_norm_q8(P, src, tok, part, pks, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s);
+                ok = stage_norm_q8(P, sm.h, gsrc, embed, tok, addw, pub.tag - 1u, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s, tp);
+                h_valid = true;
                 prof_mark(P, tp, 2 * k);
             } else if (k == 2 || k == 4) {
-                if (k == 2) stage_copy_q8(P.att_q, P.att_d, P.E / 32, xq_s, xs_s);
-                else stage_copy_q8(P.act_q, P.act_d, P.FF / 32, xq_s, xs_s);
-                prof_mark(P, tp, 2 * k);
+                const Job& jb = sm.jobs[4 * l + (k == 2 ? 1 : 3)];
+                if (ws.first_cta_unit(jb) < jb.n_units) {        // only CTAs that have a unit of the job consume its input
+                    prof_mark(P, tp, 2 * k);
+                    if (k == 2) ok = stage_poll_q8(P, P.xw + P.xo.att, P.NH * HD, pub.tag - 1u, xq_s, xs_s);
+                    else ok = stage_poll_q8(P, P.xw + P.xo.act, P.FF, pub.tag - 1u, xq_s, xs_s);
+                    prof_mark(P, tp, kProfWait);
+                }
             }
+            if (!ok) break;
             if (k == 1) {
-                if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G>(P, l, pos, sm.stage, tp);
-                else attention_phase<HD, G, G>(P, l, pos, sm.stage, tp);
+                if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, tp, pub.tag - 1u, &pub);
+                else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, tp, pub.tag - 1u, &pub);
             } else if (k != 5) {
                 const int jn = 4 * l + (k == 0 ? 0 : k == 2 ? 1 : k == 3 ? 2 : 3);
                 const float* bias = sm.lp[l].bqkv;
-                const int nq = P.NH * HD, part_off = sm.jobs[jn].part_off;
-                ok = run_cta_job(ws, P, sm, jn, lane, xq_s, xs_s, tp, [&](int g, int ln, float v0, float v1) {
+                const int nq = P.NH * HD;
+                ok = run_cta_job(ws, P, sm, jn, lane, xq_s, xs_s, pub, tp, [&](int g, int ln, float v0, float v1) {
                     if (k == 0) {                                            // + bias, RoPE, packed q / k / v
                         const int p = g * 32 + ln;
                         const float v = __fadd_rn(v0, __ldg(bias + p));
@@ -969,15 +1146,17 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                             if ((within & 1) == 0) out = __double2float_rn(__dsub_rn(__dmul_rn((double)v, c), __dmul_rn((double)partner, s)));
                             else out = __double2float_rn(__dadd_rn(__dmul_rn((double)partner, s), __dmul_rn((double)v, c)));
                         }
-                        if (p < nq + 2 * P.KVD) __stcg(P.qkv_out + p, out);
+                        if (p < nq + 2 * P.KVD) pub.local(P.xo.qkv + p, __float_as_uint(out));
                     } else if (k == 3) {                                     // SwiGLU of (gate, up), one q8_0 block per warp
                         const double gd = (double)v0;
                         const float a = __double2float_rn(__dmul_rn(__ddiv_rn(gd, __dadd_rn(1.0, exp_shared(-gd))), (double)v1));
-                        const int r = g * 32 + ln;                            // FF is a multiple of 32
-                        const int qv = quant_block_warp(a, ln, nullptr, P.act_d + g);
-                        P.act_q[r] = (int8_t)qv;
-                    } else {                                                 // O / down, unsplit: the "partial" is the whole sum; one path for the consumer
-                        __stcg(P.part + part_off + (size_t)g * 32 + ln, (double)v0);
+                        __half dq; int sq;
+                        const int qv = quant_block_warp2(a, dq, sq);         // FF is a multiple of 32: group g is block g
+                        publish_q8_block<true>(pub, P.xo.act, P.xo.act + P.FF / 4, g, ln, qv, dq, sq);
+                    } else if (k == 2) {
+                        pub.local(P.xo.o + g * 32 + ln, __float_as_uint(v0));
+                    } else {
+                        pub.shared(P.xo.down + g * 32 + ln, __float_as_uint(v0));
                     }
                 });
             } else {
@@ -988,7 +1167,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                     const int r = g * 32 + ln;
                     if (r < P.V) {
                         if (lg) lg[r] = v0;
-                        if (v0 > best || (v0 == best && r < bidx)) { best = v0; bidx = r; }
+                        // the reference's scan starts from logits[0] and moves on strict '>' (src/cpu_infer.cpp:153-154): a NaN
+                        // never wins, and a NaN in row 0 is never beaten
+                        const float vv = (r == 0 && v0 != v0) ? INFINITY : v0;
+                        if (vv > best || (vv == best && r < bidx)) { best = vv; bidx = r; }
                     }
                 });
                 #pragma unroll
@@ -1002,42 +1184,47 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 __syncthreads();
                 if (tid == 0) {
                     for (int w = 1; w < DNW; w++) if (cv[w] > cv[0] || (cv[w] == cv[0] && ci[w] < ci[0])) { cv[0] = cv[w]; ci[0] = ci[w]; }
-                    __stcg(P.cand_val + blockIdx.x, cv[0]); __stcg(P.cand_idx + blockIdx.x, ci[0]);
-                    __threadfence();
-                    const unsigned prev = atomicAdd(P.cand_cnt, 1u);
-                    if (prev == gridDim.x - 1) {                        // last CTA: final pick over all CTAs' candidates
-                        __threadfence();
-                        float b = -INFINITY; int bi = 0x7fffffff;
-                        for (unsigned c = 0; c < gridDim.x; c++) {
-                            const float v = __ldcg(P.cand_val + c); const int ix = __ldcg(P.cand_idx + c);
-                            if (v > b || (v == b && ix < bi)) { b = v; bi = ix; }
+                    pub.shared(my_cand, __float_as_uint(cv[0]));
+                    pub.shared(my_cand + 1, (unsigned)ci[0]);
+                }
+                // the next step's angles while the other CTAs' candidates arrive
+                if (step + 1 < step1) rope_table(pos + 1);
+                // every CTA makes the pick over all candidates itself (the same bits everywhere); CTA 0 writes it out
+                prof_mark(P, tp, 2 * k + 1);
+                best = -INFINITY; bidx = 0x7fffffff;
+                bool okc = ok;
+                for (int c0 = 0; c0 < n_cand && okc; c0 += 2 * DNT) {
+                    unsigned cw[4], valid = 0;
+                    if (c0 + tid < n_cand) valid |= 3u;
+                    if (c0 + DNT + tid < n_cand) valid |= 12u;
+                    const unsigned long long* cb = P.xw + P.xo.cand + (size_t)(c0 + tid) * 2;
+                    okc = tw_poll(P, pub.tag, valid, [&](int q) { return cb + (q >> 1) * (2 * DNT) + (q & 1); }, cw);
+                    #pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        if (okc && (valid >> (2 * h) & 1u)) {
+                            const float v = __uint_as_float(cw[2 * h]); const int ix = (int)cw[2 * h + 1];
+                            if (v > best || (v == best && ix < bidx)) { best = v; bidx = ix; }
                         }
-                        *P.cand_cnt = 0;
-                        __stcg(P.cur_token, bi);
-                        __stcg(P.best_val, b);
-                        P.out_tokens[step] = bi;
                     }
+                }
+                prof_mark(P, tp, kProfWait);
+                #pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+                    if (ob > best || (ob == best && oi < bidx)) { best = ob; bidx = oi; }
+                }
+                ok = __syncthreads_and(okc ? 1 : 0) != 0;       // also: cv / ci are free again
+                if (lane == 0) { cv[warp] = best; ci[warp] = bidx; }
+                __syncthreads();
+                if (tid == 0) {
+                    for (int w = 1; w < DNW; w++) if (cv[w] > cv[0] || (cv[w] == cv[0] && ci[w] < ci[0])) { cv[0] = cv[w]; ci[0] = ci[w]; }
+                    const int t = ci[0] == 0x7fffffff ? 0 : ci[0];
+                    s_tok = t;
+                    if (blockIdx.x == 0 && ok) { __stcg(P.cur_token, t); __stcg(P.best_val, cv[0]); P.out_tokens[step] = t; }
                 }
             }
             ok = __syncthreads_and(ok ? 1 : 0) != 0;          // a wait that gave up in one warp stops the whole CTA
             prof_mark(P, tp, 2 * k + 1);
-            if (!ok) break;
-            const bool last = (step == step1 - 1) && (ph == ph1 - 1);
-#if MI_TP
-            if (P.tp.on && k >= 3) {
-                // sharded phase: all CTAs' rows are in local memory -> CTA 0 exchanges with the other GPUs -> everybody goes on
-                ok = grid_barrier(P.bar, bar_gen, &s_ok);
-                if (ok && blockIdx.x == 0) {
-                    __shared__ int s_xok;
-                    ok = tp_peer_exchange(P, sm, k, l, step, &s_xok);
-                }
-                ok = __syncthreads_and(ok ? 1 : 0) != 0;
-                if (!ok) break;
-                if (!last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
-            } else
-#endif
-            if (!single && !last) ok = grid_barrier(P.bar, bar_gen, &s_ok);
-            prof_mark(P, tp, kProfBarrier);
         }
     }
 #if MI_PROF
@@ -1046,8 +1233,11 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         if (tid < kProfSlots) P.prof[tid] += s_prof[tid];
     }
 #endif
+    // CTA 0 has seen every CTA's last candidates (or has given up after a full time budget): all CTAs have read the epoch
+    if (blockIdx.x == 0 && tid == 0 && (ph1 == nph || !ok))
+        *P.epoch_dev = epoch + (unsigned)(step1 - step0) * (unsigned)nph + (ok ? 0u : (unsigned)nph);
     if (!ok) {
-        if (lane == 0) atomicMax(P.err, MI_ERR_TIMEOUT);
+        if (lane == 0) atomicMax(P.err, err_code);
         ws.drain();
     }
 }

@@ -16,6 +16,8 @@ struct mi_ctx {
     int sm_count = 0;
     int smem_optin = 0;
     int* d_err = nullptr;            // device error word (0 = none)
+    unsigned long long wait_ns = 2000000000ull;   // time budget of the decode kernel's device-side waits (mi_ctx_set_wait_budget_ns)
+    unsigned long long errors_reported = 0;       // device errors that mi_ctx_sync has reported so far
     // scratch of the split-K GEMV: partial sums and self-resetting arrival counters
     double* part = nullptr; size_t part_count = 0;
     unsigned* counters = nullptr; size_t n_counters = 0;

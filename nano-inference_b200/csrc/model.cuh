@@ -39,17 +39,16 @@ struct mi_model {
     int* d_in_tokens = nullptr; int in_capacity = 0;
     int* d_out_tokens = nullptr; int out_capacity = 0;
     size_t smem = 0;
-    size_t part_count = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* prof_buf = nullptr;
-    uint8_t* act_buf = nullptr;          // [act_q | act_d]
     float* best_buf = nullptr;           // {best logit value, greedy token (int bits)}
     int qkv_rows = 0;
-    int* tp_flags = nullptr;              // peer exchange: flags, epoch, gathered argmax candidates (see tp_peer.cu)
-    void* tp_peer[8][3] = {};             // per rank: activations, partial sums, flag block (own entries = local pointers)
+    int* tp_flags = nullptr;              // host-driven peer exchange: flags, epoch, gathered argmax candidates (see tp_peer.cu)
+    void* tp_peer[8][3] = {};             // per rank: exchange block, (unused), flag block (own entries = local pointers)
+    unsigned long long errors_seen = 0;   // value of the context's error count when this model last cleared its counters
     bool tp_peer_on = false;
     std::vector<void*> ipc_opened;        // peer mappings to close
-    int* d_pos = nullptr;                 // device-resident position for position-free launch sequences
+    int* d_pos = nullptr;                 // [2]: device-resident position for position-free launch sequences; the tag epoch
     std::vector<mi_weight> views;         // [4L+1] whole matrices in job order (QKV, O, gate/up, down per layer; lm_head), for the M-token step
     std::vector<mi::LayerPtrs> layer_ptrs;    // host copy of the per-layer norm / bias pointers
     mi::VerifyBufs vb;                    // buffers of the M-token step, allocated on first use

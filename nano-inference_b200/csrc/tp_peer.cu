@@ -1,9 +1,11 @@
-// Tensor parallelism without a collective library call on the token path: after a sharded
-// phase every GPU stores the slice it owns straight into every peer's copy of the exchanged
-// buffer over NVLink (peer pointers from CUDA IPC handles, one process per GPU), then tells
-// each peer so through a flag in the peer's memory and waits - bounded - for the peers'
-// flags.  One small kernel per exchange; the same sequence of exchanges runs on every GPU,
-// so one monotonic epoch number per GPU identifies them.  The reference is single-GPU: no
+// Peer-memory plumbing of tensor parallelism (one process per GPU): CUDA IPC handles of the
+// model's exchange block, so that the decode kernel can store its tagged words straight into
+// the other GPUs' copies over NVLink (the exchange inside the kernel needs nothing else), and
+// a host-driven form of the same exchange for phase-by-phase launch sequences: after a sharded
+// phase one small kernel stores the slice this GPU owns into every peer's copy of the
+// exchanged vector, then tells each peer so through a flag in the peer's memory and waits -
+// bounded - for the peers' flags.  The same sequence of exchanges runs on every GPU, so one
+// monotonic epoch number per GPU identifies them.  The reference is single-GPU: no
 // counterpart there.
 //
 // Why no later push can overwrite data a slower GPU still reads: the exchanges of a layer
@@ -45,10 +47,10 @@ __global__ void __launch_bounds__(1024) tp_exchange_kernel(const PeerXchg X) {
                 const uint4* s = reinterpret_cast<const uint4*>(X.local + off);
                 uint4* d = reinterpret_cast<uint4*>(X.peer[p] + off);
                 for (long long i = tid; i < (len >> 4); i += blockDim.x) d[i] = __ldcg(s + i);
-            } else {                                   // fp16 scales: two-byte granularity
-                const unsigned short* s = reinterpret_cast<const unsigned short*>(X.local + off);
-                unsigned short* d = reinterpret_cast<unsigned short*>(X.peer[p] + off);
-                for (long long i = tid; i < (len >> 1); i += blockDim.x) d[i] = __ldcg(s + i);
+            } else {                                   // every exchanged range is made of 8-byte words
+                const unsigned long long* s = reinterpret_cast<const unsigned long long*>(X.local + off);
+                unsigned long long* d = reinterpret_cast<unsigned long long*>(X.peer[p] + off);
+                for (long long i = tid; i < (len >> 3); i += blockDim.x) d[i] = __ldcg(s + i);
             }
         }
     }
@@ -76,8 +78,8 @@ __global__ void __launch_bounds__(1024) tp_exchange_kernel(const PeerXchg X) {
 
 }  // namespace
 
-// Handles of the four allocations the exchanges touch, 64 bytes each: gate/up activations, partial sums,
-// flag block, candidate block.
+// Three handles of 64 bytes each: the exchange block (twice: the second slot is kept for layout compatibility) and the
+// flag block of the host-driven exchange.
 extern "C" int mi_tp_ipc_handles(mi_ctx* ctx, mi_model* m, void* out_host) {
     if (!ctx) return MI_ERR_INVALID;
     if (!m || !out_host) return set_error(ctx, MI_ERR_INVALID, "tp_ipc_handles: null argument");
@@ -89,8 +91,8 @@ extern "C" int mi_tp_ipc_handles(mi_ctx* ctx, mi_model* m, void* out_host) {
     }
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
     cudaIpcMemHandle_t* h = reinterpret_cast<cudaIpcMemHandle_t*>(out_host);
-    MI_CUDA(ctx, cudaIpcGetMemHandle(&h[0], m->act_buf));
-    MI_CUDA(ctx, cudaIpcGetMemHandle(&h[1], m->P.part));
+    MI_CUDA(ctx, cudaIpcGetMemHandle(&h[0], m->P.xw));
+    h[1] = h[0];
     MI_CUDA(ctx, cudaIpcGetMemHandle(&h[2], m->tp_flags));
     return MI_OK;
 }
@@ -104,15 +106,16 @@ extern "C" int mi_tp_ipc_open(mi_ctx* ctx, mi_model* m, const void* all_host) {
     MI_CUDA(ctx, cudaSetDevice(ctx->device));
     const cudaIpcMemHandle_t* h = reinterpret_cast<const cudaIpcMemHandle_t*>(all_host);
     for (int r = 0; r < m->tp_world; r++) {
-        for (int k = 0; k < 3; k++) {
+        for (int k = 0; k < 3; k += 2) {               // slot 1 repeats slot 0: one mapping serves both
             void* p = nullptr;
-            if (r == m->tp_rank) p = k == 0 ? (void*)m->act_buf : k == 1 ? (void*)m->P.part : (void*)m->tp_flags;
+            if (r == m->tp_rank) p = k == 0 ? (void*)m->P.xw : (void*)m->tp_flags;
             else {
                 MI_CUDA(ctx, cudaIpcOpenMemHandle(&p, h[r * 3 + k], cudaIpcMemLazyEnablePeerAccess));
                 m->ipc_opened.push_back(p);
             }
             m->tp_peer[r][k] = p;
         }
+        m->tp_peer[r][1] = m->tp_peer[r][0];
     }
     m->tp_peer_on = true;
     return MI_OK;
@@ -129,18 +132,18 @@ extern "C" int mi_tp_exchange(mi_ctx* ctx, mi_model* m, int which, int layer) {
     for (int r = 0; r < m->tp_world; r++) X.flags_peer[r] = reinterpret_cast<int*>(m->tp_peer[r][2]);
     int g0, g1;
     if (which == MI_TP_ACT) {
+        // tagged words of the q8_0 vector: 8 value words per block, then one scale word per block
         mi_tp_partition(m->FF / 32, m->tp_rank, m->tp_world, &g0, &g1);
-        X.local = m->act_buf;
+        X.local = reinterpret_cast<uint8_t*>(m->P.xw);
         for (int r = 0; r < m->tp_world; r++) X.peer[r] = reinterpret_cast<uint8_t*>(m->tp_peer[r][0]);
-        X.off[0] = (long long)g0 * 32; X.len[0] = (long long)(g1 - g0) * 32;                       // int8 values
-        X.off[1] = (long long)m->FF + (long long)g0 * 2; X.len[1] = (long long)(g1 - g0) * 2;     // fp16 scales
+        X.off[0] = ((long long)m->P.xo.act + (long long)g0 * 8) * 8; X.len[0] = (long long)(g1 - g0) * 64;
+        X.off[1] = ((long long)m->P.xo.act + m->FF / 4 + g0) * 8; X.len[1] = (long long)(g1 - g0) * 8;
     } else if (which == MI_TP_PART_DOWN) {
         if (layer < 0 || layer >= m->L) return set_error(ctx, MI_ERR_INVALID, "tp_exchange: bad layer");
-        const Job& jb = m->jobs[4 * layer + 3];
         mi_tp_partition((m->E + 31) / 32, m->tp_rank, m->tp_world, &g0, &g1);
-        X.local = reinterpret_cast<uint8_t*>(m->P.part);
-        for (int r = 0; r < m->tp_world; r++) X.peer[r] = reinterpret_cast<uint8_t*>(m->tp_peer[r][1]);
-        X.off[0] = ((long long)jb.part_off + (long long)g0 * jb.ks * 32) * 8; X.len[0] = (long long)(g1 - g0) * jb.ks * 32 * 8;
+        X.local = reinterpret_cast<uint8_t*>(m->P.xw);
+        for (int r = 0; r < m->tp_world; r++) X.peer[r] = reinterpret_cast<uint8_t*>(m->tp_peer[r][0]);
+        X.off[0] = ((long long)m->P.xo.down + (long long)g0 * 32) * 8; X.len[0] = (long long)(g1 - g0) * 256;
     } else if (which == MI_TP_BEST) {
         // candidates live behind the flags: [kMaxWorld + 8 ints] then [world] x {float, int}; this GPU's own entry first
         // moves from the model's {value, token} pair into its slot, then the slot goes to the peers

@@ -181,3 +181,83 @@ def test_long_context_attention_paths_match_oracle(ctx, pkg, cases):
             worst = max(worst, rel_err(logits[s].cpu().numpy(), lo))
     assert worst < REL_TOL, f"logits deviate {worst:.2e}"
     m.free()
+
+
+def test_ksplit_fold_and_odd_block_counts_match_oracle(ctx, pkg, tmp_path):
+    """A shape whose down projection is K-split across CTAs (FFN 1056 = 33 blocks: one-block tiles, four splits per row
+    group, the split-0 CTA folding the others' tagged partial sums) and whose activation vector has an odd number of
+    q8_0 blocks (the pad word of the tagged layout)."""
+    import torch
+    path = gu.make_synthetic(tmp_path / "k.gguf", "tiny", seed=5, std=0.2,
+                             extra=["--bias-std", 0.2, "--layers", 3, "--embd", 128, "--ff", 1056, "--heads", 4, "--kv-heads", 2, "--vocab", 700])
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    n = 20
+    seq = [int(t) for t in np.random.default_rng(6).integers(0, V, n)]
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n + 1)
+    outs = []
+    for mode in (pkg.DECODE_PERSISTENT, pkg.DECODE_PER_PHASE):
+        m = pkg.Model(ctx, path, n + 1)
+        logits = torch.zeros((n, V), dtype=torch.float32, device="cuda")
+        pred, _ = m.decode(seq, n, 0, logits, mode)
+        outs.append((pred, logits.cpu().numpy()))
+        m.free()
+    assert outs[0][0] == outs[1][0] and np.array_equal(outs[0][1], outs[1][1])
+    worst = 0.0
+    for s, t in enumerate(seq):
+        tok, lo, _ = orc.forward(t)
+        assert tok == outs[0][0][s]
+        worst = max(worst, rel_err(outs[0][1][s], lo))
+    assert worst < REL_TOL, f"logits deviate {worst:.2e}"
+
+
+def test_a_wait_that_cannot_complete_times_out_and_the_next_call_is_correct(ctx, pkg, cases):
+    """Every device-side wait is bounded.  With the budget at 2 ms and the producers of one phase muted (a host-side test
+    hook: they compute but publish nothing) the consumers' waits run out: the call returns MI_ERR_TIMEOUT - no hang, no
+    fault - the kernel has drained its bulk copies, and the next ordinary call on the same context and model gives the
+    bits of an undisturbed model."""
+    import torch
+    path, c = cases[1]
+    g = gu.GgufReader(path)
+    V = g.config()["n_vocab"]
+    seq = [int(t) for t in np.random.default_rng(12).integers(0, V, 10)]
+    ref_m = pkg.Model(ctx, path, 32)
+    ref_logits = torch.zeros((len(seq), V), dtype=torch.float32, device="cuda")
+    want, _ = ref_m.decode(seq, len(seq), 0, ref_logits)
+    ref_m.free()
+    m = pkg.Model(ctx, path, 32)
+    ctx.set_wait_budget_ns(2_000_000)
+    try:
+        for phase in (0, 1, 3, 4, 5 * g.config()["n_layer"]):        # QKV, attention, gate/up, down of layer 0; lm_head
+            m.debug_drop_phase(phase)
+            with pytest.raises(pkg.MinferError) as e:
+                m.decode(seq, len(seq), 0)
+            assert e.value.status == 4, "expected MI_ERR_TIMEOUT"
+            m.debug_drop_phase(-1)
+            logits = torch.zeros((len(seq), V), dtype=torch.float32, device="cuda")
+            got, _ = m.decode(seq, len(seq), 0, logits)
+            assert got == want and torch.equal(logits.view(torch.int32), ref_logits.view(torch.int32)), f"after a time-out in phase {phase}"
+    finally:
+        ctx.set_wait_budget_ns(2_000_000_000)
+        m.debug_drop_phase(-1)
+    m.free()
+
+
+def test_decoding_past_the_kv_cache_is_refused_on_the_device_too(ctx, pkg, cases):
+    """The device-resident position (position-free launch sequences) is checked by the kernel itself: a step at a
+    position outside the cache records MI_ERR_LIMIT and touches nothing."""
+    path, _ = cases[0]
+    m = pkg.Model(ctx, path, 8)
+    m.set_token(3)
+    m.set_pos(7)
+    L = m.config.n_layer
+    m.launch_fused(pkg.POS_DEVICE, 0, 5 * L + 1)
+    ctx.sync()
+    kc_before = m.state("kcache", np.float16, 64).copy()
+    m.advance_pos(1)                                                  # position 8 of a cache of 8
+    m.launch_fused(pkg.POS_DEVICE, 0, 5 * L + 1)
+    with pytest.raises(pkg.MinferError) as e:
+        ctx.sync()
+    assert e.value.status == 8, "expected MI_ERR_LIMIT"
+    assert np.array_equal(m.state("kcache", np.float16, 64), kc_before)
+    m.free()
