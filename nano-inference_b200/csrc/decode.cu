@@ -163,6 +163,13 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     m->grid = ctx->sm_count;
     if (const char* gs = getenv("MINFER_GRID")) { int v = atoi(gs); if (v > 0 && v <= ctx->sm_count) m->grid = v; }
     m->max_chunks = std::max(1, m->grid / m->NKV);
+    // CTAs set aside for attention (see DecodeParams::attn_ctas): one per query head, where the grid is large enough to spare them
+    {
+        const int G = m->G, hpc = (G % 2 == 0 && G > 2) ? G / 2 : (G <= 2 ? 1 : G);      // attn_heads_per_cta<G>()
+        m->attn_ctas = (m->NH / hpc * 8 <= m->grid && attn_dedicated_smem(m->HD, hpc) + 1024 <= (size_t)ctx->smem_optin) ? m->NH / hpc : 0;
+        if (const char* ac = getenv("MINFER_ATTN_CTAS")) { int v = atoi(ac); if (v == 0) m->attn_ctas = 0; }
+    }
+    const int GG = m->grid - m->attn_ctas;                // CTAs that carry GEMV units
 
     const int E = m->E, FF = m->FF, HD = m->HD, KVD = m->KVD, L = m->L, V = m->V, NQ = m->NH * m->HD;
     int st = MI_OK;
@@ -219,7 +226,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
 
     // ---- layers
     std::vector<LayerPtrs> lp(L);
-    const int qkv_rows = NQ + 2 * KVD, W = m->grid * DNW;
+    const int qkv_rows = NQ + 2 * KVD, W = GG * DNW;
     m->qkv_rows = qkv_rows;
     int rot = 0, wrot = 0;
     auto add_job = [&](const uint8_t* base, int groups, int cols, int nacc, int kind, int layer) {
@@ -235,16 +242,16 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         if (!replicated) mi_tp_partition(groups, tp_rank, tp_world, &g0, &g1);
         jb.g_off = g0; jb.groups = g1 - g0;
         jb.base = base + (size_t)g0 * nacc * jb.nt * tile_bytes(jb.kb);
-        jb.ks = plan_ks(kind, replicated ? groups : (groups + tp_world - 1) / tp_world, jb.nt, m->grid);
+        jb.ks = plan_ks(kind, replicated ? groups : (groups + tp_world - 1) / tp_world, jb.nt, GG);
         const char* force = kind == JOB_DOWN ? getenv("MINFER_KS_DOWN") : nullptr;   // tuning knob
         if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), kMaxKSplit));
-        if (jb.ks >= m->grid) jb.ks = std::max(1, m->grid - 1);       // the CTAs of a row group's splits must be distinct
+        if (jb.ks >= GG) jb.ks = std::max(1, GG - 1);       // the CTAs of a row group's splits must be distinct
         jb.n_units = jb.groups * jb.ks;
         if (kind == JOB_LM) { jb.rot = 0; jb.wrot = 0; }
         else {
             // successive jobs start where the previous one stopped, over CTAs and over the warps of a CTA
             jb.rot = rot; jb.wrot = wrot;
-            rot = (int)(((long long)rot + jb.n_units) % m->grid);
+            rot = (int)(((long long)rot + jb.n_units) % GG);
             wrot = (wrot + nacc * ((jb.nt + jb.ks - 1) / jb.ks)) & (DNW - 1);
         }
         m->jobs.push_back(jb);
@@ -300,7 +307,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
 
     // ---- per-warp tile lists: the order in which each warp of the grid consumes tiles during one step
     {
-        const int nj = (int)m->jobs.size(), G = m->grid;
+        const int nj = (int)m->jobs.size(), G = GG;
         std::vector<std::vector<unsigned long long>> lists((size_t)G * DNW);
         std::vector<unsigned> start((size_t)G * DNW * (nj + 1), 0);
         for (int j = 0; j < nj; j++) {
@@ -390,11 +397,16 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         MI_CUDA(ctx, cudaMemcpy(m->d_pos, init, sizeof(init), cudaMemcpyHostToDevice));
     }
     P.epoch_dev = reinterpret_cast<unsigned*>(m->d_pos + 1);
-    P.drop_phase = -1;
+    P.drop_phase = -1; P.attn_ctas = m->attn_ctas; P.prof_cta = m->attn_ctas;
+    if (const char* pc = getenv("MINFER_PROFILE_CTA")) P.prof_cta = std::max(0, std::min(atoi(pc), m->grid - 1));
     P.max_seq = max_seq; P.max_chunks = m->max_chunks; P.err = ctx->d_err;
     m->prof_buf = P.prof;
     if (!getenv("MINFER_PROFILE")) P.prof = nullptr;         // the buffer exists either way; kernels only write it when asked
     m->smem = decode_smem_bytes((int)m->jobs.size(), E, FF, HD, m->G);
+    if (m->attn_ctas > 0) {
+        const int hpc = (m->G % 2 == 0 && m->G > 2) ? m->G / 2 : (m->G <= 2 ? 1 : m->G);
+        m->smem = std::max(m->smem, attn_dedicated_smem(HD, hpc));       // the attention CTAs lay the same allocation out their own way
+    }
     if (m->smem > (size_t)ctx->smem_optin)
         return set_error(ctx, MI_ERR_UNSUPPORTED, "model: decode kernel needs %zu bytes of shared memory, %d available", m->smem, ctx->smem_optin);
     MI_CUDA(ctx, cudaEventCreate(&m->ev0));

@@ -62,6 +62,12 @@
 // observed, not proved.  Each token is processed exactly as if it were alone.
 #pragma once
 #include "gemv_core.cuh"
+#ifndef MI_ATT_FN
+#define MI_ATT_FN static __device__ __noinline__
+#endif
+#ifndef MI_PIECE
+#define MI_PIECE __forceinline__
+#endif
 
 // The kernel exists in three builds.  The default one carries no profiling code and no peer stores.  A translation unit
 // that defines MI_PROF 1 before including this file gets the instrumented build (timer marks between the hot instructions
@@ -89,6 +95,7 @@ constexpr int DNT = DNW * 32;
 constexpr int DS = 3;             // ring slots per warp
 constexpr int DSLOT = 4608;       // bytes per slot: the largest tile (8 blocks)
 constexpr int kAttnChunk = 64;    // smallest KV range worth its own CTA
+constexpr int kShortAttnMax = 256;      // up to this many cached positions one CTA handles the whole range of a query head (attention_short)
 constexpr int kPerHeadAttnMax = 1024;   // up to this many cached positions a CTA handles one query head, beyond it a whole GQA group
 constexpr int kMaxKSplit = 4;     // cross-CTA K-splits of the down projection
 constexpr int kMaxWorldTP = 8;
@@ -169,7 +176,13 @@ struct DecodeParams {
     int pos0;
     const int* pos_dev;              // optional: first position read from device memory instead (a captured launch sequence stays position-free)
     int* err;
-    unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA 0 (see kProf*)
+    unsigned long long* prof;        // optional [32]: nanoseconds per phase part on CTA prof_cta (see kProf*)
+    int prof_cta;
+    // CTAs [0, attn_ctas) do nothing but attention; the GEMV phases (and the greedy pick) are dealt over the other
+    // CTAs [attn_ctas, grid).  At short context one CTA per query head runs attention, and a CTA that also carried GEMV
+    // units would walk both phases' code every layer; kept apart, each CTA's instructions stay in its instruction cache.
+    // 0: every CTA does everything.  Beyond kShortAttnMax positions the GEMV CTAs take attention chunks as well.
+    int attn_ctas;
     TpPeerParams tp;
 };
 
@@ -205,10 +218,11 @@ __host__ __device__ inline size_t decode_smem_bytes(int njobs, int E, int FF, in
 // timer read and a shared-memory add, not a global round trip on the critical path.
 #if MI_PROF
 __shared__ unsigned long long s_prof[kProfSlots];
+__shared__ unsigned long long s_prof_t;          // start of the open interval (thread 0 of the profiled CTA)
 #endif
-__device__ __forceinline__ void prof_mark(const DecodeParams& P, unsigned long long& t, int k) {
+__device__ __forceinline__ void prof_mark(const DecodeParams& P, int k) {
 #if MI_PROF
-    if (P.prof && blockIdx.x == 0 && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); s_prof[k] += n - t; t = n; }
+    if (P.prof && (int)blockIdx.x == P.prof_cta && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); s_prof[k] += n - s_prof_t; s_prof_t = n; }
 #endif
 }
 
@@ -261,9 +275,23 @@ static __device__ __noinline__ bool tw_spin(const unsigned long long* p, unsigne
     }
 }
 
+// One warp waits together: the lowest lane that misses a word polls that word, the other lanes sit at the vote, so a
+// waiting warp keeps one load in flight, not thirty-two (148 CTAs polling with every thread load the L2 as hard as the
+// weight stream does).  Called by all lanes of a warp with the first missing address of each (null: none).  Returns 0 when
+// no lane misses anything, 1 after the polled word has arrived (every lane then fetches its missing words again), -1 when
+// the wait gave up.
+__device__ __forceinline__ int tw_wait_warp(const unsigned long long* miss, unsigned tag, unsigned long long budget_ns, const int* err) {
+    const unsigned mm = __ballot_sync(0xffffffffu, miss != nullptr);
+    if (!mm) return 0;
+    const int leader = __ffs(mm) - 1;
+    int r = 1;
+    if ((int)(threadIdx.x & 31) == leader) r = tw_spin(miss, tag, budget_ns, err) ? 1 : -1;
+    return __shfl_sync(0xffffffffu, r, leader);
+}
+
 // Load the N words addr(k) (k with bit k of `valid` set) and return their payloads once all carry `tag`.  All loads are
-// issued before any is looked at; if some word is not there yet, the thread polls the first such word and then fetches
-// every missing word again (they were produced together, most have landed meanwhile).
+// issued before any is looked at; if some word is not there yet, the warp polls one such word and then every lane fetches
+// its missing words again (they were produced together, most have landed meanwhile).  All 32 lanes of a warp must call.
 template <int N, class AddrFn>
 __device__ __forceinline__ bool tw_poll(const DecodeParams& P, unsigned tag, unsigned valid, AddrFn addr, unsigned (&out)[N]) {
     unsigned long long w[N];
@@ -273,8 +301,9 @@ __device__ __forceinline__ bool tw_poll(const DecodeParams& P, unsigned tag, uns
         const unsigned long long* miss = nullptr;
         #pragma unroll
         for (int k = N - 1; k >= 0; k--) if (!tw_is(w[k], tag)) miss = addr(k);
-        if (!miss) break;
-        if (!tw_spin(miss, tag, P.wait_ns, P.err)) return false;
+        const int st = tw_wait_warp(miss, tag, P.wait_ns, P.err);
+        if (st == 0) break;
+        if (st < 0) return false;
         #pragma unroll
         for (int k = 0; k < N; k++) if (!tw_is(w[k], tag)) w[k] = tw_ld(addr(k));
     }
@@ -316,13 +345,16 @@ struct WarpStream {
     unsigned long long next;         // entry at the cursor (valid while left > 0)
     int issued, consumed;
     int W, sid, warp;                // warp slots in the grid, this warp's slot, warp in CTA
+    int gcta, ggrid;                 // this CTA's index among the CTAs that carry GEMV units (negative: attention only), their number
     uint64_t policy;                 // L2 evict-first for the weight stream
 
     __device__ __forceinline__ void init(const DecodeSmem& sm, const DecodeParams& P, int warp_, int step0, int step1, int j0, int j1) {
         warp = warp_; policy = l2_policy_evict_first();
         ring = sm.ring + (size_t)warp * DS * DSLOT; bars = sm.bars + warp * DS; jobs = sm.jobs;
-        W = gridDim.x * DNW; sid = warp * gridDim.x + blockIdx.x;      // consecutive warp units land on different SMs
-        const int slot = blockIdx.x * DNW + warp, nj = 4 * P.L + 2;
+        gcta = (int)blockIdx.x - P.attn_ctas; ggrid = (int)gridDim.x - P.attn_ctas;
+        W = ggrid * DNW; sid = warp * ggrid + gcta;      // consecutive warp units land on different SMs
+        if (gcta < 0) { e0 = e1 = c = 0; issued = consumed = 0; left = 0; next = 0ull; tab = nullptr; return; }
+        const int slot = gcta * DNW + warp, nj = 4 * P.L + 2;
         tab = P.tile_tab + (size_t)slot * P.tile_stride;
         e0 = __ldg(P.tile_start + (size_t)slot * nj + j0);
         e1 = __ldg(P.tile_start + (size_t)slot * nj + j1);
@@ -344,7 +376,7 @@ struct WarpStream {
         for (int k = consumed; k < issued; k++) (void)mbar_wait_bounded(&bars[k % DS], (k / DS) & 1);
     }
     __device__ __forceinline__ int first_cta_unit(const Job& jb) const {
-        const int G = (int)gridDim.x, r = jb.rot % G, b = (int)blockIdx.x;
+        const int G = ggrid, r = jb.rot % G, b = gcta;
         return b >= r ? b - r : b + G - r;
     }
     __device__ __forceinline__ int first_warp_unit(const Job& jb) const {
@@ -367,21 +399,21 @@ static __device__ __noinline__ double tile_dot_row_rare(int kb, const uint8_t* t
 
 // consume the next tile of this warp's stream into acc (block index b0 = t * kb)
 __device__ __forceinline__ double tile_consume(WarpStream& ws, int lane, int kb, int t, const int8_t* xq_s, const float2* xs_s,
-                                               double acc, bool& ok, const DecodeParams* PP = nullptr, unsigned long long* tp = nullptr) {
+                                               double acc, bool& ok, const DecodeParams* PP = nullptr) {
     if (!ok) return acc;
     const int slot = ws.consumed % DS;
-    if (tp) prof_mark(*PP, *tp, 18);
+    if (PP) prof_mark(*PP, 18);
     if (!mbar_wait_bounded(&ws.bars[slot], (ws.consumed / DS) & 1)) { ok = false; return acc; }
-    if (tp) prof_mark(*PP, *tp, 20);
+    if (PP) prof_mark(*PP, 20);
     const uint8_t* tile = ws.ring + (size_t)slot * DSLOT;
     if (kb == 8) acc = tile_dot_row<8, false>(tile, lane, t * 8, xq_s, xs_s, acc, nullptr);
     else acc = tile_dot_row_rare(kb, tile, lane, t, xq_s, xs_s, acc);
     ws.consumed++;
     __syncwarp();
-    if (tp) prof_mark(*PP, *tp, 21);
+    if (PP) prof_mark(*PP, 21);
     if (lane == 0) ws.issue_one();
     __syncwarp();
-    if (tp) prof_mark(*PP, *tp, 22);
+    if (PP) prof_mark(*PP, 22);
     return acc;
 }
 
@@ -414,20 +446,20 @@ __device__ __forceinline__ void publish_q8_block(const Pub& pub, int qoff, int s
 // the CTA of split 0 waits for them, adds them to its own in split order and calls epi.
 // Every warp passes the same number of __syncthreads, also after a wait gave up.
 template <class Epi>
-__device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& P, const DecodeSmem& sm, int j, int lane,
-                                            const int8_t* xq_s, const float2* xs_s, const Pub& pub, unsigned long long& tp, Epi epi) {
+__device__ MI_PIECE bool run_cta_job(WarpStream& ws, const DecodeParams& P, const DecodeSmem& sm, int j, int lane,
+                                            const int8_t* xq_s, const float2* xs_s, const Pub& pub, Epi epi) {
     const Job jb = ws.jobs[j];                          // registers: the fields are used many times
     bool ok = true;
     int uidx = 0;
-    for (int u = ws.first_cta_unit(jb); u < jb.n_units; u += (int)gridDim.x, uidx++) {
+    for (int u = ws.first_cta_unit(jb); u < jb.n_units; u += ws.ggrid, uidx++) {
         const UnitShape s = unit_shape(jb, u, uidx);
         double a0 = 0.0, a1 = 0.0;
         for (int i = (ws.warp - s.wrot) & (DNW - 1); i < s.n; i += DNW) {
             const bool first = i < s.ntu;                       // which of the unit's two accumulators (gate / up) the tile feeds
-            const double r = tile_consume(ws, lane, jb.kb, s.t0 + (first ? i : i - s.ntu), xq_s, xs_s, first ? a0 : a1, ok, &P, &tp);
+            const double r = tile_consume(ws, lane, jb.kb, s.t0 + (first ? i : i - s.ntu), xq_s, xs_s, first ? a0 : a1, ok, &P);
             if (first) a0 = r; else a1 = r;
         }
-        prof_mark(P, tp, 18);
+        prof_mark(P, 18);
         double* fb = sm.fold + (size_t)(uidx & 1) * DNW * 2 * 32;
         fb[(ws.warp * 2) * 32 + lane] = a0;
         fb[(ws.warp * 2 + 1) * 32 + lane] = a1;
@@ -446,8 +478,8 @@ __device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& 
                 } else {
                     unsigned pw[2 * (kMaxKSplit - 1)];
                     const unsigned long long* base = P.xw + slot;
-                    if (ok) ok = tw_poll(P, pub.tag, (1u << (2 * (jb.ks - 1))) - 1u, [&](int k) { return base + (k >> 1) * 64 + (k & 1); }, pw);
-                    ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+                    const bool got = tw_poll(P, pub.tag, (1u << (2 * (jb.ks - 1))) - 1u, [&](int k) { return base + (k >> 1) * 64 + (k & 1); }, pw);   // all lanes, always
+                    ok = __all_sync(0xffffffffu, (ok && got) ? 1 : 0) != 0;
                     if (ok) {
                         #pragma unroll
                         for (int q = 0; q < kMaxKSplit - 1; q++)
@@ -459,14 +491,14 @@ __device__ __forceinline__ bool run_cta_job(WarpStream& ws, const DecodeParams& 
                 epi(gg, lane, __double2float_rn(v0), __double2float_rn(v1));
             }
         }
-        prof_mark(P, tp, 19);
+        prof_mark(P, 19);
     }
     return ok;
 }
 
 // lm_head: a unit (row group) belongs to one warp; epi(g, lane, v).
 template <class Epi>
-__device__ __forceinline__ bool run_warp_job(WarpStream& ws, int j, int lane, const int8_t* xq_s, const float2* xs_s, Epi epi) {
+__device__ MI_PIECE bool run_warp_job(WarpStream& ws, int j, int lane, const int8_t* xq_s, const float2* xs_s, Epi epi) {
     const Job jb = ws.jobs[j];
     bool ok = true;
     for (int u = ws.first_warp_unit(jb); u < jb.n_units && ok; u += ws.W) {
@@ -507,19 +539,20 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
 }
 
 // Residual add + RMSNorm + q8_0 staging:
-//   x = h (this CTA's copy of the residual stream in shared memory; or gsrc, the copy CTA 0 committed to global memory,
-//       when the launch starts here; or the embedding row of `token`)
+//   x = h (this CTA's copy of the residual stream in shared memory; or gsrc, the copy the first GEMV CTA committed to
+//       global memory, when the launch starts here; or the embedding row of `token`)
 //       + the projection output published as tagged fp32 words at addw   [if addw]
-//   h = x;  CTA 0 also commits x to global memory;
+//   h = x;  the first GEMV CTA also commits x to global memory;
 //   xq_s / xs_s = q8_0( x * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
-// Warp w owns the 32-element blocks w, w+8, ...; lane = element, so a thread holds at most
-// NB values and everything stays in registers.  All loads (vector, tagged words, norm weights)
-// are requested before anything waits on them, and the NB quantizer chains of a warp are
-// interleaved so their latencies overlap.  Sum of squares in double (every x*x is exact there).
+// Warp w owns the 32-element blocks w, w+8, ...; lane = element, so a thread holds at most NB values and everything
+// stays in registers.  All loads (vector, tagged words, norm weights) are requested before anything waits on them, and
+// the NB quantizer chains of a warp are interleaved so their latencies overlap (a loop over the blocks, quantizing one
+// after the other from shared memory, has a fifth of the instructions and measured 30 % slower).  Sum of squares in
+// double (every x*x is exact there).
 template <int NB>
 __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token,
                                                 const unsigned long long* addw, unsigned tag, float* commit, const float* __restrict__ w,
-                                                int E, float eps, double* red, int8_t* xq_s, float2* xs_s, unsigned long long& tpf) {
+                                                int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nb = E / 32;
     float x[NB], wv[NB];
     unsigned valid = 0;
@@ -544,9 +577,9 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     bool ok = true;
     if (addw) {
         unsigned aw[NB];
-        prof_mark(P, tpf, 23);
+        prof_mark(P, 23);
         ok = tw_poll(P, tag, valid, [&](int k) { return addw + (size_t)(warp + k * DNW) * 32 + lane; }, aw);
-        prof_mark(P, tpf, kProfWait);
+        prof_mark(P, kProfWait);
         #pragma unroll
         for (int k = 0; k < NB; k++) if (valid >> k & 1u) x[k] = __fadd_rn(x[k], __uint_as_float(aw[k]));
     }
@@ -557,16 +590,16 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
         else {
             const int e = (warp + k * DNW) * 32 + lane;
             h_s[e] = x[k];
-            if (commit && blockIdx.x == 0) __stcg(commit + e, x[k]);
+            if (commit && (int)blockIdx.x == P.attn_ctas) __stcg(commit + e, x[k]);
         }
         const double xd = x[k]; ss = __fma_rn(xd, xd, ss);
     }
     #pragma unroll
     for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
     if (lane == 0) red[warp] = ss;
-    prof_mark(P, tpf, 23);
+    prof_mark(P, 23);
     if (!__syncthreads_and(ok ? 1 : 0)) return false;
-    prof_mark(P, tpf, 24);
+    prof_mark(P, 24);
     double tot = 0.0;
     #pragma unroll
     for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
@@ -592,20 +625,20 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
             if (lane == 0) xs_s[b] = make_float2(__half2float(__float2half_rn(__fdiv_rn(a[k], 127.f))), __int2float_rn(8 * sq[k]));
         }
     }
-    prof_mark(P, tpf, 25);
+    prof_mark(P, 25);
     __syncthreads();
-    prof_mark(P, tpf, 26);
+    prof_mark(P, 26);
     return true;
 }
 
 #define MI_NORM_ARGS const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token, const unsigned long long* addw, unsigned tag, \
-                     float* commit, const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s, unsigned long long& tpf
-#define MI_NORM_PASS P, h_s, gsrc, embed, token, addw, tag, commit, w, E, eps, red, xq_s, xs_s, tpf
+                     float* commit, const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s
+#define MI_NORM_PASS P, h_s, gsrc, embed, token, addw, tag, commit, w, E, eps, red, xq_s, xs_s
 static __device__ __noinline__ bool stage_norm_q8_wide(MI_NORM_ARGS) {
     if ((E / 32 + DNW - 1) / DNW <= 16) return stage_norm_q8_t<16>(MI_NORM_PASS);
     return stage_norm_q8_t<32>(MI_NORM_PASS);
 }
-__device__ __forceinline__ bool stage_norm_q8(MI_NORM_ARGS) {
+__device__ __forceinline__ bool stage_norm_q8u(MI_NORM_ARGS) {
     const int per_warp = (E / 32 + DNW - 1) / DNW;
     if (per_warp <= 4) return stage_norm_q8_t<4>(MI_NORM_PASS);
     if (per_warp <= 6) return stage_norm_q8_t<6>(MI_NORM_PASS);
@@ -613,11 +646,12 @@ __device__ __forceinline__ bool stage_norm_q8(MI_NORM_ARGS) {
     return stage_norm_q8_wide(MI_NORM_PASS);
 }
 
+
 // A q8_0 vector published as tagged words by other CTAs -> shared memory: int8 values, and per block {fp32 of the fp16
 // scale, float(8 * sum of the block's values)}.  Thread t takes the 16-byte word pairs t, t + 256, ...; all of a
 // thread's loads are in flight together.
 template <int NP>
-__device__ __forceinline__ bool stage_poll_q8_t(const DecodeParams& P, const unsigned long long* vw, int n, unsigned tag, int8_t* xq_s, float2* xs_s) {
+__device__ MI_PIECE bool stage_poll_q8_t(const DecodeParams& P, const unsigned long long* vw, int n, unsigned tag, int8_t* xq_s, float2* xs_s) {
     const int tid = threadIdx.x, nq2 = n / 8, tot2 = nq2 + (n / 32 + 1) / 2, nbk = n / 32;     // pairs of value words, all pairs, blocks
     unsigned long long w[NP][2];
     #pragma unroll
@@ -635,8 +669,9 @@ __device__ __forceinline__ bool stage_poll_q8_t(const DecodeParams& P, const uns
             if (!tw_is(w[k][1], tag)) miss = vw + 2 * (tid + k * DNT) + 1;
             if (!tw_is(w[k][0], tag)) miss = vw + 2 * (tid + k * DNT);
         }
-        if (!miss) break;
-        if (!tw_spin(miss, tag, P.wait_ns, P.err)) { ok = false; break; }
+        const int st = tw_wait_warp(miss, tag, P.wait_ns, P.err);
+        if (st == 0) break;
+        if (st < 0) { ok = false; break; }
         #pragma unroll
         for (int k = 0; k < NP; k++) {
             if (!tw_is(w[k][0], tag) || !tw_is(w[k][1], tag)) {
@@ -697,8 +732,8 @@ __device__ __forceinline__ bool stage_poll_q8(const DecodeParams& P, const unsig
 // TG: inputs (q, and k / v of the new position) and the q8_0 output travel as tagged words (the decode loop); otherwise they
 // are plain arrays (the attention kernel of the M-token step).  Returns false if a wait gave up (CTA-uniform).
 template <int HD, int G, int GQ, bool STORE_KV = true, bool QNAT = false, bool TG = false>
-__device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage, unsigned long long& tp,
-                                                unsigned tag_in = 0, const Pub* pub = nullptr) {
+__device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, int pos, uint8_t* stage,
+                                                unsigned tag_in = 0, const Pub pub = Pub()) {
     constexpr int DPW = HD / 32;           // dims per lane in pass 2 and while folding (dim = lane + 32*i)
     constexpr int SW = HD + 2;             // doubles per (head) state: o[HD], m, l
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -756,7 +791,7 @@ __device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, in
         }
         __syncthreads();
     }
-    prof_mark(P, tp, 14);
+    prof_mark(P, 14);
     const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
     const int n = p1 - p0, a0 = p0 + (int)((long long)n * warp / DNW), a1 = p0 + (int)((long long)n * (warp + 1) / DNW);
     const __half* kbase = P.kc + ((size_t)l * P.max_seq) * P.KVD + (size_t)kvh * HD;
@@ -888,7 +923,7 @@ __device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, in
         }
         __syncwarp();
     }
-    prof_mark(P, tp, 15);
+    prof_mark(P, 15);
     #pragma unroll
     for (int j = 0; j < G; j++) {
         double* sw = scr + (size_t)(warp * G + j) * SW;
@@ -929,7 +964,7 @@ __device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, in
                 if constexpr (TG) {
                     __half dq; int sq;
                     const int qv8 = quant_block_warp2(v, dq, sq);
-                    publish_q8_block<false>(*pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+                    publish_q8_block<false>(pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
                 } else {
                     P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
                 }
@@ -941,7 +976,7 @@ __device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, in
             if (lane == 0) { __stcg(gp + HD, (double)mm); __stcg(gp + HD + 1, ll); }
         }
     }
-    prof_mark(P, tp, 16);
+    prof_mark(P, 16);
     if (nch == 1) return true;
     __threadfence();
     __syncthreads();
@@ -1000,13 +1035,492 @@ __device__ __forceinline__ bool attention_phase(const DecodeParams& P, int l, in
             if constexpr (TG) {
                 __half dq; int sq;
                 const int qv8 = quant_block_warp2(v, dq, sq);
-                publish_q8_block<false>(*pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+                publish_q8_block<false>(pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
             } else {
                 P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
             }
         }
     }
     return true;
+}
+
+// ---- attention over a short causal range (at most 256 positions): one CTA per query head ---------------
+// The whole range of a head fits one CTA, so the softmax is computed the way the reference's CPU program writes it
+// (src/cpu_infer.cpp:121-140): all scores, their maximum, exp(score - max) once per position, then the weighted sum of the
+// V rows and the division - no running maximum, no rescaling, no merge of partial states.
+//   pass 1  warp w takes a contiguous eighth of the positions; eight lanes share a position (HD/8 dims each), the dot
+//           product is carried in double and folded over the eight lanes; score = fp32(dot) * 1/sqrt(HD) in fp32;
+//   max     every warp scans the scores in shared memory; thread t computes the weight of position t (one double exp);
+//   pass 2  warp w, same positions: lane = dims {lane + 32 i}; o += w[p] * V[p], l += w[p] in position order;
+//   finish  warp i (i < HD/32) adds the eight warps' partial sums in warp order, divides, rounds to fp32, quantizes its
+//           32-dim block to q8_0 and publishes it.
+// Same interface and template flags as attention_phase.
+template <int HD, int GQ, bool STORE_KV = true, bool QNAT = false, bool TG = false>
+MI_ATT_FN bool attention_short(const DecodeParams& P, int l, int pos, uint8_t* stage,
+                                                unsigned tag_in = 0, const Pub pub = Pub()) {
+    constexpr int DPW = HD / 32;
+    constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2;                 // lanes per position in pass 1, dims per lane, padded stride
+    constexpr int KV4 = DPL * 2 / 16 > 0 ? DPL * 2 / 16 : 1;              // 16-byte loads per lane and position
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((int)blockIdx.x >= P.NH) return true;
+    const int head = blockIdx.x, kvh = head / GQ, Lp = pos + 1;
+    double* qs = reinterpret_cast<double*>(stage);                         // [LPP][QSTR]
+    double* wt = qs + LPP * QSTR;                                          // [256] weights
+    double* ow = wt + 256;                                                 // [DNW][HD] partial outputs
+    double* lw = ow + DNW * HD;                                            // [DNW] partial denominators
+    float* sc = reinterpret_cast<float*>(lw + DNW);                        // [256] scores
+    if constexpr (TG) {
+        const int nq = P.NH * HD;
+        unsigned qw[3], valid = 0;
+        if (tid < HD) valid = STORE_KV ? 7u : 1u;
+        const unsigned long long* qv = P.xw + P.xo.qkv;
+        const int dk = tid < HD / 2 ? 2 * tid : 2 * (tid - HD / 2) + 1;    // packed slot of dim `tid`
+        const bool okq = tw_poll(P, tag_in, valid, [&](int k) -> const unsigned long long* {
+            return k == 0 ? qv + (size_t)head * HD + dk : k == 1 ? qv + nq + (size_t)kvh * HD + dk : qv + nq + P.KVD + (size_t)kvh * HD + tid;
+        }, qw);
+        if (tid < HD) {
+            qs[(tid / DPL) * QSTR + tid % DPL] = (double)__uint_as_float(qw[0]);
+            if (STORE_KV) {                                               // CTAs that share a kv head store the same bits
+                P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__uint_as_float(qw[1]));
+                P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__uint_as_float(qw[2]));
+            }
+        }
+        if (!__syncthreads_and(okq ? 1 : 0)) return false;
+    } else {
+        if (tid < HD) {
+            const int pk = QNAT ? tid : (tid < HD / 2 ? 2 * tid : 2 * (tid - HD / 2) + 1);
+            qs[(tid / DPL) * QSTR + tid % DPL] = (double)__ldcg(P.qkv_out + (size_t)head * HD + pk);
+            if (STORE_KV) {
+                const int nq = P.NH * HD, pkk = tid < HD / 2 ? 2 * tid : 2 * (tid - HD / 2) + 1;
+                P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__ldcg(P.qkv_out + nq + (size_t)kvh * HD + pkk));
+                P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = __float2half_rn(__ldcg(P.qkv_out + nq + P.KVD + (size_t)kvh * HD + tid));
+            }
+        }
+        __syncthreads();
+    }
+    prof_mark(P, 14);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
+    const int a0 = (int)((long long)Lp * warp / DNW), a1 = (int)((long long)Lp * (warp + 1) / DNW);      // at most 32 positions
+    const __half* kbase = P.kc + ((size_t)l * P.max_seq) * P.KVD + (size_t)kvh * HD;
+    const __half* vbase = P.vc + ((size_t)l * P.max_seq) * P.KVD + (size_t)kvh * HD;
+    const int np = a1 - a0;
+    // pass 1: four positions per sweep, rounds of four sweeps whose K rows are all requested before the first is used
+    {
+        const int sub = lane >> 3, li = lane & 7;
+        const double* qj = qs + li * QSTR;
+        #pragma unroll 1
+        for (int s0 = 0; s0 * 4 < np; s0 += 4) {
+            uint4 kraw[4][KV4];
+            #pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if ((s0 + u) * 4 >= np) continue;                          // warp-uniform
+                const int pi = min((s0 + u) * 4 + sub, np - 1);
+                const __half* kr = kbase + (size_t)(a0 + pi) * P.KVD + li * DPL;
+                if constexpr (DPL >= 8) {
+                    #pragma unroll
+                    for (int c = 0; c < KV4; c++) kraw[u][c] = __ldcg(reinterpret_cast<const uint4*>(kr) + c);
+                } else {
+                    const uint2 k2 = __ldcg(reinterpret_cast<const uint2*>(kr));
+                    kraw[u][0] = make_uint4(k2.x, k2.y, 0u, 0u);
+                }
+            }
+            #pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if ((s0 + u) * 4 < np) {                                   // warp-uniform
+                    const int pi = (s0 + u) * 4 + sub;
+                    double acc = 0.0;
+                    #pragma unroll
+                    for (int c = 0; c < KV4; c++) {
+                        const __half2* hh = reinterpret_cast<const __half2*>(&kraw[u][c]);
+                        #pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            if (c * 8 + 2 * e < DPL) {
+                                const float2 f = __half22float2(hh[e]);
+                                const double2 qq = *reinterpret_cast<const double2*>(qj + c * 8 + 2 * e);
+                                acc = __fma_rn(qq.x, (double)f.x, acc);
+                                acc = __fma_rn(qq.y, (double)f.y, acc);
+                            }
+                        }
+                    }
+                    #pragma unroll
+                    for (int sft = 1; sft <= 4; sft <<= 1) acc = __dadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, sft));
+                    if (li == 0 && pi < np) sc[a0 + pi] = __fmul_rn(__double2float_rn(acc), inv);
+                }
+            }
+        }
+    }
+    prof_mark(P, 27);
+    // the V rows of this warp's positions: requested now, used after the weights are known
+    // (lane = the dim pairs {2 lane, 2 lane + 1} + 64 j: one 4-byte load per pair; head_dim 32: lane = dim)
+    // (the first sixteen; a warp has more only beyond 128 positions, and fetches those when it gets there)
+    constexpr int VB = 16, VP = DPW >= 2 ? DPW / 2 : 1;
+    unsigned vh[VB][VP];
+    auto load_v = [&](int r) {
+        #pragma unroll
+        for (int u = 0; u < VB; u++) {
+            const __half* vrow = vbase + (size_t)(a0 + min(r * VB + u, max(np - 1, 0))) * P.KVD;
+            if constexpr (DPW >= 2) {
+                #pragma unroll
+                for (int j = 0; j < VP; j++) vh[u][j] = __ldcg(reinterpret_cast<const unsigned*>(vrow) + lane + 32 * j);
+            } else {
+                vh[u][0] = __ldcg(reinterpret_cast<const unsigned short*>(vrow) + lane);
+            }
+        }
+    };
+    if (np > 0) load_v(0);
+    prof_mark(P, 28);
+    __syncthreads();
+    prof_mark(P, 15);
+    // maximum over the whole range (every warp scans all scores), then one weight per thread
+    float mx = -INFINITY;
+    #pragma unroll
+    for (int i = 0; i < 8; i++) if (lane + 32 * i < Lp) mx = fmaxf(mx, sc[lane + 32 * i]);
+    mx = warp_max_float(mx);
+    if (tid < Lp) wt[tid] = exp_shared((double)sc[tid] - (double)mx);
+    prof_mark(P, 29);
+    __syncthreads();
+    prof_mark(P, 30);
+    // pass 2
+    double o[DPW], ls = 0.0;
+    #pragma unroll
+    for (int i = 0; i < DPW; i++) o[i] = 0.0;
+    #pragma unroll 1
+    for (int r = 0; r * VB < np; r++) {
+        if (r > 0) load_v(r);
+        #pragma unroll
+        for (int u = 0; u < VB; u++) {
+            if (r * VB + u < np) {
+                const double w = wt[a0 + r * VB + u];
+                ls = __dadd_rn(ls, w);
+                if constexpr (DPW >= 2) {
+                    #pragma unroll
+                    for (int j = 0; j < VP; j++) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&vh[u][j]));
+                        o[2 * j] = __fma_rn(w, (double)f.x, o[2 * j]);
+                        o[2 * j + 1] = __fma_rn(w, (double)f.y, o[2 * j + 1]);
+                    }
+                } else {
+                    o[0] = __fma_rn(w, (double)__half2float(__ushort_as_half((unsigned short)vh[u][0])), o[0]);
+                }
+            }
+        }
+    }
+    if constexpr (DPW >= 2) {
+        #pragma unroll
+        for (int j = 0; j < VP; j++) *reinterpret_cast<double2*>(ow + warp * HD + 2 * (lane + 32 * j)) = make_double2(o[2 * j], o[2 * j + 1]);
+    } else {
+        ow[warp * HD + lane] = o[0];
+    }
+    if (lane == 0) lw[warp] = ls;
+    prof_mark(P, 31);
+    // the new position's K / V rows (plain stores above) are performed before anything this CTA publishes
+    if (TG && STORE_KV && tid < HD) __threadfence();
+    __syncthreads();
+    prof_mark(P, 16);
+    if (warp < DPW) {
+        const int d = warp * 32 + lane;
+        double ob = ow[d], ll = lw[0];
+        #pragma unroll
+        for (int w = 1; w < DNW; w++) { ob = __dadd_rn(ob, ow[w * HD + d]); ll = __dadd_rn(ll, lw[w]); }
+        const float v = __double2float_rn(__ddiv_rn(ob, ll));
+        const int e = head * HD + d;
+        __stcg(P.att + e, v);
+        if constexpr (TG) {
+            __half dq; int sq;
+            const int qv8 = quant_block_warp2(v, dq, sq);
+            publish_q8_block<false>(pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+        } else {
+            P.att_q[e] = (int8_t)quant_block_warp(v, lane, nullptr, P.att_d + (e >> 5));
+        }
+    }
+    prof_mark(P, 17);
+    return true;
+}
+
+// ---- short-range attention on the CTAs set aside for it ------------------------------------------------
+// A CTA of [0, attn_ctas) handles HPC query heads of one kv head and nothing else, which buys two things.  (1) The K and V
+// rows of the cached positions are known long before the layer's q arrives, so the CTA copies them into shared memory
+// ahead of time (one bulk copy per row, rows padded by 16 bytes against bank conflicts; the copy for the next layer is
+// issued as soon as this layer's arithmetic has left the buffer): between q's arrival and the published output there is
+// no global load at all.  (2) One fp16 -> double conversion of a K or V element serves all HPC heads.
+// The new position's K and V come with q as tagged words; they go into the shared-memory rows directly and to the global
+// cache after the output has been published (fenced before this CTA's next output, which is what later readers wait for).
+// Per head the arithmetic is attention_short's, operation for operation: same bits.
+constexpr int kAttnRows = kShortAttnMax;
+template <int HD> __host__ __device__ constexpr int attn_row_bytes() { return 2 * HD + 16; }
+__host__ __device__ inline size_t attn_dedicated_smem(int HD, int HPC) {
+    return (size_t)2 * kAttnRows * (2 * HD + 16) + (size_t)HPC * (HD + 16) * 8 + (size_t)HPC * kAttnRows * 8 + (size_t)DNW * HPC * HD * 8 +
+           (size_t)DNW * HPC * 8 + (size_t)HPC * kAttnRows * 4 + 64;
+}
+template <int G> __host__ __device__ constexpr int attn_heads_per_cta() { return (G % 2 == 0 && G > 2) ? G / 2 : (G <= 2 ? 1 : G); }
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+struct AttnPrefetch { uint64_t* bar; unsigned parity; int layer, pos; bool pending; bool ok; };
+
+// Request the K and V rows of positions [0, pos) of `layer` for this CTA's kv head (whole CTA; ends with the copies in flight).
+template <int HD>
+__device__ __forceinline__ void attn_prefetch_issue(const DecodeParams& P, uint8_t* smem, AttnPrefetch& pf, int layer, int pos, int kvh) {
+    constexpr int RSB = attn_row_bytes<HD>();
+    const int tid = threadIdx.x;
+    pf.layer = layer; pf.pos = pos; pf.pending = pos > 0;
+    if (pos <= 0) return;
+    if (tid == 0) { fence_proxy_async(); mbar_expect_tx(pf.bar, 2u * (unsigned)pos * (2u * HD)); }
+    __syncthreads();
+    uint8_t* Kb = smem; uint8_t* Vb = smem + (size_t)kAttnRows * RSB;
+    for (int p = tid; p < pos; p += DNT) {
+        const size_t row = ((size_t)layer * P.max_seq + p) * P.KVD + (size_t)kvh * HD;
+        bulk_g2s(Kb + (size_t)p * RSB, P.kc + row, 2 * HD, pf.bar);
+        bulk_g2s(Vb + (size_t)p * RSB, P.vc + row, 2 * HD, pf.bar);
+    }
+}
+
+template <int HD, int GQ, int HPC>
+__device__ __forceinline__ AttnPrefetch attention_dedicated(const DecodeParams& P, int l, int pos, uint8_t* smem, AttnPrefetch pf,
+                                                                unsigned tag_in, const Pub pub, int next_layer, int next_pos) {
+    constexpr int DPW = HD / 32, RSB = attn_row_bytes<HD>();
+    constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2, KV4 = DPL * 2 / 16 > 0 ? DPL * 2 / 16 : 1;
+    constexpr int QN = (HPC * HD + DNT - 1) / DNT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h0 = (int)blockIdx.x * HPC, kvh = h0 / GQ, Lp = pos + 1, nq = P.NH * HD;
+    uint8_t* Kb = smem; uint8_t* Vb = smem + (size_t)kAttnRows * RSB;
+    double* qs = reinterpret_cast<double*>(smem + (size_t)2 * kAttnRows * RSB);   // [HPC][LPP][QSTR]
+    double* wt = qs + HPC * LPP * QSTR;                                         // [HPC][rows]
+    double* ow = wt + HPC * kAttnRows;                                          // [DNW][HPC][HD]
+    double* lw = ow + DNW * HPC * HD;                                           // [DNW][HPC]
+    float* sc = reinterpret_cast<float*>(lw + DNW * HPC);                       // [HPC][rows]
+    // the rows of this (layer, position) should be on their way already; a launch's first layer requests them here
+    if (!(pf.layer == l && pf.pos == pos)) {
+        if (pf.pending) { (void)mbar_wait_bounded(pf.bar, pf.parity); pf.parity ^= 1u; }
+        attn_prefetch_issue<HD>(P, smem, pf, l, pos, kvh);
+    }
+    // q of this CTA's heads and k / v of the new position (tagged words, packed order: dim d sits at 2d (d < HD/2) or 2(d-HD/2)+1)
+    unsigned qw[QN + 2], valid = 0;
+    #pragma unroll
+    for (int k = 0; k < QN; k++) if (tid + k * DNT < HPC * HD) valid |= 1u << k;
+    if (tid < HD) valid |= 3u << QN;
+    const unsigned long long* qv = P.xw + P.xo.qkv;
+    const int dk = tid < HD / 2 ? 2 * tid : 2 * (tid - HD / 2) + 1;
+    bool ok = tw_poll(P, tag_in, valid, [&](int k) -> const unsigned long long* {
+        if (k < QN) {
+            const int i = tid + k * DNT, j = i / HD, d = i % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
+            return qv + (size_t)(h0 + j) * HD + pk;
+        }
+        return k == QN ? qv + nq + (size_t)kvh * HD + dk : qv + nq + P.KVD + (size_t)kvh * HD + tid;
+    }, qw);
+    #pragma unroll
+    for (int k = 0; k < QN; k++) {
+        const int i = tid + k * DNT;
+        if (i < HPC * HD) { const int j = i / HD, d = i % HD; qs[(j * LPP + d / DPL) * QSTR + d % DPL] = (double)__uint_as_float(qw[k]); }
+    }
+    const __half knew = __float2half_rn(__uint_as_float(qw[QN])), vnew = __float2half_rn(__uint_as_float(qw[QN + 1]));
+    if (tid < HD) {
+        reinterpret_cast<__half*>(Kb + (size_t)pos * RSB)[tid] = knew;
+        reinterpret_cast<__half*>(Vb + (size_t)pos * RSB)[tid] = vnew;
+    }
+    prof_mark(P, 14);
+    if (ok && pf.pending) { ok = mbar_wait_bounded(pf.bar, pf.parity); pf.parity ^= 1u; pf.pending = false; }
+    if (!__syncthreads_and(ok ? 1 : 0)) { pf.ok = false; return pf; }
+    prof_mark(P, 27);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
+    const int a0 = (int)((long long)Lp * warp / DNW), a1 = (int)((long long)Lp * (warp + 1) / DNW), np = a1 - a0;
+    // pass 1: four positions per sweep, eight lanes per position; one conversion of the K row serves all heads.  The lane's
+    // slice of every head's q sits in registers for all sweeps: read from shared memory per sweep, the 16-byte broadcast
+    // loads (512 bytes written back per warp instruction) were the larger half of this pass.
+    {
+        const int sub = lane >> 3, li = lane & 7;
+        double qr[HPC][DPL];
+        #pragma unroll
+        for (int j = 0; j < HPC; j++) {
+            const double* qj = qs + (j * LPP + li) * QSTR;
+            #pragma unroll
+            for (int e = 0; e < DPL; e += 2) { const double2 qq = *reinterpret_cast<const double2*>(qj + e); qr[j][e] = qq.x; qr[j][e + 1] = qq.y; }
+        }
+        #pragma unroll 1
+        for (int s0 = 0; s0 * 4 < np; s0++) {
+            const int pi = s0 * 4 + sub;
+            const uint4* kr = reinterpret_cast<const uint4*>(Kb + (size_t)(a0 + min(pi, np - 1)) * RSB + li * DPL * 2);
+            double kd[DPL];
+            if constexpr (DPL >= 8) {
+                #pragma unroll
+                for (int c = 0; c < KV4; c++) {
+                    const uint4 kk = kr[c];
+                    const __half2* hh = reinterpret_cast<const __half2*>(&kk);
+                    #pragma unroll
+                    for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hh[e]); kd[c * 8 + 2 * e] = (double)f.x; kd[c * 8 + 2 * e + 1] = (double)f.y; }
+                }
+            } else {
+                const uint2 kk = *reinterpret_cast<const uint2*>(kr);
+                const __half2* hh = reinterpret_cast<const __half2*>(&kk);
+                #pragma unroll
+                for (int e = 0; e < DPL / 2; e++) { const float2 f = __half22float2(hh[e]); kd[2 * e] = (double)f.x; kd[2 * e + 1] = (double)f.y; }
+            }
+            double acc[HPC];
+            #pragma unroll
+            for (int j = 0; j < HPC; j++) {
+                double a = 0.0;
+                #pragma unroll
+                for (int e = 0; e < DPL; e++) a = __fma_rn(qr[j][e], kd[e], a);
+                acc[j] = a;
+            }
+            #pragma unroll
+            for (int sft = 1; sft <= 4; sft <<= 1)
+                #pragma unroll
+                for (int j = 0; j < HPC; j++) acc[j] = __dadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], sft));
+            if (li == 0 && pi < np) {
+                #pragma unroll
+                for (int j = 0; j < HPC; j++) sc[j * kAttnRows + a0 + pi] = __fmul_rn(__double2float_rn(acc[j]), inv);
+            }
+        }
+    }
+    __syncthreads();
+    prof_mark(P, 15);
+    // per head: maximum over the whole range, then one weight per (head, position)
+    float mx[HPC];
+    #pragma unroll
+    for (int j = 0; j < HPC; j++) {
+        float m = -INFINITY;
+        #pragma unroll
+        for (int i = 0; i < kAttnRows / 32; i++) if (lane + 32 * i < Lp) m = fmaxf(m, sc[j * kAttnRows + lane + 32 * i]);
+        mx[j] = warp_max_float(m);
+    }
+    for (int idx = tid; idx < HPC * Lp; idx += DNT) {
+        const int j = idx / Lp, p = idx - j * Lp;
+        float mj = mx[0];
+        #pragma unroll
+        for (int jj = 1; jj < HPC; jj++) if (j == jj) mj = mx[jj];
+        wt[j * kAttnRows + p] = exp_shared((double)sc[j * kAttnRows + p] - (double)mj);
+    }
+    prof_mark(P, 29);
+    __syncthreads();
+    prof_mark(P, 30);
+    // pass 2: lane = the dim pairs {2 lane, 2 lane + 1} + 64 jj (head_dim 32: lane = dim)
+    constexpr int VP = DPW >= 2 ? DPW / 2 : 1;
+    double o[HPC][DPW], ls[HPC];
+    #pragma unroll
+    for (int j = 0; j < HPC; j++) {
+        ls[j] = 0.0;
+        #pragma unroll
+        for (int i = 0; i < DPW; i++) o[j][i] = 0.0;
+    }
+    #pragma unroll 2
+    for (int u = 0; u < np; u++) {
+        const uint8_t* vrow = Vb + (size_t)(a0 + u) * RSB;
+        double vd[DPW];
+        if constexpr (DPW >= 2) {
+            #pragma unroll
+            for (int jj = 0; jj < VP; jj++) {
+                const float2 f = __half22float2(reinterpret_cast<const __half2*>(vrow)[lane + 32 * jj]);
+                vd[2 * jj] = (double)f.x; vd[2 * jj + 1] = (double)f.y;
+            }
+        } else {
+            vd[0] = (double)__half2float(reinterpret_cast<const __half*>(vrow)[lane]);
+        }
+        #pragma unroll
+        for (int j = 0; j < HPC; j++) {
+            const double w = wt[j * kAttnRows + a0 + u];
+            ls[j] = __dadd_rn(ls[j], w);
+            #pragma unroll
+            for (int i = 0; i < DPW; i++) o[j][i] = __fma_rn(w, vd[i], o[j][i]);
+        }
+    }
+    #pragma unroll
+    for (int j = 0; j < HPC; j++) {
+        double* od = ow + (size_t)(warp * HPC + j) * HD;
+        if constexpr (DPW >= 2) {
+            #pragma unroll
+            for (int jj = 0; jj < VP; jj++) *reinterpret_cast<double2*>(od + 2 * (lane + 32 * jj)) = make_double2(o[j][2 * jj], o[j][2 * jj + 1]);
+        } else {
+            od[lane] = o[j][0];
+        }
+        if (lane == 0) lw[warp * HPC + j] = ls[j];
+    }
+    prof_mark(P, 31);
+    __syncthreads();
+    prof_mark(P, 16);
+    // finish: one 32-dim block of one head per warp and round
+    for (int b = warp; b < HPC * DPW; b += DNW) {
+        const int j = b / DPW, d = (b % DPW) * 32 + lane;
+        double ob = ow[(size_t)j * HD + d], ll = lw[j];
+        #pragma unroll
+        for (int w = 1; w < DNW; w++) { ob = __dadd_rn(ob, ow[(size_t)(w * HPC + j) * HD + d]); ll = __dadd_rn(ll, lw[w * HPC + j]); }
+        const float v = __double2float_rn(__ddiv_rn(ob, ll));
+        const int e = (h0 + j) * HD + d;
+        __stcg(P.att + e, v);
+        __half dq; int sq;
+        const int qv8 = quant_block_warp2(v, dq, sq);
+        publish_q8_block<false>(pub, P.xo.att, P.xo.att + P.NH * HD / 4, e >> 5, lane, qv8, dq, sq);
+    }
+    prof_mark(P, 17);
+    // the new position into the global cache (CTAs that share a kv head store the same bits); performed, for the generic and
+    // the bulk-copy path alike, before this CTA publishes anything else
+    if (tid < HD) {
+        P.kc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = knew;
+        P.vc[((size_t)l * P.max_seq + pos) * P.KVD + (size_t)kvh * HD + tid] = vnew;
+        __threadfence();
+        fence_proxy_async();
+    }
+    __syncthreads();                                  // the buffer is free, the stores are fenced
+    if (next_layer >= 0 && next_pos + 1 <= kShortAttnMax) attn_prefetch_issue<HD>(P, smem, pf, next_layer, next_pos, kvh);
+    else { pf.layer = -1; pf.pending = false; }
+    pf.ok = true;
+    return pf;
+}
+
+// The whole life of a CTA that does nothing but attention: every step, every layer, wait for q, attend, publish.  One call
+// at the top of the kernel, out of line: its registers and instructions are its own, and the CTAs that carry the GEMV phases
+// never see any of it (measured: an out-of-line call inside their per-layer loop, or this code inlined into it, costs the
+// GEMV phases 10 - 25 %).
+template <int HD, int G>
+static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int step0, int step1, int ph0, int ph1, uint8_t* smem, uint8_t* stage, uint64_t* bar) {
+    const int nph = 5 * P.L + 1;
+    pdl_launch_dependents();
+    pdl_wait_prior();
+    AttnPrefetch apf; apf.bar = bar; apf.parity = 0; apf.layer = -1; apf.pos = -1; apf.pending = false; apf.ok = true;
+    const unsigned epoch = __ldcg(P.epoch_dev);
+    const int pos_base = P.pos_dev ? __ldcg(P.pos_dev) : P.pos0;
+    bool ok = true;
+    int err_code = MI_ERR_TIMEOUT;
+#if MI_PROF
+    const long long prof_c0 = clock64(); const unsigned long long prof_t0 = gtime_ns();
+    if (threadIdx.x == 0) s_prof_t = prof_t0;
+#endif
+    for (int step = step0; step < step1 && ok; step++) {
+        const int pos = pos_base + step;
+        if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }
+        const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;
+        for (int l = max(0, (ph0 + 3) / 5); 5 * l + 1 < ph1 && l < P.L && ok; l++) {
+            const int ph = 5 * l + 1;
+            Pub pub;
+            pub.xw = P.xw; pub.tag = tag0 + (unsigned)ph; pub.mute = ph == P.drop_phase;
+#if MI_TP
+            pub.tp = &P.tp;
+#endif
+            if (pos + 1 <= kShortAttnMax) {
+                // where this CTA's next attention will be: the next layer of this step, or layer 0 of the next step
+                int nl = -1, np_ = pos;
+                if (ph + 5 < ph1 && l + 1 < P.L) nl = l + 1;
+                else if (step + 1 < step1 && ph0 <= 1) { nl = 0; np_ = pos + 1; }
+                apf = attention_dedicated<HD, G, attn_heads_per_cta<G>()>(P, l, pos, smem, apf, pub.tag - 1u, pub, nl, np_);
+                ok = apf.ok;
+            } else {
+                if (apf.pending) { (void)mbar_wait_bounded(apf.bar, apf.parity); apf.parity ^= 1u; apf.pending = false; apf.layer = -1; }
+                if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
+                else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
+            }
+            ok = __syncthreads_and(ok ? 1 : 0) != 0;
+            prof_mark(P, 3);
+        }
+    }
+#if MI_PROF
+    if (P.prof && (int)blockIdx.x == P.prof_cta) {
+        if (threadIdx.x == 0) { s_prof[8] = (unsigned long long)(clock64() - prof_c0); s_prof[9] = gtime_ns() - prof_t0; }
+        __syncthreads();
+        if (threadIdx.x < kProfSlots) P.prof[threadIdx.x] += s_prof[threadIdx.x];
+    }
+#endif
+    if (apf.pending) (void)mbar_wait_bounded(apf.bar, apf.parity);      // copies in flight target this CTA's shared memory
+    if (!ok && (threadIdx.x & 31) == 0) atomicMax(P.err, err_code);
 }
 
 // ---- the kernel ---------------------------------------------------------------------
@@ -1029,6 +1543,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     sm.h = reinterpret_cast<float*>(after_jobs + 1024 + 256 + kFoldBytes);
     sm.stage = after_jobs + 1024 + 256 + kFoldBytes + ((size_t)P.E * 4 + 127) / 128 * 128;
     __shared__ int s_tok;
+    __shared__ uint64_t s_attn_bar;
 #if MI_PROF
     if (tid < kProfSlots) s_prof[tid] = 0;
 #endif
@@ -1037,12 +1552,21 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         reinterpret_cast<int*>(sm.jobs)[i] = __ldg(reinterpret_cast<const int*>(P.jobs) + i);
     for (int i = tid; i < P.L * (int)(sizeof(LayerPtrs) / 4); i += DNT)
         reinterpret_cast<int*>(sm.lp)[i] = __ldg(reinterpret_cast<const int*>(P.layers) + i);
+    const bool attn_only = (int)blockIdx.x < P.attn_ctas;        // this CTA does nothing but attention; it lays the shared memory out its own way
     if (lane == 0) {
-        #pragma unroll
-        for (int s = 0; s < DS; s++) mbar_init(&sm.bars[warp * DS + s], 1);
+        if (!attn_only) {
+            #pragma unroll
+            for (int s = 0; s < DS; s++) mbar_init(&sm.bars[warp * DS + s], 1);
+        }
+        if (warp == 0) mbar_init(&s_attn_bar, 1);
         mbar_fence_init();
     }
     __syncthreads();
+
+    if (attn_only) {                                  // CTAs [0, attn_ctas): attention and nothing else
+        attn_cta_main<HD, G>(P, step0, step1, ph0, ph1, smem, sm.stage, &s_attn_bar);
+        return;
+    }
 
     // jobs covered by the phase range of this launch
     auto job_of_phase = [&](int ph) -> int {          // first job at or after phase ph
@@ -1067,8 +1591,8 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     const unsigned epoch = __ldcg(P.epoch_dev);
     const int pos_base = P.pos_dev ? __ldcg(P.pos_dev) : P.pos0;
     // candidates of the greedy pick: one {value, index} pair of words per CTA (and per GPU when the exchange runs in here)
-    const int cand_world = P.tp.on ? P.tp.world : 1, n_cand = cand_world * (int)gridDim.x;
-    const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * (int)gridDim.x + (int)blockIdx.x) * 2;
+    const int cand_world = P.tp.on ? P.tp.world : 1, n_cand = cand_world * ws.ggrid;
+    const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * ws.ggrid + ws.gcta) * 2;
 
     auto rope_table = [&](int pos) {                   // cos / sin of this position's angles, fp32 angle as src/cpu_infer.cpp:54
         if (tid < HD / 2) {
@@ -1077,7 +1601,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         }
     };
 
-    unsigned long long tp = (MI_PROF && P.prof) ? gtime_ns() : 0;
+#if MI_PROF
+    const long long prof_c0 = clock64(); const unsigned long long prof_t0 = gtime_ns();
+    if (tid == 0) s_prof_t = prof_t0;
+#endif
     if (step0 < step1) rope_table(pos_base + step0);
     __syncthreads();
     for (int step = step0; step < step1 && ok; step++) {
@@ -1085,7 +1612,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;        // tag of (step, phase 0)
         if (step > step0 && ph1 != nph) { rope_table(pos); __syncthreads(); }     // (otherwise the previous step's lm_head phase has made the table)
-        prof_mark(P, tp, kProfStep);
+        prof_mark(P, kProfStep);
         for (int ph = ph0; ph < ph1 && ok; ph++) {
             const int l = ph / 5, k = ph == nph - 1 ? 5 : ph % 5;
             Pub pub;
@@ -1114,27 +1641,30 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 } else {
                     gsrc = h_valid ? nullptr : P.h_mid; addw = P.xw + P.xo.down; nw = P.out_norm;
                 }
-                ok = stage_norm_q8(P, sm.h, gsrc, embed, tok, addw, pub.tag - 1u, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s, tp);
+                ok = stage_norm_q8u(P, sm.h, gsrc, embed, tok, addw, pub.tag - 1u, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s);
                 h_valid = true;
-                prof_mark(P, tp, 2 * k);
+                prof_mark(P, 2 * k);
             } else if (k == 2 || k == 4) {
                 const Job& jb = sm.jobs[4 * l + (k == 2 ? 1 : 3)];
                 if (ws.first_cta_unit(jb) < jb.n_units) {        // only CTAs that have a unit of the job consume its input
-                    prof_mark(P, tp, 2 * k);
+                    prof_mark(P, 2 * k);
                     if (k == 2) ok = stage_poll_q8(P, P.xw + P.xo.att, P.NH * HD, pub.tag - 1u, xq_s, xs_s);
                     else ok = stage_poll_q8(P, P.xw + P.xo.act, P.FF, pub.tag - 1u, xq_s, xs_s);
-                    prof_mark(P, tp, kProfWait);
+                    prof_mark(P, kProfWait);
                 }
             }
             if (!ok) break;
             if (k == 1) {
-                if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, tp, pub.tag - 1u, &pub);
-                else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, tp, pub.tag - 1u, &pub);
+                if (pos + 1 <= kShortAttnMax && P.attn_ctas > 0) {
+                    // the attention CTAs' business
+                } else if (pos + 1 <= kShortAttnMax) ok = attention_short<HD, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+                else if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+                else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
             } else if (k != 5) {
                 const int jn = 4 * l + (k == 0 ? 0 : k == 2 ? 1 : k == 3 ? 2 : 3);
                 const float* bias = sm.lp[l].bqkv;
                 const int nq = P.NH * HD;
-                ok = run_cta_job(ws, P, sm, jn, lane, xq_s, xs_s, pub, tp, [&](int g, int ln, float v0, float v1) {
+                ok = run_cta_job(ws, P, sm, jn, lane, xq_s, xs_s, pub, [&](int g, int ln, float v0, float v1) {
                     if (k == 0) {                                            // + bias, RoPE, packed q / k / v
                         const int p = g * 32 + ln;
                         const float v = __fadd_rn(v0, __ldg(bias + p));
@@ -1190,7 +1720,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 // the next step's angles while the other CTAs' candidates arrive
                 if (step + 1 < step1) rope_table(pos + 1);
                 // every CTA makes the pick over all candidates itself (the same bits everywhere); CTA 0 writes it out
-                prof_mark(P, tp, 2 * k + 1);
+                prof_mark(P, 2 * k + 1);
                 best = -INFINITY; bidx = 0x7fffffff;
                 bool okc = ok;
                 for (int c0 = 0; c0 < n_cand && okc; c0 += 2 * DNT) {
@@ -1207,7 +1737,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                         }
                     }
                 }
-                prof_mark(P, tp, kProfWait);
+                prof_mark(P, kProfWait);
                 #pragma unroll
                 for (int o = 16; o; o >>= 1) {
                     const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
@@ -1220,21 +1750,23 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                     for (int w = 1; w < DNW; w++) if (cv[w] > cv[0] || (cv[w] == cv[0] && ci[w] < ci[0])) { cv[0] = cv[w]; ci[0] = ci[w]; }
                     const int t = ci[0] == 0x7fffffff ? 0 : ci[0];
                     s_tok = t;
-                    if (blockIdx.x == 0 && ok) { __stcg(P.cur_token, t); __stcg(P.best_val, cv[0]); P.out_tokens[step] = t; }
+                    if (ws.gcta == 0 && ok) { __stcg(P.cur_token, t); __stcg(P.best_val, cv[0]); P.out_tokens[step] = t; }
                 }
             }
             ok = __syncthreads_and(ok ? 1 : 0) != 0;          // a wait that gave up in one warp stops the whole CTA
-            prof_mark(P, tp, 2 * k + 1);
+            prof_mark(P, 2 * k + 1);
         }
     }
 #if MI_PROF
-    if (P.prof && blockIdx.x == 0) {
+    if (P.prof && (int)blockIdx.x == P.prof_cta) {
+        if (tid == 0) { s_prof[8] = (unsigned long long)(clock64() - prof_c0); s_prof[9] = gtime_ns() - prof_t0; }     // SM cycles and nanoseconds of the launch (overwrites two phase slots)
         __syncthreads();
         if (tid < kProfSlots) P.prof[tid] += s_prof[tid];
     }
 #endif
-    // CTA 0 has seen every CTA's last candidates (or has given up after a full time budget): all CTAs have read the epoch
-    if (blockIdx.x == 0 && tid == 0 && (ph1 == nph || !ok))
+    // the first GEMV CTA has seen every CTA's last candidates, which descend from every attention CTA's output (or it has given
+    // up after a full time budget): all CTAs have read the epoch
+    if (ws.gcta == 0 && tid == 0 && (ph1 == nph || !ok))
         *P.epoch_dev = epoch + (unsigned)(step1 - step0) * (unsigned)nph + (ok ? 0u : (unsigned)nph);
     if (!ok) {
         if (lane == 0) atomicMax(P.err, err_code);

@@ -29,7 +29,7 @@ struct mi_model {
     int device = 0;
     int L = 0, E = 0, FF = 0, NH = 0, NKV = 0, HD = 0, KVD = 0, V = 0, G = 0;
     float eps = 1e-6f, rope_base = 1e6f;
-    int max_seq = 0, grid = 0, max_chunks = 0;
+    int max_seq = 0, grid = 0, max_chunks = 0, attn_ctas = 0;
     int tp_rank = 0, tp_world = 1;
     bool tied = false;
     int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)

@@ -99,10 +99,10 @@ __global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ D
     Q.attn_part = P.attn_part + (size_t)m * P.NH * P.max_chunks * (HD + 2);
     Q.attn_cnt = P.attn_cnt + (size_t)m * P.NH;
     Q.prof = nullptr;
-    unsigned long long tp = 0;
     const int pos = (pos0_dev ? __ldg(pos0_dev) : pos0_val) + m;
-    if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G, false, QNAT>(Q, l, pos, smem, tp);
-    else attention_phase<HD, G, G, false, QNAT>(Q, l, pos, smem, tp);
+    if (pos + 1 <= kShortAttnMax) attention_short<HD, G, false, QNAT>(Q, l, pos, smem);
+    else if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G, false, QNAT>(Q, l, pos, smem);
+    else attention_phase<HD, G, G, false, QNAT>(Q, l, pos, smem);
 }
 
 // SwiGLU of the interleaved gate / up groups -> q8_0; one warp per 32-element block
