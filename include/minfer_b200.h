@@ -88,6 +88,20 @@ MI_API int mi_device_free(mi_ctx* ctx, void* ptr_dev);
 MI_API int mi_memcpy_to_device(mi_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes);
 MI_API int mi_memcpy_to_host(mi_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes);
 
+/* ---- machine probes ------------------------------------------------------ */
+
+/* Read-only streaming bandwidth of this GPU as the kernels here stream: the call allocates `bytes`
+ * of device memory (use several GB: far more than the L2), reads it `repeats` times in one launch
+ * each and returns the best GB/s.  variant 0: 16-byte loads, eight in flight per thread; variant 1:
+ * the GEMV's transport (per-warp ring of 4608-byte bulk copies).  The method of the reference's
+ * bench/roofline.cu:39-116. */
+MI_API int mi_probe_read_bw(mi_ctx* ctx, size_t bytes, int variant, int repeats, float* gbs_out);
+/* One-way latency, in nanoseconds at the nominal SM clock, of an 8-byte word stored by one SM until
+ * a polling SM sees it (two CTAs answering each other `iters` times): the cost of a phase boundary
+ * of the decode kernel.  Stands where the reference measures its grid barrier
+ * (bench/roofline.cu:125-149). */
+MI_API int mi_probe_hop_ns(mi_ctx* ctx, int iters, float* ns_out);
+
 /* ---- weights: GGUF q4_0 -> tiled device layout --------------------------- */
 
 /* Upload `count` consecutive row-major q4_0 matrices of rows x cols (18-byte
@@ -227,6 +241,36 @@ MI_API int mi_model_state_ptr(const mi_model* model, int which, void** ptr, int6
  * src/cuda_infer.cu:1031-1201 and the mega kernel of src/mega.cu:597-903. */
 MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
                      int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms);
+/* Top-1 minus top-2 logit of each of the first n steps of the last mi_decode call on this model
+ * (host memory out).  The reference's engine reports this margin per token (src/mega.cu:385-392,
+ * 523-550, printed at :1189, 1196, 1241); its A/B harness reads it (tools/ab.sh:41,49). */
+MI_API int mi_decode_margins(mi_ctx* ctx, mi_model* model, int n, float* margins_host);
+
+/* ---- streaming hand-off of generated tokens ----------------------------------- */
+
+/* A token ring: pinned host memory mapped into the GPU's address space.  A generation started with
+ * mi_decode_run publishes every step's greedy token, its logit margin and a GPU time stamp into the
+ * ring while the kernel is still running (the count of valid entries is raised every fourth step
+ * and at the end, after a system-scope fence); the host polls mi_ring_peek and can print or stop
+ * reading at any time.  The reference's mega driver does exactly this: src/mega.cu:1130-1137 (the
+ * mapped ring), :847-856 (publish), :1166-1178 (host poll).  Entries accumulate over successive
+ * runs until mi_ring_reset; a run that would overflow the ring is refused with MI_ERR_LIMIT. */
+typedef struct mi_token_ring mi_token_ring;
+MI_API int mi_ring_create(mi_ctx* ctx, int capacity, mi_token_ring** out);
+MI_API int mi_ring_destroy(mi_ctx* ctx, mi_token_ring* ring);
+/* Waits for the stream, then forgets all entries. */
+MI_API int mi_ring_reset(mi_ctx* ctx, mi_token_ring* ring);
+/* Number of valid entries right now (acquire load) and the arrays they live in (host pointers,
+ * valid for the ring's lifetime): tokens, margins, GPU nanosecond stamps.  Any pointer may be NULL. */
+MI_API int mi_ring_peek(const mi_token_ring* ring, int* count, const int32_t** tokens, const float** margins,
+                        const uint64_t** ns);
+/* mi_decode with the persistent engine, asynchronous: enqueue n_steps steps at positions pos0..,
+ * return at once; the tokens arrive in `ring`.  mi_ctx_sync waits for the end (and reports a
+ * time-out).  The proposal of the reference-side boundary, mi_decode_run(ctx, model, prompt,
+ * n_prompt, n_gen, ring), in this library's argument convention. */
+MI_API int mi_decode_run(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
+                         mi_token_ring* ring);
+
 /* Test hook for the time-out path: from now on the producers of phase `phase` (5 * layer + kind;
  * 5 * n_layer = lm_head) compute but publish nothing, so the waits of that phase's consumers run
  * out after the context's wait budget and the call returns MI_ERR_TIMEOUT - nothing hangs or
@@ -250,6 +294,23 @@ MI_API int mi_decode_phases(mi_ctx* ctx, mi_model* model, int32_t token, int pos
  * fp32.  The model's current token becomes out_tokens[M-1].  Synchronous.  Unsharded models only. */
 MI_API int mi_verify(mi_ctx* ctx, mi_model* model, const int32_t* tokens_host, int M, int pos0,
                      int32_t* out_tokens_host, float* logits_dev, float* elapsed_ms);
+
+/* Greedy generation with lossless n-gram speculation: process the prompt (16 tokens per weight
+ * pass), then generate n_gen tokens.  Each step drafts up to draftk (0..15; 0 = no speculation)
+ * tokens by prompt lookup - the tokens that followed the latest earlier occurrence of the last
+ * ngmax .. 1 tokens of the sequence so far - scores the current token and the draft in ONE
+ * M-token pass (mi_verify) and keeps the longest prefix of the draft that equals the model's own
+ * greedy tokens; without a draft it runs one single-token step (mi_decode).  Because a token's
+ * logits are the same bits in both kinds of step, out_tokens_host[0 .. n_gen) is exactly the
+ * sequence plain greedy decoding produces (the first id is the prediction after the last prompt
+ * token).  margins_host (optional, [n_gen]): the logit margin (top-1 minus top-2) of the step that
+ * produced each id.  stats (optional, 4 values): generation steps, drafted tokens, accepted tokens,
+ * steps that ran a draft.  The reference's speculative loops: src/cuda_infer.cu:1203-1292 (host) and
+ * src/mega.cu:557-589, 863-895 (in-kernel); its gate tools/specbench.sh:33-36. */
+MI_API int mi_generate_spec(mi_ctx* ctx, mi_model* model, const int32_t* prompt_host, int n_prompt, int n_gen, int ngmax,
+                            int draftk, int32_t* out_tokens_host, float* margins_host, int64_t* stats);
+/* Logit margins of the first n tokens of the last mi_verify pass on this model. */
+MI_API int mi_verify_margins(mi_ctx* ctx, mi_model* model, int n, float* margins_host);
 
 /* Split-KV causal attention with grouped queries for M (1..16) consecutive query positions
  * (replaces attn_partial + attn_combine, src/cuda_infer.cu:650-702, and mega's attention + combine,

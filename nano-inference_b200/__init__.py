@@ -41,6 +41,8 @@ SIGNATURES = {
     "mi_ctx_sync": (_i32, [_vp]),
     "mi_last_error": (C.c_char_p, [_vp]),
     "mi_ctx_set_wait_budget_ns": (_i32, [_vp, C.c_uint64]),
+    "mi_probe_read_bw": (_i32, [_vp, C.c_size_t, _i32, _i32, C.POINTER(C.c_float)]),
+    "mi_probe_hop_ns": (_i32, [_vp, _i32, C.POINTER(C.c_float)]),
     "mi_model_debug_drop_phase": (_i32, [_vp, _i32]),
     "mi_ctx_sm_count": (_i32, [_vp]),
     "mi_device_malloc": (_i32, [_vp, C.c_size_t, C.POINTER(_vp)]),
@@ -65,7 +67,15 @@ SIGNATURES = {
     "mi_model_state_ptr": (_i32, [_vp, _i32, C.POINTER(_vp), C.POINTER(_i64)]),
     "mi_decode": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp, _vp, _i32, C.POINTER(C.c_float)]),
     "mi_decode_phases": (_i32, [_vp, _vp, _i32, _i32, _i32, _i32]),
+    "mi_decode_margins": (_i32, [_vp, _vp, _i32, _vp]),
+    "mi_ring_create": (_i32, [_vp, _i32, C.POINTER(_vp)]),
+    "mi_ring_destroy": (_i32, [_vp, _vp]),
+    "mi_ring_reset": (_i32, [_vp, _vp]),
+    "mi_ring_peek": (_i32, [_vp, C.POINTER(_i32), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp)]),
+    "mi_decode_run": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _vp]),
     "mi_verify": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(C.c_float)]),
+    "mi_generate_spec": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "mi_verify_margins": (_i32, [_vp, _vp, _i32, _vp]),
     "mi_attn_splitkv": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "mi_tp_partition": (None, [_i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_i32)]),
     "mi_model_load_gguf_tp": (_i32, [_vp, C.c_char_p, _i32, _i32, _i32, C.POINTER(_vp)]),
@@ -167,6 +177,18 @@ class Context:
     def sync(self):
         self.check(self.lib.mi_ctx_sync(self.h), "mi_ctx_sync")
 
+    def probe_read_bw(self, nbytes, variant=0, repeats=3):
+        """Read-only streaming GB/s over a freshly allocated buffer of nbytes (variant 0: 16-byte loads, 1: bulk-copy ring)."""
+        v = C.c_float()
+        self.check(self.lib.mi_probe_read_bw(self.h, int(nbytes), variant, repeats, C.byref(v)), "mi_probe_read_bw")
+        return v.value
+
+    def probe_hop_ns(self, iters=2000):
+        """One-way store-to-load latency between two SMs, nanoseconds."""
+        v = C.c_float()
+        self.check(self.lib.mi_probe_hop_ns(self.h, iters, C.byref(v)), "mi_probe_hop_ns")
+        return v.value
+
     def set_wait_budget_ns(self, ns):
         """Time budget of the decode kernel's device-side waits (default 2 s)."""
         self.check(self.lib.mi_ctx_set_wait_budget_ns(self.h, int(ns)), "mi_ctx_set_wait_budget_ns")
@@ -235,6 +257,40 @@ class Weight:
             pass
 
 
+class TokenRing:
+    """Host-mapped ring a running generation publishes its tokens into: wraps mi_token_ring."""
+
+    def __init__(self, ctx, capacity):
+        self.ctx = ctx
+        h = _vp()
+        ctx.check(ctx.lib.mi_ring_create(ctx.h, capacity, C.byref(h)), "mi_ring_create")
+        self.h = h
+
+    def peek(self):
+        """(count, tokens, margins, ns) of the entries valid right now, as lists."""
+        n, t, g, s = _i32(), _vp(), _vp(), _vp()
+        self.ctx.check(self.ctx.lib.mi_ring_peek(self.h, C.byref(n), C.byref(t), C.byref(g), C.byref(s)), "mi_ring_peek")
+        k = n.value
+        toks = list((C.c_int32 * k).from_address(t.value)) if k else []
+        mar = list((C.c_float * k).from_address(g.value)) if k else []
+        ns = list((C.c_uint64 * k).from_address(s.value)) if k else []
+        return k, toks, mar, ns
+
+    def reset(self):
+        self.ctx.check(self.ctx.lib.mi_ring_reset(self.ctx.h, self.h), "mi_ring_reset")
+
+    def free(self):
+        if self.h and self.ctx.h:
+            self.ctx.lib.mi_ring_destroy(self.ctx.h, self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class Model:
     """A loaded GGUF model with its KV cache and decode state: wraps mi_model."""
 
@@ -257,6 +313,19 @@ class Model:
                                               _ptr(out), _ptr(logits), mode, C.byref(ms)), "mi_decode")
         return out[:n_steps].tolist(), ms.value
 
+    def margins(self, n):
+        """Top-1 minus top-2 logit of the first n steps of the last decode call (numpy float32)."""
+        import numpy as np
+        out = np.empty(max(n, 1), dtype=np.float32)
+        self.ctx.check(self.ctx.lib.mi_decode_margins(self.ctx.h, self.h, n, _ptr(out)), "mi_decode_margins")
+        return out[:n]
+
+    def decode_run(self, in_tokens, n_steps, pos0, ring):
+        """Asynchronous persistent decode whose tokens arrive in `ring` (a TokenRing) while the kernel runs."""
+        import numpy as np
+        toks = np.ascontiguousarray(in_tokens, dtype=np.int32)
+        self.ctx.check(self.ctx.lib.mi_decode_run(self.ctx.h, self.h, _ptr(toks) if toks.size else None, toks.size, n_steps, pos0, ring.h), "mi_decode_run")
+
     def verify(self, tokens, pos0=0, logits=None):
         """One M-token pass (M = len(tokens) <= 16): returns (greedy token after each, device milliseconds)."""
         import numpy as np
@@ -265,6 +334,17 @@ class Model:
         ms = C.c_float(0)
         self.ctx.check(self.ctx.lib.mi_verify(self.ctx.h, self.h, _ptr(toks), toks.size, pos0, _ptr(out), _ptr(logits), C.byref(ms)), "mi_verify")
         return out.tolist(), ms.value
+
+    def generate_spec(self, prompt, n_gen, ngmax=3, draftk=4):
+        """Greedy generation with lossless n-gram speculation; returns (ids, stats dict)."""
+        import numpy as np
+        toks = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.empty(max(n_gen, 1), dtype=np.int32)
+        st = np.zeros(4, dtype=np.int64)
+        mg = np.zeros(max(n_gen, 1), dtype=np.float32)
+        self.ctx.check(self.ctx.lib.mi_generate_spec(self.ctx.h, self.h, _ptr(toks), toks.size, n_gen, ngmax, draftk, _ptr(out), _ptr(mg), _ptr(st)), "mi_generate_spec")
+        return out[:n_gen].tolist(), {"steps": int(st[0]), "drafted": int(st[1]), "accepted": int(st[2]), "spec_steps": int(st[3]),
+                                      "margins": mg[:n_gen]}
 
     def prefill(self, tokens, pos0=0, chunk=16):
         """Prompt processing through the M-token step, `chunk` tokens per weight pass; returns (token after the last one, ms)."""

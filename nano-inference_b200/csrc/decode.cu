@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <new>
 #include <string>
 #include <vector>
@@ -378,7 +379,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         x.act = take(q8_words(FF));
         x.down = take((E + 31) / 32 * 32);
         x.dpart = take((E + 31) / 32 * (kMaxKSplit - 1) * 64);
-        x.cand = take(kMaxWorldTP * m->grid * 2);
+        x.cand = take(kMaxWorldTP * m->grid * 4);
         x.total = off;
     }
     if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
@@ -446,8 +447,70 @@ extern "C" int mi_model_state_ptr(const mi_model* m, int which, void** ptr, int6
     return MI_OK;
 }
 
+struct mi_token_ring {
+    int capacity = 0;
+    void* host = nullptr;           // one mapped pinned allocation: count | tokens | margins | ns
+    int* h_count = nullptr; int32_t* h_tokens = nullptr; float* h_margins = nullptr; unsigned long long* h_ns = nullptr;
+    int* d_count = nullptr; int32_t* d_tokens = nullptr; float* d_margins = nullptr; unsigned long long* d_ns = nullptr;
+    int used = 0;                   // entries handed to launches so far
+};
+
+extern "C" int mi_ring_create(mi_ctx* ctx, int capacity, mi_token_ring** out) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!out || capacity < 1) return set_error(ctx, MI_ERR_INVALID, "ring_create: bad argument");
+    *out = nullptr;
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    mi_token_ring* r = new (std::nothrow) mi_token_ring();
+    if (!r) return set_error(ctx, MI_ERR_NOMEM, "ring_create: host allocation failed");
+    const size_t cap = (size_t)capacity, bytes = 64 + cap * 4 + cap * 4 + cap * 8 + 64;
+    cudaError_t e = cudaHostAlloc(&r->host, bytes, cudaHostAllocMapped);
+    if (e != cudaSuccess) { delete r; return set_error(ctx, MI_ERR_NOMEM, "ring_create: cudaHostAlloc(%zu) failed: %s", bytes, cudaGetErrorString(e)); }
+    memset(r->host, 0, bytes);
+    void* dev = nullptr;
+    e = cudaHostGetDevicePointer(&dev, r->host, 0);
+    if (e != cudaSuccess) { cudaFreeHost(r->host); delete r; return set_error(ctx, MI_ERR_CUDA, "ring_create: cudaHostGetDevicePointer failed"); }
+    auto carve = [&](uint8_t* base) {
+        struct { int* c; int32_t* t; float* g; unsigned long long* n; } v;
+        v.c = reinterpret_cast<int*>(base); v.n = reinterpret_cast<unsigned long long*>(base + 64);
+        v.t = reinterpret_cast<int32_t*>(base + 64 + cap * 8); v.g = reinterpret_cast<float*>(base + 64 + cap * 8 + cap * 4);
+        return v;
+    };
+    auto h = carve(reinterpret_cast<uint8_t*>(r->host)); auto d = carve(reinterpret_cast<uint8_t*>(dev));
+    r->h_count = h.c; r->h_tokens = h.t; r->h_margins = h.g; r->h_ns = h.n;
+    r->d_count = d.c; r->d_tokens = d.t; r->d_margins = d.g; r->d_ns = d.n;
+    r->capacity = capacity;
+    *out = r;
+    return MI_OK;
+}
+
+extern "C" int mi_ring_destroy(mi_ctx* ctx, mi_token_ring* r) {
+    if (!r) return MI_OK;
+    if (ctx) { cudaSetDevice(ctx->device); cudaStreamSynchronize(ctx->stream); }
+    if (r->host) cudaFreeHost(r->host);
+    delete r;
+    return MI_OK;
+}
+
+extern "C" int mi_ring_reset(mi_ctx* ctx, mi_token_ring* r) {
+    if (!r) return MI_ERR_INVALID;
+    if (ctx) { cudaSetDevice(ctx->device); cudaStreamSynchronize(ctx->stream); }
+    r->used = 0;
+    __atomic_store_n(r->h_count, 0, __ATOMIC_RELEASE);
+    return MI_OK;
+}
+
+extern "C" int mi_ring_peek(const mi_token_ring* r, int* count, const int32_t** tokens, const float** margins, const uint64_t** ns) {
+    if (!r) return MI_ERR_INVALID;
+    if (count) *count = __atomic_load_n(r->h_count, __ATOMIC_ACQUIRE);
+    if (tokens) *tokens = r->h_tokens;
+    if (margins) *margins = r->h_margins;
+    if (ns) *ns = reinterpret_cast<const uint64_t*>(r->h_ns);
+    return MI_OK;
+}
+
 static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
-                       int32_t* out_tokens_host, float* logits_dev, int mode, int ph0, int ph1, float* elapsed_ms) {
+                       int32_t* out_tokens_host, float* logits_dev, int mode, int ph0, int ph1, float* elapsed_ms,
+                       mi_token_ring* ring = nullptr, bool async = false) {
     if (!ctx) return MI_ERR_INVALID;
     if (!m) return set_error(ctx, MI_ERR_INVALID, "decode: null model");
     if (n_steps < 0 || n_forced < 0 || pos0 < 0) return set_error(ctx, MI_ERR_INVALID, "decode: negative count");
@@ -465,9 +528,12 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
         m->in_capacity = n_forced * 2;
     }
     if (n_steps > m->out_capacity) {
-        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, (size_t)n_steps * 2))) return st;
+        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, (size_t)n_steps * 2)) || (st = dev_alloc(ctx, m, &m->d_margins, (size_t)n_steps * 2))) return st;
         m->out_capacity = n_steps * 2;
     }
+    m->last_steps = n_steps;
+    if (ring && ring->used + n_steps > ring->capacity)
+        return set_error(ctx, MI_ERR_LIMIT, "decode: the token ring holds %d entries, %d are used and %d more are asked for", ring->capacity, ring->used, n_steps);
     if (n_forced) MI_CUDA(ctx, cudaMemcpyAsync(m->d_in_tokens, in_tokens_host, (size_t)n_forced * 4, cudaMemcpyHostToDevice, ctx->stream));
     DecodeParams P = m->P;
     if (m->tp_world > 1) {
@@ -482,7 +548,13 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
     P.wait_ns = ctx->wait_ns;
     if ((st = mi::reset_after_error(ctx, m))) return st;
     P.in_tokens = m->d_in_tokens; P.n_forced = n_forced; P.out_tokens = m->d_out_tokens; P.pos0 = pos0;
+    P.out_margins = m->d_margins;
     P.logits = logits_dev; P.logits_stride = m->V;
+    if (ring) {
+        P.ring.count = ring->d_count; P.ring.tokens = ring->d_tokens; P.ring.margins = ring->d_margins; P.ring.ns = ring->d_ns;
+        P.ring.capacity = ring->capacity; P.ring.base = ring->used;
+        ring->used += n_steps;
+    }
     const int nph = 5 * m->L + 1;
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
     if (mode == MI_DECODE_PERSISTENT) {
@@ -498,6 +570,7 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
         return set_error(ctx, MI_ERR_INVALID, "decode: unknown mode %d", mode);
     }
     MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    if (async) return MI_OK;                          // the caller follows the ring and synchronizes itself
     if (out_tokens_host)
         MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, m->d_out_tokens, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     st = mi_ctx_sync(ctx);
@@ -510,6 +583,21 @@ extern "C" int mi_decode(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host
                          int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms) {
     return decode_impl(ctx, m, in_tokens_host, n_forced, n_steps, pos0, out_tokens_host, logits_dev, mode, 0,
                        m ? 5 * m->L + 1 : 0, elapsed_ms);
+}
+
+extern "C" int mi_decode_run(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0, mi_token_ring* ring) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!ring) return set_error(ctx, MI_ERR_INVALID, "decode_run: null ring");
+    return decode_impl(ctx, m, in_tokens_host, n_forced, n_steps, pos0, nullptr, nullptr, MI_DECODE_PERSISTENT, 0, m ? 5 * m->L + 1 : 0, nullptr, ring, true);
+}
+
+extern "C" int mi_decode_margins(mi_ctx* ctx, mi_model* m, int n, float* margins_host) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !margins_host || n < 0 || n > m->last_steps) return set_error(ctx, MI_ERR_INVALID, "decode_margins: the last decode call ran %d steps", m ? m->last_steps : 0);
+    if (n == 0) return MI_OK;
+    MI_CUDA(ctx, cudaMemcpyAsync(margins_host, m->d_margins, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return MI_OK;
 }
 
 extern "C" int mi_decode_phases(mi_ctx* ctx, mi_model* m, int32_t token, int pos, int phase_begin, int phase_end) {
@@ -623,11 +711,11 @@ static int launch_phases(mi_ctx* ctx, mi_model* m, int pos, int phase_begin, int
     if (!dev_pos && (pos < 0 || pos >= m->max_seq)) return set_error(ctx, MI_ERR_LIMIT, "decode_launch: position %d outside the KV cache of %d", pos, m->max_seq);
     int st;
     if (m->out_capacity < 1) {
-        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, 16))) return st;
+        if ((st = dev_alloc(ctx, m, &m->d_out_tokens, 16)) || (st = dev_alloc(ctx, m, &m->d_margins, 16))) return st;
         m->out_capacity = 16;
     }
     DecodeParams P = m->P;
-    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.pos0 = dev_pos ? 0 : pos; P.logits = nullptr; P.logits_stride = m->V;
+    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_out_tokens; P.out_margins = m->d_margins; P.pos0 = dev_pos ? 0 : pos; P.logits = nullptr; P.logits_stride = m->V;
     P.pos_dev = dev_pos ? m->d_pos : nullptr;
     P.wait_ns = ctx->wait_ns;
     if ((st = mi::reset_after_error(ctx, m))) return st;

@@ -136,9 +136,13 @@ struct XwLayout {
     int act;        // q8_0 of SwiGLU(gate, up) [FF]                                     (pushed to the other GPUs)
     int down;       // [E] fp32 bits: down projection                                    (pushed)
     int dpart;      // [E/32][kMaxKSplit-1][32][2]: double partial sums (lo, hi) of the down K-splits 1..
-    int cand;       // [kMaxWorldTP][grid][2]: argmax candidates {fp32 value bits}, {index}   (pushed)
+    int cand;       // [kMaxWorldTP][grid][4]: argmax candidates {best value}, {its row}, {second-best value}, -   (pushed)
     int total;
 };
+
+// Host-mapped (pinned, device-visible) memory through which a running generation hands its tokens to the host
+// (src/mega.cu:1130-1137): the kernel fills tokens / margins / ns from entry `base` on and raises *count.
+struct TokenRing { int* count; int* tokens; float* margins; unsigned long long* ns; int capacity, base; };
 
 struct DecodeParams {
     int L, E, FF, NH, NKV, HD, KVD, V;
@@ -170,6 +174,8 @@ struct DecodeParams {
     int8_t* att_q; __half* att_d;
     __half* kc; __half* vc; int max_seq;       // [L][max_seq][KVD]
     double* attn_part; unsigned* attn_cnt; int max_chunks;  // [NH][max_chunks][HD+2], [NKV]
+    float* out_margins;              // optional [n_steps]: top-1 minus top-2 logit of every step
+    TokenRing ring;                  // optional: host-mapped ring the first GEMV CTA publishes every step's token into
     float* best_val;                 // value of the best logit (tensor parallelism with host-side exchange: this GPU's rows only)
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
     float* logits; long long logits_stride;    // optional [n_steps][stride]
@@ -225,6 +231,27 @@ __device__ __forceinline__ void prof_mark(const DecodeParams& P, int k) {
     if (P.prof && (int)blockIdx.x == P.prof_cta && threadIdx.x == 0) { const unsigned long long n = gtime_ns(); s_prof[k] += n - s_prof_t; s_prof_t = n; }
 #endif
 }
+
+// A greedy-pick candidate: best value, its row (lowest row wins ties), and the runner-up value.
+struct Cand {
+    float best; int idx; float second;
+    __device__ __forceinline__ void add(float v, int r) {
+        if (v > best || (v == best && r < idx)) { second = best; best = v; idx = r; }
+        else if (v > second) second = v;
+    }
+    __device__ __forceinline__ void merge(const Cand& o) {
+        if (o.best > best || (o.best == best && o.idx < idx)) { second = fmaxf(best, o.second); best = o.best; idx = o.idx; }
+        else second = fmaxf(second, o.best);
+    }
+    __device__ __forceinline__ void warp_reduce() {
+        #pragma unroll
+        for (int s = 16; s; s >>= 1) {
+            Cand o;
+            o.best = __shfl_xor_sync(0xffffffffu, best, s); o.idx = __shfl_xor_sync(0xffffffffu, idx, s); o.second = __shfl_xor_sync(0xffffffffu, second, s);
+            merge(o);
+        }
+    }
+};
 
 // ---- tagged words ---------------------------------------------------------------------
 // One 64-bit access carries value and tag together, so there is nothing to order between them.
@@ -1592,7 +1619,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     const int pos_base = P.pos_dev ? __ldcg(P.pos_dev) : P.pos0;
     // candidates of the greedy pick: one {value, index} pair of words per CTA (and per GPU when the exchange runs in here)
     const int cand_world = P.tp.on ? P.tp.world : 1, n_cand = cand_world * ws.ggrid;
-    const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * ws.ggrid + ws.gcta) * 2;
+    const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * ws.ggrid + ws.gcta) * 4;
 
     auto rope_table = [&](int pos) {                   // cos / sin of this position's angles, fp32 angle as src/cpu_infer.cpp:54
         if (tid < HD / 2) {
@@ -1691,7 +1718,9 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 });
             } else {
                 // ---- lm_head on the staged final norm, greedy argmax (lowest index wins ties)
-                float best = -INFINITY; int bidx = 0x7fffffff;
+                // Each candidate is {best value, its row, second-best value}: the runner-up gives the logit margin (top-1 minus
+                // top-2) that the reference's engine reports per token (src/mega.cu:523-550, 385-392).
+                Cand cd; cd.best = -INFINITY; cd.idx = 0x7fffffff; cd.second = -INFINITY;
                 float* lg = P.logits ? P.logits + (long long)(step - step0) * P.logits_stride : nullptr;
                 ok = run_warp_job(ws, 4 * P.L, lane, xq_s, xs_s, [&](int g, int ln, float v0) {
                     const int r = g * 32 + ln;
@@ -1700,57 +1729,65 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                         // the reference's scan starts from logits[0] and moves on strict '>' (src/cpu_infer.cpp:153-154): a NaN
                         // never wins, and a NaN in row 0 is never beaten
                         const float vv = (r == 0 && v0 != v0) ? INFINITY : v0;
-                        if (vv > best || (vv == best && r < bidx)) { best = vv; bidx = r; }
+                        cd.add(vv, r);
                     }
                 });
-                #pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
-                    if (ob > best || (ob == best && oi < bidx)) { best = ob; bidx = oi; }
-                }
+                cd.warp_reduce();
                 __syncthreads();
-                float* cv = reinterpret_cast<float*>(sm.red); int* ci = reinterpret_cast<int*>(sm.red) + 16;
-                if (lane == 0) { cv[warp] = best; ci[warp] = bidx; }
+                float* cv = reinterpret_cast<float*>(sm.red); int* ci = reinterpret_cast<int*>(sm.red) + 16; float* c2 = reinterpret_cast<float*>(sm.red) + 32;
+                if (lane == 0) { cv[warp] = cd.best; ci[warp] = cd.idx; c2[warp] = cd.second; }
                 __syncthreads();
                 if (tid == 0) {
-                    for (int w = 1; w < DNW; w++) if (cv[w] > cv[0] || (cv[w] == cv[0] && ci[w] < ci[0])) { cv[0] = cv[w]; ci[0] = ci[w]; }
-                    pub.shared(my_cand, __float_as_uint(cv[0]));
-                    pub.shared(my_cand + 1, (unsigned)ci[0]);
+                    Cand t; t.best = cv[0]; t.idx = ci[0]; t.second = c2[0];
+                    for (int w = 1; w < DNW; w++) { Cand o; o.best = cv[w]; o.idx = ci[w]; o.second = c2[w]; t.merge(o); }
+                    pub.shared(my_cand, __float_as_uint(t.best));
+                    pub.shared(my_cand + 1, (unsigned)t.idx);
+                    pub.shared(my_cand + 2, __float_as_uint(t.second));
                 }
                 // the next step's angles while the other CTAs' candidates arrive
                 if (step + 1 < step1) rope_table(pos + 1);
-                // every CTA makes the pick over all candidates itself (the same bits everywhere); CTA 0 writes it out
+                // every CTA makes the pick over all candidates itself (the same bits everywhere); the first GEMV CTA writes it out
                 prof_mark(P, 2 * k + 1);
-                best = -INFINITY; bidx = 0x7fffffff;
+                cd.best = -INFINITY; cd.idx = 0x7fffffff; cd.second = -INFINITY;
                 bool okc = ok;
                 for (int c0 = 0; c0 < n_cand && okc; c0 += 2 * DNT) {
-                    unsigned cw[4], valid = 0;
-                    if (c0 + tid < n_cand) valid |= 3u;
-                    if (c0 + DNT + tid < n_cand) valid |= 12u;
-                    const unsigned long long* cb = P.xw + P.xo.cand + (size_t)(c0 + tid) * 2;
-                    okc = tw_poll(P, pub.tag, valid, [&](int q) { return cb + (q >> 1) * (2 * DNT) + (q & 1); }, cw);
+                    unsigned cw[6], valid = 0;
+                    if (c0 + tid < n_cand) valid |= 7u;
+                    if (c0 + DNT + tid < n_cand) valid |= 56u;
+                    const unsigned long long* cb = P.xw + P.xo.cand + (size_t)(c0 + tid) * 4;
+                    okc = tw_poll(P, pub.tag, valid, [&](int q) { return cb + (q / 3) * (4 * DNT) + (q % 3); }, cw);
                     #pragma unroll
                     for (int h = 0; h < 2; h++) {
-                        if (okc && (valid >> (2 * h) & 1u)) {
-                            const float v = __uint_as_float(cw[2 * h]); const int ix = (int)cw[2 * h + 1];
-                            if (v > best || (v == best && ix < bidx)) { best = v; bidx = ix; }
+                        if (okc && (valid >> (3 * h) & 1u)) {
+                            Cand o; o.best = __uint_as_float(cw[3 * h]); o.idx = (int)cw[3 * h + 1]; o.second = __uint_as_float(cw[3 * h + 2]);
+                            cd.merge(o);
                         }
                     }
                 }
                 prof_mark(P, kProfWait);
-                #pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    const float ob = __shfl_xor_sync(0xffffffffu, best, o); const int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
-                    if (ob > best || (ob == best && oi < bidx)) { best = ob; bidx = oi; }
-                }
-                ok = __syncthreads_and(okc ? 1 : 0) != 0;       // also: cv / ci are free again
-                if (lane == 0) { cv[warp] = best; ci[warp] = bidx; }
+                cd.warp_reduce();
+                ok = __syncthreads_and(okc ? 1 : 0) != 0;       // also: cv / ci / c2 are free again
+                if (lane == 0) { cv[warp] = cd.best; ci[warp] = cd.idx; c2[warp] = cd.second; }
                 __syncthreads();
                 if (tid == 0) {
-                    for (int w = 1; w < DNW; w++) if (cv[w] > cv[0] || (cv[w] == cv[0] && ci[w] < ci[0])) { cv[0] = cv[w]; ci[0] = ci[w]; }
-                    const int t = ci[0] == 0x7fffffff ? 0 : ci[0];
-                    s_tok = t;
-                    if (ws.gcta == 0 && ok) { __stcg(P.cur_token, t); __stcg(P.best_val, cv[0]); P.out_tokens[step] = t; }
+                    Cand t; t.best = cv[0]; t.idx = ci[0]; t.second = c2[0];
+                    for (int w = 1; w < DNW; w++) { Cand o; o.best = cv[w]; o.idx = ci[w]; o.second = c2[w]; t.merge(o); }
+                    const int tok = t.idx == 0x7fffffff ? 0 : t.idx;
+                    s_tok = tok;
+                    if (ws.gcta == 0 && ok) {
+                        const float margin = __fsub_rn(t.best, t.second);
+                        __stcg(P.cur_token, tok); __stcg(P.best_val, t.best); P.out_tokens[step] = tok;
+                        if (P.out_margins) P.out_margins[step] = margin;
+                        if (P.ring.count) {
+                            // the host reads along: token, margin and time of every step into mapped host memory, the count of
+                            // valid entries every fourth step and at the end, after a system-scope fence (src/mega.cu:847-856)
+                            const int slot = P.ring.base + (step - step0);
+                            if (slot < P.ring.capacity) {
+                                P.ring.tokens[slot] = tok; P.ring.margins[slot] = margin; P.ring.ns[slot] = gtime_ns();
+                                if (((step - step0) & 3) == 3 || step == step1 - 1) { __threadfence_system(); *reinterpret_cast<volatile int*>(P.ring.count) = slot + 1; }
+                            }
+                        }
+                    }
                 }
             }
             ok = __syncthreads_and(ok ? 1 : 0) != 0;          // a wait that gave up in one warp stops the whole CTA

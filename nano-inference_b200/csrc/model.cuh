@@ -22,6 +22,7 @@ struct VerifyBufs {
     bool warm[51] = {};                // index: M + 17 * attention regime (see verify.cu)
     double* attn_part = nullptr; unsigned* attn_cnt = nullptr;   // [M][NH][max_chunks][HD+2], [M][NH]
     unsigned long long* amax_key = nullptr; unsigned* amax_cnt = nullptr;   // [M] argmax scratch, self-clearing
+    float* margins = nullptr;          // [M] greedy logit minus the runner-up
 };
 }
 
@@ -38,6 +39,7 @@ struct mi_model {
     mi::DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
     int* d_in_tokens = nullptr; int in_capacity = 0;
     int* d_out_tokens = nullptr; int out_capacity = 0;
+    float* d_margins = nullptr; int last_steps = 0;   // top-1 minus top-2 logit of every step of the last decode call
     size_t smem = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     unsigned long long* prof_buf = nullptr;

@@ -1,0 +1,110 @@
+// Lossless n-gram (prompt-lookup) speculative decoding on top of the two step kinds of this library: the single-token
+// decode step and the M-token step, whose logits for a token are the same bits whatever else shares the pass.  A drafted
+// token is kept only if it equals the greedy token the model itself produces at that position, so the output is, token
+// for token, what plain greedy decoding gives.
+//
+// Follows the reference's host-side loop (src/cuda_infer.cu:1203-1292: draft from the latest earlier occurrence of the
+// current suffix, verify cur + draft in one weight pass, accept the longest matching prefix, continue from the model's
+// own token at the first mismatch, an acceptance estimate that switches drafting off while it does not pay and probes
+// now and then) with the longest-suffix-first lookup of its in-kernel form (src/mega.cu:557-576: n-gram lengths
+// ngmax .. 1).
+#include "model.cuh"
+
+#include <algorithm>
+#include <vector>
+
+using namespace mi;
+
+namespace {
+
+// the up to kmax tokens that followed the latest earlier occurrence of the last ng tokens of seq, ng = ngmax .. 1
+int ngram_draft(const std::vector<int32_t>& seq, int ngmax, int kmax, int32_t* draft) {
+    const int L = (int)seq.size();
+    if (kmax <= 0) return 0;
+    for (int ng = ngmax; ng >= 1; ng--) {
+        if (L < ng + 1) continue;
+        for (int j = L - ng - 1; j >= 0; j--) {
+            bool m = true;
+            for (int k = 0; k < ng && m; k++) m = seq[j + k] == seq[L - ng + k];
+            if (m) {
+                const int n = std::min(kmax, L - (j + ng));
+                for (int k = 0; k < n; k++) draft[k] = seq[j + ng + k];
+                return n;
+            }
+        }
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int mi_generate_spec(mi_ctx* ctx, mi_model* m, const int32_t* prompt_host, int n_prompt, int n_gen, int ngmax, int draftk,
+                                int32_t* out_tokens_host, float* margins_host, int64_t* stats) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !prompt_host || !out_tokens_host || n_prompt < 1 || n_gen < 0) return set_error(ctx, MI_ERR_INVALID, "generate_spec: bad argument");
+    if (m->tp_world != 1) return set_error(ctx, MI_ERR_UNSUPPORTED, "generate_spec: the M-token step runs on an unsharded model");
+    if (n_prompt + n_gen > m->max_seq) return set_error(ctx, MI_ERR_LIMIT, "generate_spec: %d prompt + %d generated tokens exceed the KV cache of %d", n_prompt, n_gen, m->max_seq);
+    constexpr int kMaxPass = 16;                                     // tokens per M-token pass
+    ngmax = std::max(1, std::min(ngmax, 8));
+    draftk = std::max(0, std::min(draftk, kMaxPass - 1));
+    int64_t n_steps = 0, n_drafted = 0, n_accepted = 0, n_specruns = 0;
+    int st;
+    // prompt: up to 16 tokens per weight pass; the last token's prediction is generated token #1
+    std::vector<int32_t> seq(prompt_host, prompt_host + n_prompt);
+    int32_t pred[kMaxPass];
+    for (int i = 0; i < n_prompt; i += kMaxPass) {
+        const int mt = std::min(kMaxPass, n_prompt - i);
+        if ((st = mi_verify(ctx, m, prompt_host + i, mt, i, pred, nullptr, nullptr))) return st;
+        if (i + mt == n_prompt) seq.push_back(pred[mt - 1]);
+    }
+    // margin of the token that is current: the logit margin of the step that predicted it
+    float mg[kMaxPass], cur_margin = 0.f;
+    if (margins_host) {
+        const int last = (n_prompt - 1) % kMaxPass;
+        if ((st = mi_verify_margins(ctx, m, last + 1, mg))) return st;
+        cur_margin = mg[last];
+    }
+    int32_t cur = seq.back();
+    int pos = n_prompt, n_emit = 0;
+    // while the recent acceptance rate is low a verify pass costs more than it brings: fall back to plain steps and probe
+    // every 32nd step with a single drafted token (src/cuda_infer.cu:1233-1243)
+    float ewma = 0.6f; const float gate = 0.55f; long probe = 0;
+    int32_t draft[kMaxPass], hb[kMaxPass], r[kMaxPass];
+    while (n_emit < n_gen) {
+        bool allow = ewma >= gate, probing = false;
+        if (!allow && (probe++ % 32) == 0) { allow = true; probing = true; }
+        int K = (allow && draftk > 0) ? ngram_draft(seq, ngmax, draftk, draft) : 0;
+        if (probing) K = std::min(K, 1);
+        K = std::min(K, m->max_seq - 1 - pos);                         // KV headroom
+        K = std::min(K, n_gen - n_emit - 1);                          // nothing is gained by drafting past the end
+        if (K <= 0) {
+            int32_t nxt;
+            if ((st = mi_decode(ctx, m, &cur, 1, 1, pos, &nxt, nullptr, MI_DECODE_PERSISTENT, nullptr))) return st;
+            if (margins_host) { margins_host[n_emit] = cur_margin; if ((st = mi_decode_margins(ctx, m, 1, &cur_margin))) return st; }
+            out_tokens_host[n_emit++] = cur;
+            cur = nxt; pos++; seq.push_back(cur);
+            n_steps++;
+            continue;
+        }
+        const int T = K + 1;                                          // cur and the draft at positions pos .. pos+K
+        hb[0] = cur;
+        for (int k = 0; k < K; k++) hb[1 + k] = draft[k];
+        if ((st = mi_verify(ctx, m, hb, T, pos, r, nullptr, nullptr))) return st;       // r[j] = the model's token after hb[j]
+        int a = 0;
+        while (a < K && draft[a] == r[a]) a++;
+        if (margins_host) {
+            if ((st = mi_verify_margins(ctx, m, T, mg))) return st;
+            margins_host[n_emit] = cur_margin;
+            for (int k = 0; k < a && n_emit + 1 + k < n_gen; k++) margins_host[n_emit + 1 + k] = mg[k];      // draft[k] was predicted by pass row k
+            cur_margin = mg[a];
+        }
+        out_tokens_host[n_emit++] = cur;
+        for (int k = 0; k < a && n_emit < n_gen; k++) out_tokens_host[n_emit++] = draft[k];
+        for (int k = 0; k < a; k++) seq.push_back(draft[k]);
+        cur = r[a]; pos += a + 1; seq.push_back(cur);                  // the model's own token at the first mismatch
+        ewma = 0.7f * ewma + 0.3f * ((float)a / (float)K);
+        n_steps++; n_specruns++; n_drafted += K; n_accepted += a;
+    }
+    if (stats) { stats[0] = n_steps; stats[1] = n_drafted; stats[2] = n_accepted; stats[3] = n_specruns; }
+    return MI_OK;
+}

@@ -154,6 +154,25 @@ __global__ void __launch_bounds__(512) vf_argmax(const float* logits, long long 
     }
 }
 
+// logit margin of every token of the pass: its greedy logit minus the largest other logit (one CTA per token)
+__global__ void __launch_bounds__(1024) vf_margin(const float* logits, long long stride, int V, const int* winner, float* margins) {
+    __shared__ float red[32];
+    pdl_launch_dependents(); pdl_wait_prior();
+    const int m = blockIdx.x, win = winner[m];
+    const float* lg = logits + (size_t)m * stride;
+    float second = -INFINITY;
+    for (int r = threadIdx.x; r < V; r += blockDim.x) { const float v = lg[r]; if (r != win && v > second) second = v; }
+    #pragma unroll
+    for (int o = 16; o; o >>= 1) second = fmaxf(second, __shfl_xor_sync(0xffffffffu, second, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = second;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); w++) second = fmaxf(second, red[w]);
+        const float best = (win >= 0 && win < V) ? lg[win] : -INFINITY;
+        margins[m] = __fsub_rn(best == best ? best : INFINITY, second);      // (a NaN in row 0 wins like +inf, as in the single-token step)
+    }
+}
+
 size_t attn_smem_bytes(int HD, int G) {
     return ((size_t)DNW * G * (HD + 2) * 8 + (size_t)DNW * 32 * G * 8 + (size_t)G * (HD + 16) * 8 + 127) / 128 * 128;
 }
@@ -187,7 +206,8 @@ int ensure_bufs(mi_ctx* ctx, mi_model* m) {
         (st = dev_alloc(ctx, m, &b.tokens, (size_t)M + 1)) || (st = dev_alloc(ctx, m, &b.out, (size_t)M)) ||
         (st = dev_alloc(ctx, m, &b.attn_part, (size_t)M * m->NH * m->max_chunks * (m->HD + 2))) ||
         (st = dev_alloc(ctx, m, &b.attn_cnt, (size_t)M * m->NH)) ||
-        (st = dev_alloc(ctx, m, &b.amax_key, (size_t)M)) || (st = dev_alloc(ctx, m, &b.amax_cnt, (size_t)M)))
+        (st = dev_alloc(ctx, m, &b.amax_key, (size_t)M)) || (st = dev_alloc(ctx, m, &b.amax_cnt, (size_t)M)) ||
+        (st = dev_alloc(ctx, m, &b.margins, (size_t)M)))
         return st;
     b.pos0 = b.tokens + M;            // tokens and position travel in one copy
     b.cap = M;
@@ -239,6 +259,7 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M, int regime) {
     if ((st = mi_gemm_q4_q8(ctx, &m->views[4 * L], b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, nullptr, b.logits))) return st;
     MI_CUDA(ctx, launch_k(pdl, vf_argmax, dim3(kArgmaxSlices, M), dim3(512), 0, ctx->stream, (const float*)b.logits, (long long)V, V, b.out,
                           b.amax_key, b.amax_cnt));
+    MI_CUDA(ctx, launch_k(pdl, vf_margin, dim3(M), dim3(1024), 0, ctx->stream, (const float*)b.logits, (long long)V, V, (const int*)b.out, b.margins));
     return MI_OK;
 }
 
@@ -306,6 +327,15 @@ extern "C" int mi_verify(mi_ctx* ctx, mi_model* m, const int32_t* tokens_host, i
     st = mi_ctx_sync(ctx);
     if (st != MI_OK) return st;
     if (elapsed_ms) MI_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, m->ev0, m->ev1));
+    return MI_OK;
+}
+
+extern "C" int mi_verify_margins(mi_ctx* ctx, mi_model* m, int n, float* margins_host) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !margins_host || n < 0 || n > VMAX || !m->vb.margins) return set_error(ctx, MI_ERR_INVALID, "verify_margins: bad argument, or no M-token pass has run");
+    if (n == 0) return MI_OK;
+    MI_CUDA(ctx, cudaMemcpyAsync(margins_host, m->vb.margins, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return MI_OK;
 }
 

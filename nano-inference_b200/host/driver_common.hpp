@@ -11,18 +11,28 @@
 // needs a real vocabulary and is outside this path.
 //
 // Environment: TEACHER=k (ids are a reference sequence whose first k are the
-// prompt; report top-1 agreement at every later position, as
-// src/cuda_infer.cu:1148-1160 / src/mega.cu:1192-1205), MAXSEQ=n (KV cache
-// positions; default prompt + n_gen + 8), WARMUP=n (untimed steps before the run),
-// PROFILE=1 (per-phase time on CTA 0, persistent engine), GPU=i (device index),
-// TCHUNK=m (prompt / teacher-forced tokens per weight pass through the M-token step,
-// 1..16, default 16; 1 = one decode step per token; src/cuda_infer.cu:1130-1144).
+// prompt; report top-1 agreement at every later position, with this engine's logit
+// margin on the misses, as src/cuda_infer.cu:1148-1160 / src/mega.cu:1192-1205),
+// MAXSEQ=n (KV cache positions; default prompt + n_gen + 8), WARMUP=n (untimed steps
+// before the run), PROFILE=1 (per-phase time on one CTA, persistent engine), GPU=i
+// (device index), TCHUNK=m (prompt / teacher-forced tokens per weight pass through
+// the M-token step, 1..16, default 16; 1 = one decode step per token;
+// src/cuda_infer.cu:1130-1144), SPEC=0|1 (lossless n-gram speculation;
+// default 1 in mega, 0 in cuda_infer, as in the reference: src/mega.cu:1020,
+// src/cuda_infer.cu:1167), NGMAX / NG (longest n-gram, default 3), DRAFTK (drafted
+// tokens per step, default 4), MARGINS=1 (last stderr line "i:tok:margin ..." for
+// every generated token, src/mega.cu:1241), SEGMENTS=w (tok/s over windows of w
+// tokens, src/mega.cu:1236-1240), ATTN (accepted and ignored: attention is always
+// split-KV here).  The mega driver prints ids as they arrive through the host-mapped
+// token ring while the kernel is still generating (src/mega.cu:1166-1178).
 #pragma once
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "minfer_b200.h"
@@ -82,57 +92,125 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
                 ms += cms;
             }
         }
+        std::vector<float> h((size_t)P * c.n_vocab);
+        if ((st = mi_memcpy_to_host(ctx, h.data(), logits, h.size() * sizeof(float)))) die(ctx, "mi_memcpy_to_host", st);
+        auto margin_at = [&](int i) {                            // top-1 minus top-2 logit of position i
+            const float* lg = h.data() + (size_t)i * c.n_vocab;
+            float b1 = -INFINITY, b2 = -INFINITY;
+            for (int v = 0; v < c.n_vocab; v++) { if (lg[v] > b1) { b2 = b1; b1 = lg[v]; } else if (lg[v] > b2) b2 = lg[v]; }
+            return b1 - b2;
+        };
         int agree = 0, total = 0;
         for (int i = teacher - 1; i + 1 < P; i++, total++) {
             if (pred[i] == ids[i + 1]) { agree++; continue; }
-            fprintf(stderr, "  pos %d: ref %d, %s %d\n", i + 1, ids[i + 1], tag, pred[i]);
+            fprintf(stderr, "  pos %d: ref %d, %s %d (%s margin %.4f)\n", i + 1, ids[i + 1], tag, pred[i], tag, margin_at(i));
         }
         // FNV-1a over the bits of every logit of every position: equal hashes mean bit-identical logits
-        std::vector<float> h((size_t)P * c.n_vocab);
-        if ((st = mi_memcpy_to_host(ctx, h.data(), logits, h.size() * sizeof(float)))) die(ctx, "mi_memcpy_to_host", st);
         unsigned long long hsh = 1469598103934665603ull;
         const unsigned char* b = reinterpret_cast<const unsigned char*>(h.data());
         for (size_t i = 0; i < h.size() * 4; i++) { hsh ^= b[i]; hsh *= 1099511628211ull; }
-        fprintf(stderr, "teacher-forced top-1 agreement: %d/%d | %d positions in %.1f ms | logit hash %016llx\n", agree, total, P, ms, hsh);
+        fprintf(stderr, "teacher-forced top-1 agreement: %d/%d | %d positions in %.1f ms (%.2f ms per %d-token step) | logit hash %016llx\n", agree, total, P,
+                ms, ms * tchunk / P, tchunk, hsh);
         mi_device_free(ctx, logits);
         mi_model_free(ctx, model); mi_ctx_destroy(ctx);
         return 0;
     }
 
-    // prefill: tchunk prompt tokens per weight pass (or one step per token); the last one predicts generated token #1
-    std::vector<int32_t> out(P > 0 ? P : 1);
-    float pms = 0;
+    const bool persistent = mode == MI_DECODE_PERSISTENT;
+    const int spec = env_int("SPEC", persistent ? 1 : 0);
+    const int ngmax = env_int("NGMAX", env_int("NG", 3)), draftk = env_int("DRAFTK", 4);
+    std::vector<int32_t> gen;                 // the n_gen generated ids
+    std::vector<float> margin;                // their logit margins (where the step kind reports one)
+    std::vector<unsigned long long> stamp;    // GPU time of each (ring path)
+    double dms = 0, ttft = -1;
+    long long n_steps = 0, n_drafted = 0, n_accepted = 0;
     const auto t0 = std::chrono::steady_clock::now();
-    if (tchunk == 1) {
-        if ((st = mi_decode(ctx, model, ids.data(), P, P, 0, out.data(), nullptr, mode, &pms))) die(ctx, "mi_decode (prefill)", st);
-    } else {
-        for (int i = 0; i < P; i += tchunk) {
-            const int mtok = P - i < tchunk ? P - i : tchunk;
-            float cms = 0;
-            if ((st = mi_verify(ctx, model, ids.data() + i, mtok, i, out.data() + i, nullptr, &cms))) die(ctx, "mi_verify (prefill)", st);
-            pms += cms;
+    auto since = [&]() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count(); };
+    if (spec && n_gen > 0) {
+        // lossless n-gram speculation: the library's loop over single-token steps and M-token verify passes
+        gen.resize(n_gen); margin.resize(n_gen);
+        int64_t stats[4] = {0, 0, 0, 0};
+        if ((st = mi_generate_spec(ctx, model, ids.data(), P, n_gen, ngmax, draftk, gen.data(), margin.data(), stats))) die(ctx, "mi_generate_spec", st);
+        dms = since(); ttft = dms / (n_gen > 0 ? n_gen : 1);
+        n_steps = stats[0]; n_drafted = stats[1]; n_accepted = stats[2];
+        for (int i = 0; i < n_gen; i++) printf("%d ", gen[i]);
+        printf("\n");
+        float minm = 1e30f; int mi = 0;
+        for (int i = 0; i < n_gen; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
+        fprintf(stderr, "minfer-%s decode: %d tok in %.1f ms = %.2f tok/s | first token after %.1f ms (prompt %d) | min logit margin %.4f at #%d | prompt included in the time; NGMAX=%d DRAFTK=%d\n",
+                tag, n_gen, dms, dms > 0 ? n_gen * 1e3 / dms : 0.0, ttft, P, minm, mi, ngmax, draftk);
+    } else if (n_gen > 0) {
+        // prompt: all but its last token, tchunk per weight pass (or one step per token); the last prompt token is the
+        // first step of the generation itself, so that every generated id comes with its margin
+        float pms = 0;
+        std::vector<int32_t> out(P > 0 ? P : 1);
+        if (P > 1) {
+            if (tchunk == 1) {
+                if ((st = mi_decode(ctx, model, ids.data(), P - 1, P - 1, 0, out.data(), nullptr, mode, &pms))) die(ctx, "mi_decode (prefill)", st);
+            } else {
+                for (int i = 0; i < P - 1; i += tchunk) {
+                    const int mtok = P - 1 - i < tchunk ? P - 1 - i : tchunk;
+                    float cms = 0;
+                    if ((st = mi_verify(ctx, model, ids.data() + i, mtok, i, out.data() + i, nullptr, &cms))) die(ctx, "mi_verify (prefill)", st);
+                    pms += cms;
+                }
+            }
+        }
+        fprintf(stderr, "minfer-%s prefill: %d tok in %.1f ms (%d per pass)\n", tag, P - 1, pms, tchunk);
+        gen.resize(n_gen); margin.resize(n_gen);
+        if (persistent) {
+            // one launch generates everything; the ids are printed as the kernel publishes them
+            mi_token_ring* ring = nullptr;
+            if ((st = mi_ring_create(ctx, n_gen, &ring))) die(ctx, "mi_ring_create", st);
+            if ((st = mi_decode_run(ctx, model, &ids[P - 1], 1, n_gen, P - 1, ring))) die(ctx, "mi_decode_run", st);
+            stamp.resize(n_gen);
+            int seen = 0;
+            const int32_t* rt; const float* rm; const uint64_t* rn;
+            for (;;) {
+                int cnt = 0;
+                mi_ring_peek(ring, &cnt, &rt, &rm, &rn);
+                for (; seen < cnt; seen++) {
+                    if (ttft < 0) ttft = since();
+                    gen[seen] = rt[seen]; margin[seen] = rm[seen]; stamp[seen] = rn[seen];
+                    printf("%d ", gen[seen]); fflush(stdout);
+                }
+                if (seen >= n_gen) break;
+                if (since() > 600e3) { fprintf(stderr, "minfer-%s: no token for ten minutes\n", tag); break; }
+                std::this_thread::sleep_for(std::chrono::microseconds(100));
+            }
+            if ((st = mi_ctx_sync(ctx))) die(ctx, "mi_decode_run", st);
+            mi_ring_destroy(ctx, ring);
+            printf("\n");
+            if (seen < n_gen) return 1;
+            dms = n_gen > 1 ? (double)(stamp[n_gen - 1] - stamp[0]) / 1e6 : 0.0;          // first to last token, on the GPU's clock
+        } else {
+            float ms = 0;
+            if ((st = mi_decode(ctx, model, &ids[P - 1], 1, n_gen, P - 1, gen.data(), nullptr, mode, &ms))) die(ctx, "mi_decode", st);
+            if ((st = mi_decode_margins(ctx, model, n_gen, margin.data()))) die(ctx, "mi_decode_margins", st);
+            ttft = since();
+            dms = n_gen > 1 ? ms * (n_gen - 1) / n_gen : 0.0;
+            for (int i = 0; i < n_gen; i++) printf("%d ", gen[i]);
+            printf("\n");
+        }
+        n_steps = n_gen;
+        float minm = 1e30f; int mi = 0;
+        for (int i = 0; i < n_gen; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
+        const int timed = n_gen - 1;
+        fprintf(stderr, "minfer-%s decode: %d tok in %.1f ms = %.2f tok/s | first token after %.1f ms (prompt %d) | min logit margin %.4f at #%d\n", tag, timed,
+                dms, dms > 0 ? timed * 1e3 / dms : 0.0, ttft, P, minm, mi);
+        if (timed > 0 && dms > 0) {
+            const double bytes = (double)c.q4_weight_bytes_per_token + (double)c.kv_bytes_per_position * (P + n_gen / 2.0);
+            fprintf(stderr, "minfer-%s: %.1f us/token, %.0f GB/s of weight + KV bytes (%.1f MB/token)\n", tag, dms * 1e3 / timed,
+                    bytes * timed / (dms * 1e-3) / 1e9, bytes / 1e6);
         }
     }
-    const double ttft = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    fprintf(stderr, "minfer-%s prefill: %d tok in %.1f ms (%d per pass)\n", tag, P, pms, tchunk);
-    std::vector<int32_t> gen;
-    int32_t next = out[P - 1];
-    gen.push_back(next);
-    float dms = 0;
-    if (n_gen > 1) {
-        std::vector<int32_t> more(n_gen - 1);
-        if ((st = mi_decode(ctx, model, &next, 1, n_gen - 1, P, more.data(), nullptr, mode, &dms))) die(ctx, "mi_decode", st);
-        gen.insert(gen.end(), more.begin(), more.end());
-    }
-    for (int i = 0; i < n_gen && i < (int)gen.size(); i++) printf("%d ", gen[i]);
-    printf("\n");
-    const int timed = n_gen - 1;
-    fprintf(stderr, "minfer-%s decode: %d tok in %.1f ms = %.2f tok/s | first token after %.1f ms (prompt %d)\n", tag, timed, dms,
-            dms > 0 ? timed * 1e3 / dms : 0.0, ttft, P);
-    if (timed > 0) {
-        const double bytes = (double)c.q4_weight_bytes_per_token + (double)c.kv_bytes_per_position * (P + n_gen / 2.0);
-        fprintf(stderr, "minfer-%s: %.1f us/token, %.0f GB/s of weight + KV bytes (%.1f MB/token)\n", tag, dms * 1e3 / timed,
-                bytes * timed / (dms * 1e-3) / 1e9, bytes / 1e6);
+    if (n_steps > 0)
+        fprintf(stderr, "minfer-%s: %lld generation steps, %.2f tokens/step | drafted %lld, accepted %lld (%.0f%%)%s\n", tag, n_steps,
+                (double)n_gen / n_steps, n_drafted, n_accepted, n_drafted ? 100.0 * n_accepted / n_drafted : 0.0, spec ? "" : " [SPEC=0]");
+    if (getenv("SEGMENTS") && !stamp.empty()) {                      // tok/s over consecutive windows: the slope with depth
+        const int w = atoi(getenv("SEGMENTS"));
+        for (int i = 0; w > 0 && i + w < n_gen; i += w)
+            fprintf(stderr, "  tokens %4d-%4d (pos %4d): %.1f tok/s\n", i, i + w, P + i, w * 1e9 / (double)(stamp[i + w] - stamp[i]));
     }
     if (env_int("PROFILE", 0)) {
         void* p = nullptr; int64_t nb = 0;
@@ -143,7 +221,7 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
             // barrier, 13 = step prologue, 14..16 = attention (q staging, scan, fold + merge), 18 / 19 = tile loops and
             // fold + epilogue of the per-layer GEMV phases
             const char* ph[6] = {"P1 QKV", "P2 attention", "P3 Wo", "P4 gate/up", "P5 down", "lm_head"};
-            const double steps = (double)(P + n_gen - 1 + env_int("WARMUP", 2));
+            const double steps = (double)(P + n_gen - 1 + env_int("WARMUP", 2));   // (with TCHUNK > 1 the prompt is not in the profile)
             auto us = [&](int k) { return pr[k] / 1e3 / steps; };
             double tot = 0;
             for (int k = 0; k < 6; k++) {
@@ -153,10 +231,12 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
             }
             fprintf(stderr, "  %-13s %8.1f %8.1f us/token (tile loops, fold + epilogue of P1 / P3 / P4 / P5)\n", "GEMV units", us(18), us(19));
             tot += us(18) + us(19);
-            fprintf(stderr, "  %-13s %8.1f us/token; step prologue %.1f; total %.1f us/position on CTA 0\n", "grid barrier", us(12), us(13),
+            fprintf(stderr, "  %-13s %8.1f us/token; step prologue %.1f; total %.1f us/position on the profiled CTA\n", "waits", us(12), us(13),
                     tot + us(12) + us(13));
         }
     }
+    if (getenv("MARGINS") && !margin.empty())
+        for (int i = 0; i < n_gen; i++) fprintf(stderr, "%d:%d:%.4f%c", i, gen[i], margin[i], i + 1 < n_gen ? ' ' : '\n');
     mi_model_free(ctx, model);
     mi_ctx_destroy(ctx);
     return 0;

@@ -2,11 +2,19 @@
 
 Each rank owns a contiguous range of the 32-row groups of the gate/up, down and lm_head
 matrices (nine tenths of the bytes; QKV and O are computed in full by every rank, so
-attention needs no exchange) and runs the decode phases through the C ABI
-(mi_decode_launch, asynchronous); after a sharded phase it all-reduces the buffer the phase wrote (NCCL through torch.distributed, on the same
-stream).  Entries a rank does not own are zero before the reduction, so the sum
-reproduces the single-GPU values bit for bit - the buffers are reduced as raw bytes,
-which is valid for every element type because x + 0 never carries.
+attention needs no exchange).  Two ways to run it:
+
+  * decode_persistent(): one cooperative launch per GPU for the whole generation.  What a
+    sharded phase produces leaves the kernel as tagged 8-byte words, stored into the local
+    exchange block and, over NVLink, into every other GPU's (peer pointers from CUDA IPC
+    handles, enable_peer_exchange()); consumers poll the words they need.  No collective,
+    no barrier, no host in the loop.
+  * step() / decode(): the phases through mi_decode_launch (asynchronous) with an exchange
+    after each sharded phase - an NCCL all-reduce of the vector the phase wrote (entries a
+    rank does not own are zero before the reduction, so the sum reproduces the single-GPU
+    words bit for bit: the buffers are reduced as raw bytes, x + 0 never carries), or the
+    library's own push kernel (mi_tp_exchange) - optionally captured into one CUDA graph
+    per token.
 
 The reference is single-GPU; this module has no counterpart in it.
 """
@@ -114,6 +122,8 @@ class TPDecoder:
     def decode(self, in_tokens, n_steps, pos0=0):
         """Like Model.decode: forced tokens first, then greedy; returns the greedy token after every step."""
         out = []
+        if pos0 < 0 or pos0 + n_steps > self.model.config.max_seq:
+            raise ValueError(f"positions {pos0}..{pos0 + n_steps - 1} exceed the KV cache of {self.model.config.max_seq}")
         if self.graph is not None:
             self.model.set_pos(pos0)
         for s in range(n_steps):

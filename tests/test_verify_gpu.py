@@ -112,7 +112,7 @@ def attention_f64(q, K, V, n_head, n_kv, hd, pos):
 
 
 @pytest.mark.parametrize("n_head,n_kv,hd", [(12, 2, 128), (14, 2, 64), (4, 2, 32)])
-@pytest.mark.parametrize("pos0,M", [(0, 1), (0, 16), (250, 9), (1017, 16), (3000, 4)])
+@pytest.mark.parametrize("pos0,M", [(0, 1), (0, 16), (250, 9), (1017, 16), (3000, 4), (8191, 1), (8191 - 15, 16), (32767, 1), (32767 - 15, 16)])
 def test_attn_splitkv_matches_float64_softmax(ctx, pkg, n_head, n_kv, hd, pos0, M):
     import torch
     rng = np.random.default_rng(pos0 * 31 + M + hd)
@@ -172,3 +172,32 @@ def test_graph_replay_matches_plain_launches(pkg, ctx, tiny):
     assert again_tok == want_tok
     assert np.array_equal(again.view(np.uint32), want.view(np.uint32))
     plain.free(); m.free()
+
+
+@pytest.mark.parametrize("context", [8192, 32768])
+def test_m_invariance_at_long_cached_contexts(ctx, pkg, tiny, context):
+    """The multi-token configuration's long contexts: the KV cache pre-filled with seeded N(0,1) fp16 for `context`
+    positions, then the same 16 drafted tokens scored with M = 1, 2, 4, 8, 16 tokens per weight pass starting at
+    position `context`.  Every token's logits must be the same bits whatever M is, and equal to the single-token decode
+    kernel's (whose chunked attention walks the same ranges)."""
+    import torch
+    g = gu.GgufReader(tiny)
+    V = g.config()["n_vocab"]
+    seq = [int(t) for t in np.random.default_rng(context).integers(0, V, 16)]
+    m = pkg.Model(ctx, tiny, context + 17)
+    gen = torch.Generator(device="cuda"); gen.manual_seed(context)
+    for name in ("kcache", "vcache"):
+        m.state_tensor(name).view(torch.float16).normal_(generator=gen)
+    torch.cuda.synchronize()
+    ref = None
+    for M in (1, 2, 4, 8, 16):
+        tok, lg = run_chunks(m, seq, M, V, pos0=context)          # each pass rewrites positions context.. with the same values
+        if ref is None:
+            ref, ref_tok = lg, tok
+        else:
+            assert tok == ref_tok, f"M={M}: greedy ids differ"
+            assert np.array_equal(lg.view(np.uint32), ref.view(np.uint32)), f"M={M}: logits differ from M=1 at context {context}"
+    dl = torch.zeros((16, V), dtype=torch.float32, device="cuda")
+    dtok, _ = m.decode(seq, 16, context, dl, pkg.DECODE_PERSISTENT)
+    assert dtok == ref_tok and np.array_equal(dl.cpu().numpy().view(np.uint32), ref.view(np.uint32)), "decode kernel differs from the M-token step"
+    m.free()
