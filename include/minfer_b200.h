@@ -160,11 +160,14 @@ MI_API int mi_block_isums_q4_q8(mi_ctx* ctx, const mi_weight* w, const int8_t* x
  * inside the library image: 65536 partial sums and 2048 counters, 528 KB that every
  * GPU which loads the library holds until the process exits.  A call whose stack
  * needs more (row groups x K-splits x 32 > 65536, or more than 2048 row groups
- * over the whole stack when it is K-split) returns MI_ERR_LIMIT and does nothing.
+ * over the whole stack when it is K-split) returns MI_ERR_LIMIT and does nothing
+ * (the shared scratch is not touched either).
  * It calls no cudaMalloc, cudaFree or other allocating routine.
  * The first call on a device looks the array's device address up (one symbol
- * query, with that device current); make that first call before any stream
- * capture begins.  All calls share the one array and it keeps whatever the last
+ * query, made with the context's device current; the calling thread's current
+ * device is put back before the call returns); make that first call before any
+ * stream capture begins.  First calls from several host threads are serialized
+ * by the library.  All calls share the one array and it keeps whatever the last
  * call left in it (the counters are cleared at the start of every call): two calls
  * that overlap on the GPU - different streams, or different contexts on the same
  * device - race on it and give wrong results; serialize them.

@@ -1,6 +1,7 @@
 // Standalone q4_0 x q8_0 GEMV over a stack of equal matrices (one launch), plus
 // the integer block-sum dump used for bit-exact parity checks.
 #include "gemv_core.cuh"
+#include <mutex>
 
 namespace mi {
 
@@ -76,6 +77,9 @@ static int launch_one(mi_ctx* ctx, const mi_weight* w, const GemvIO& io, int ksp
                              "the built-in scratch holds %zu and %zu", base_units, ks, (size_t)base_units * ks * 32, base_units,
                              fixed->part_cap, fixed->counter_cap);
         sc.part = fixed->part; sc.counters = fixed->counters;
+        // the counters this launch uses must read zero when the kernel starts, whatever an earlier call left behind;
+        // a call that is refused above, or that needs no K-split, leaves the shared scratch alone
+        MI_CUDA(ctx, cudaMemsetAsync(fixed->counters, 0, (size_t)base_units * sizeof(unsigned), ctx->stream));
     } else if (ks > 1) {
         int st = ensure_scratch(ctx, (size_t)base_units * ks * 32, (size_t)base_units);
         if (st != MI_OK) return st;
@@ -129,11 +133,20 @@ static int noalloc_scratch(mi_ctx* ctx, FixedScratch* out) {
     static double* part_addr[16] = {nullptr};
     static unsigned* counter_addr[16] = {nullptr};
     if (ctx->device < 0 || ctx->device >= 16) return set_error(ctx, MI_ERR_UNSUPPORTED, "no-allocation gemv: device index %d beyond 15", ctx->device);
+    static std::mutex lock;                             // two host threads may make their first call at once
+    std::lock_guard<std::mutex> hold(lock);
     if (!part_addr[ctx->device]) {
+        // a symbol's address is looked up on the current device: make the context's device current for the query and
+        // put the caller's device back afterwards
+        int prev = -1;
+        MI_CUDA(ctx, cudaGetDevice(&prev));
         MI_CUDA(ctx, cudaSetDevice(ctx->device));
         double* p = nullptr; unsigned* c = nullptr;
-        MI_CUDA(ctx, cudaGetSymbolAddress((void**)&p, g_noalloc_part));
-        MI_CUDA(ctx, cudaGetSymbolAddress((void**)&c, g_noalloc_counters));
+        const cudaError_t e1 = cudaGetSymbolAddress((void**)&p, g_noalloc_part);
+        const cudaError_t e2 = cudaGetSymbolAddress((void**)&c, g_noalloc_counters);
+        if (prev >= 0 && prev != ctx->device) cudaSetDevice(prev);
+        if (e1 != cudaSuccess || e2 != cudaSuccess)
+            return set_error(ctx, MI_ERR_CUDA, "no-allocation gemv: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
         part_addr[ctx->device] = p; counter_addr[ctx->device] = c;
     }
     out->part = part_addr[ctx->device]; out->counters = counter_addr[ctx->device];
@@ -154,8 +167,6 @@ extern "C" int mi_gemv_q4_q8_noalloc(mi_ctx* ctx, const mi_weight* w, const int8
     FixedScratch fx;
     int st = noalloc_scratch(ctx, &fx);
     if (st != MI_OK) return st;
-    // the counters must read zero when the kernel starts, whatever an earlier call left behind
-    MI_CUDA(ctx, cudaMemsetAsync(fx.counters, 0, kNoAllocCounters * sizeof(unsigned), ctx->stream));
     GemvIO io{xq_dev, reinterpret_cast<const __half*>(xd_dev), bias_dev, y_dev, (long long)w->rows, (int)w->rows, nullptr, ctx->d_err};
     switch (w->kb) {
         case 8: return launch_one<8, 8, 3, false>(ctx, w, io, 0, &fx);

@@ -88,9 +88,19 @@ public:
         if (align == 0) align = 32;
         size_t pos = (size_t)(cur_ - base_);
         size_t data_start = (pos + align - 1) / align * align;
+        if (data_start > size_) return "tensor data would start past the end of the file";
         for (auto& in : infos) {
-            size_t nb = in.t.nbytes();
-            if (data_start + in.off + nb > size_) return "tensor " + in.name + " runs past the end of the file";
+            // a crafted file must not get past these with wrapped arithmetic: every dimension positive and at most
+            // 2^31, the element count at most 2^40 (so the byte count cannot overflow), offset and size each checked
+            // against what is left of the file
+            unsigned long long elems = 1;
+            for (int64_t d : in.t.ne) {
+                if (d <= 0 || d > (1ll << 31)) return "tensor " + in.name + ": dimension out of range";
+                elems *= (unsigned long long)d;
+                if (elems > (1ull << 40)) return "tensor " + in.name + ": implausibly large";
+            }
+            const size_t nb = in.t.nbytes(), room = size_ - data_start;
+            if (in.off > room || nb > room - in.off) return "tensor " + in.name + " runs past the end of the file";
             in.t.data = base_ + data_start + in.off;
             tensors_.emplace(in.name, in.t);
         }

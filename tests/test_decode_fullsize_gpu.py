@@ -76,13 +76,12 @@ def test_fullsize_engines_and_m_token_step_agree_bit_for_bit(ctx, pkg, tmp_path,
     m.free()
 
 
-def test_config2_window_sampled_against_the_oracle(ctx, pkg, tmp_path):
-    """The benchmark configuration itself: 1.5B shape, 64-token seeded prompt, 128 generated tokens.  The GPU runs the
-    whole window; the oracle (about a second and a half per token on the host) follows the GPU's tokens teacher-forced
-    through all 191 positions only for its KV cache... which is the cost, so it is bounded: the oracle walks the first
-    64 + 17 positions fully (prompt, then every generated position up to the 17th) and the test compares greedy ids at
-    each and logits at the last prompt position and every 16th generated one.  The remaining generated positions are
-    covered by engine-vs-engine bit equality (persistent kernel == kernel sequence) over the full window."""
+def test_config2_window_against_the_oracle(ctx, pkg, tmp_path):
+    """The benchmark configuration itself: 1.5B shape, 64-token seeded prompt, 128 generated tokens, KV cache for 4096
+    positions.  The GPU generates the window; the oracle then follows the GPU's tokens teacher-forced through all 191
+    positions (a tenth of a second each on the test machine) and must predict the same id at every one; logits are
+    compared at the last prompt position, at every 16th generated position and at the last.  The kernel-sequence
+    engine must give the persistent kernel's bits over the whole window."""
     import torch
     path = gu.make_synthetic(tmp_path / "m.gguf", "1.5b", seed=20251)
     g = gu.GgufReader(path)
@@ -99,11 +98,10 @@ def test_config2_window_sampled_against_the_oracle(ctx, pkg, tmp_path):
     lg2 = torch.zeros((n_steps, V), dtype=torch.float32, device="cuda")
     pred2, _ = m2.decode(seq, n_steps, 0, lg2, pkg.DECODE_PER_PHASE)
     assert pred2 == pred and torch.equal(lg.view(torch.int32), lg2.view(torch.int32)), "kernel sequence differs from the persistent kernel over the window"
-    n_orc = 64 + 17
-    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n_orc + 1)
-    check = {63, 64 + 16 - 1, n_orc - 1}
+    orc = ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=n_steps + 1)
+    check = {63} | {63 + 16 * k for k in range(1, 8)} | {n_steps - 1}
     worst = 0.0
-    for s in range(n_orc):
+    for s in range(n_steps):
         tok, lo, _ = orc.forward(seq[s], want_logits=s in check)
         assert tok == pred[s], f"greedy id differs from the oracle at position {s}"
         if s in check:

@@ -42,8 +42,13 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice(ctx, rows, cols, 
     want = ref.cpu().numpy()
     for call in range(2):                                   # second call: scratch holds the first call's leftovers
         y = torch.full((count, rows), float("nan"), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         ctx.gemv_q4_q8_noalloc(w, xq, xd, y, bias=bias)
         ctx.sync()
+        # what the entry point exists for: the device's free memory is the same after the call (these shapes are K-split,
+        # the regular entry point grows a scratch buffer for them)
+        assert torch.cuda.mem_get_info()[0] == free_before, f"call {call} changed the free device memory"
         got = y.cpu().numpy()
         # the tolerance of the GEMV parity tests (1e-3 of the output scale); both paths sum in
         # double and round once, so in practice the bits are equal
@@ -70,3 +75,15 @@ def test_noalloc_entry_point_refuses_what_does_not_fit(ctx, pkg):
         ctx.gemv_q4_q8_noalloc(w, xq, xd, y)
     assert e.value.status == 8 and "built-in scratch" in str(e.value)
     ctx.sync()
+    # the other limit: few enough row groups for the counters, but groups x K-splits x 32 partial sums beyond 65536
+    groups = 1100
+    ks = min(-(-(2 * ctx.sm_count * 8) // groups), 2)        # the kernel's split for this stack, capped by its two tiles per row group
+    if ks > 1 and groups * ks * 32 > 65536:
+        rows2 = 32 * groups
+        raw2 = np.zeros(rows2 * (cols // 32) * 18, dtype=np.uint8)
+        w2 = ctx.upload_q4_0(raw2, rows2, cols, 1)
+        y2 = torch.zeros((1, rows2), dtype=torch.float32, device="cuda")
+        with pytest.raises(pkg.MinferError) as e2:
+            ctx.gemv_q4_q8_noalloc(w2, xq, xd, y2)
+        assert e2.value.status == 8 and "partial sums" in str(e2.value)
+        ctx.sync()
