@@ -571,23 +571,31 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
 //       + the projection output published as tagged fp32 words at addw   [if addw]
 //   h = x;  the first GEMV CTA also commits x to global memory;
 //   xq_s / xs_s = q8_0( x * (1/sqrt(float(ss/n) + eps)) * w )   (src/cpu_infer.cpp:40-46).
-// Warp w owns the 32-element blocks w, w+8, ...; lane = element, so a thread holds at most NB values and everything
-// stays in registers.  All loads (vector, tagged words, norm weights) are requested before anything waits on them, and
-// the NB quantizer chains of a warp are interleaved so their latencies overlap (a loop over the blocks, quantizing one
-// after the other from shared memory, has a fifth of the instructions and measured 30 % slower).  Sum of squares in
-// double (every x*x is exact there).
-template <int NB>
+// Two thread mappings.  Gathering (tagged words in, residual add, sum of squares): warp w owns the 32-element blocks
+// w, w+8, ...; lane = element, so every warp-wide load of tagged words is one contiguous 256-byte run and all of a
+// thread's words are requested before anything waits on them.  Quantizing (after the sum of squares is known): EPL
+// consecutive elements per thread, 32/EPL threads per q8_0 block, read back from shared memory; the block maximum and the
+// block sum fold over 32/EPL lanes with log2(32/EPL) shuffles.  (One element per thread and warp-wide REDUX reductions,
+// twelve per warp at the 1.5B shape, measured 1500 cycles for the quantizer alone: the reduction unit, not the
+// arithmetic, set the time.)  Sum of squares in double (every x*x is exact there).
+template <int NB, int EPL>
 __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token,
                                                 const unsigned long long* addw, unsigned tag, float* commit, const float* __restrict__ w,
                                                 int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
+    constexpr int LPB = 32 / EPL;                        // lanes per block while quantizing
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nb = E / 32;
-    float x[NB], wv[NB];
+    // the norm weights of the quantizing pass: requested now, used after the barrier
+    const int qt_b = tid / LPB, qt_e0 = tid * EPL;
+    const bool qlive = qt_b < nb;
+    float wv[EPL];
+    #pragma unroll
+    for (int i = 0; i < EPL; i++) wv[i] = __ldg(w + (qlive ? qt_e0 : 0) + i);
+    float x[NB];
     unsigned valid = 0;
     #pragma unroll
     for (int k = 0; k < NB; k++) {
         const int b = min(warp + k * DNW, nb - 1), e = b * 32 + lane;      // clamped: every address is valid
         if (warp + k * DNW < nb) valid |= 1u << k;
-        wv[k] = __ldg(w + e);
         x[k] = embed ? 0.f : (gsrc ? __ldcg(gsrc + e) : h_s[e]);
     }
     if (embed) {                                                 // layer 0: the embedding row, value (nibble - 8) * d (src/gguf.h:94-102)
@@ -613,13 +621,12 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     double ss = 0.0;
     #pragma unroll
     for (int k = 0; k < NB; k++) {
-        if (!(valid >> k & 1u)) x[k] = 0.f;                      // a clamped duplicate: contributes nothing
-        else {
+        if (valid >> k & 1u) {
             const int e = (warp + k * DNW) * 32 + lane;
             h_s[e] = x[k];
             if (commit && (int)blockIdx.x == P.attn_ctas) __stcg(commit + e, x[k]);
+            const double xd = x[k]; ss = __fma_rn(xd, xd, ss);
         }
-        const double xd = x[k]; ss = __fma_rn(xd, xd, ss);
     }
     #pragma unroll
     for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
@@ -632,24 +639,36 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
     const float mean = __double2float_rn(__ddiv_rn(tot, (double)E));
     const float scale = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, eps)));
-    float v[NB], a[NB]; int q[NB], sq[NB];
-    #pragma unroll
-    for (int k = 0; k < NB; k++) { v[k] = __fmul_rn(__fmul_rn(x[k], scale), wv[k]); a[k] = fabsf(v[k]); }
-    #pragma unroll
-    for (int k = 0; k < NB; k++) a[k] = warp_max_nonneg(a[k]);
-    #pragma unroll
-    for (int k = 0; k < NB; k++) {
-        const float inv = a[k] > 0.f ? __fdiv_rn(127.f, a[k]) : 0.f;
-        q[k] = __float2int_rn(__fmul_rn(v[k], inv)); sq[k] = q[k];
-    }
-    #pragma unroll
-    for (int k = 0; k < NB; k++) sq[k] = warp_sum_int(sq[k]);
-    #pragma unroll
-    for (int k = 0; k < NB; k++) {
-        const int b = warp + k * DNW;
-        if (b < nb) {
-            xq_s[b * 32 + lane] = (int8_t)q[k];
-            if (lane == 0) xs_s[b] = make_float2(__half2float(__float2half_rn(__fdiv_rn(a[k], 127.f))), __int2float_rn(8 * sq[k]));
+    // quantize: this thread's EPL elements of block qt_b (vectors beyond 256 * EPL elements: further rounds)
+    for (int t = tid; (t & ~31) / LPB < nb; t += DNT) {              // warp-uniform trip count: the folds below are warp-wide
+        const int b = t / LPB;
+        const bool live = b < nb;
+        const int e0 = live ? t * EPL : 0;                            // a lane past the vector computes on block 0 and stores nothing
+        float v[EPL], a = 0.f;
+        #pragma unroll
+        for (int i = 0; i < EPL; i++) {
+            const float wi = t == tid ? wv[i] : __ldg(w + e0 + i);
+            v[i] = __fmul_rn(__fmul_rn(h_s[e0 + i], scale), wi); a = fmaxf(a, fabsf(v[i]));
+        }
+        #pragma unroll
+        for (int o = 1; o < LPB; o <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+        int q[EPL], sq = 0;
+        #pragma unroll
+        for (int i = 0; i < EPL; i++) { q[i] = __float2int_rn(__fmul_rn(v[i], inv)); sq += q[i]; }
+        #pragma unroll
+        for (int o = 1; o < LPB; o <<= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (live) {
+            if constexpr (EPL >= 4) {
+                #pragma unroll
+                for (int i = 0; i < EPL; i += 4)
+                    *reinterpret_cast<unsigned*>(xq_s + e0 + i) = (unsigned)(q[i] & 0xff) | ((unsigned)(q[i + 1] & 0xff) << 8) |
+                                                                  ((unsigned)(q[i + 2] & 0xff) << 16) | ((unsigned)(q[i + 3] & 0xff) << 24);
+            } else {
+                #pragma unroll
+                for (int i = 0; i < EPL; i++) xq_s[e0 + i] = (int8_t)q[i];
+            }
+            if ((t % LPB) == 0) xs_s[b] = make_float2(__half2float(__float2half_rn(__fdiv_rn(a, 127.f))), __int2float_rn(8 * sq));
         }
     }
     prof_mark(P, 25);
@@ -661,18 +680,19 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
 #define MI_NORM_ARGS const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token, const unsigned long long* addw, unsigned tag, \
                      float* commit, const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s
 #define MI_NORM_PASS P, h_s, gsrc, embed, token, addw, tag, commit, w, E, eps, red, xq_s, xs_s
-static __device__ __noinline__ bool stage_norm_q8_wide(MI_NORM_ARGS) {
-    if ((E / 32 + DNW - 1) / DNW <= 16) return stage_norm_q8_t<16>(MI_NORM_PASS);
-    return stage_norm_q8_t<32>(MI_NORM_PASS);
+// blocks per warp while gathering (NB) and elements per thread while quantizing (EPL: the largest of 8, 4, 2, 1 with
+// which 256 threads cover the vector, 8 in several rounds beyond 2048 elements)
+static __device__ __noinline__ bool stage_norm_q8_rare(MI_NORM_ARGS) {
+    if (E <= 256) return stage_norm_q8_t<1, 1>(MI_NORM_PASS);
+    if (E <= 512) return stage_norm_q8_t<2, 2>(MI_NORM_PASS);
+    if (E <= 1024) return stage_norm_q8_t<4, 4>(MI_NORM_PASS);
+    if (E <= 4096) return stage_norm_q8_t<16, 8>(MI_NORM_PASS);
+    return stage_norm_q8_t<32, 8>(MI_NORM_PASS);
 }
 __device__ __forceinline__ bool stage_norm_q8u(MI_NORM_ARGS) {
-    const int per_warp = (E / 32 + DNW - 1) / DNW;
-    if (per_warp <= 4) return stage_norm_q8_t<4>(MI_NORM_PASS);
-    if (per_warp <= 6) return stage_norm_q8_t<6>(MI_NORM_PASS);
-    if (per_warp <= 8) return stage_norm_q8_t<8>(MI_NORM_PASS);
-    return stage_norm_q8_wide(MI_NORM_PASS);
+    if (E > 1024 && E <= 2048) return stage_norm_q8_t<8, 8>(MI_NORM_PASS);
+    return stage_norm_q8_rare(MI_NORM_PASS);
 }
-
 
 // A q8_0 vector published as tagged words by other CTAs -> shared memory: int8 values, and per block {fp32 of the fp16
 // scale, float(8 * sum of the block's values)}.  Thread t takes the 16-byte word pairs t, t + 256, ...; all of a
