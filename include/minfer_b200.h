@@ -315,6 +315,25 @@ MI_API int mi_generate_spec(mi_ctx* ctx, mi_model* model, const int32_t* prompt_
 /* Logit margins of the first n tokens of the last mi_verify pass on this model. */
 MI_API int mi_verify_margins(mi_ctx* ctx, mi_model* model, int n, float* margins_host);
 
+/* ---- batched decode of independent sequences ------------------------------------- */
+
+/* A batch object owns n_slots KV-cache slabs of max_seq positions each (fp16, laid out like the
+ * model's own cache) for sequences decoded together.  mi_batch_step runs ONE decode step for n
+ * of them: sequence i has its current token tokens_host[i] at position positions_host[i] of slab
+ * slots_host[i] (distinct slots within a call).  Up to 16 sequences share one pass over the
+ * weights as columns of the M-token step (tcgen05 GEMM, one attention CTA set per column over
+ * that column's own slab); more sequences run further passes.  Every column is processed exactly
+ * as if it were alone: out_tokens_host[i] and logits_dev[i][n_vocab] are the bits a batch-1 decode
+ * of that sequence gives.  Prompts enter the same way, one token per step and sequence (or through
+ * mi_verify on the model's own cache for a single sequence).  The reference has no independent-
+ * sequence batching (README.md:54); its closest code is gemv_dp4a_batch<T>
+ * (src/cuda_infer.cu:183-222). */
+typedef struct mi_batch mi_batch;
+MI_API int mi_batch_create(mi_ctx* ctx, mi_model* model, int n_slots, int max_seq, mi_batch** out);
+MI_API int mi_batch_free(mi_ctx* ctx, mi_batch* batch);
+MI_API int mi_batch_step(mi_ctx* ctx, mi_batch* batch, int n, const int32_t* tokens_host, const int32_t* slots_host,
+                         const int32_t* positions_host, int32_t* out_tokens_host, float* logits_dev, float* elapsed_ms);
+
 /* Split-KV causal attention with grouped queries for M (1..16) consecutive query positions
  * (replaces attn_partial + attn_combine, src/cuda_infer.cu:650-702, and mega's attention + combine,
  * src/mega.cu:414-521, 705-741).  q_dev: [M][n_head * head_dim] fp32 in natural dimension order

@@ -76,6 +76,9 @@ SIGNATURES = {
     "mi_verify": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, C.POINTER(C.c_float)]),
     "mi_generate_spec": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "mi_verify_margins": (_i32, [_vp, _vp, _i32, _vp]),
+    "mi_batch_create": (_i32, [_vp, _vp, _i32, _i32, C.POINTER(_vp)]),
+    "mi_batch_free": (_i32, [_vp, _vp]),
+    "mi_batch_step": (_i32, [_vp, _vp, _i32, _vp, _vp, _vp, _vp, _vp, C.POINTER(C.c_float)]),
     "mi_attn_splitkv": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "mi_tp_partition": (None, [_i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_i32)]),
     "mi_model_load_gguf_tp": (_i32, [_vp, C.c_char_p, _i32, _i32, _i32, C.POINTER(_vp)]),
@@ -248,6 +251,37 @@ class Weight:
     def free(self):
         if self.h and self.ctx.h:
             self.ctx.lib.mi_weight_free(self.ctx.h, self.h)
+        self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Batch:
+    """KV slabs for sequences decoded together, one step per call: wraps mi_batch."""
+
+    def __init__(self, model, n_slots, max_seq):
+        self.ctx, self.model = model.ctx, model
+        h = _vp()
+        self.ctx.check(self.ctx.lib.mi_batch_create(self.ctx.h, model.h, n_slots, max_seq, C.byref(h)), "mi_batch_create")
+        self.h = h
+
+    def step(self, tokens, slots, positions, logits=None):
+        """One decode step of len(tokens) sequences; returns (next greedy token of each, device milliseconds)."""
+        import numpy as np
+        t = np.ascontiguousarray(tokens, dtype=np.int32); s = np.ascontiguousarray(slots, dtype=np.int32)
+        p = np.ascontiguousarray(positions, dtype=np.int32)
+        out = np.empty(t.size, dtype=np.int32)
+        ms = C.c_float(0)
+        self.ctx.check(self.ctx.lib.mi_batch_step(self.ctx.h, self.h, t.size, _ptr(t), _ptr(s), _ptr(p), _ptr(out), _ptr(logits), C.byref(ms)), "mi_batch_step")
+        return out.tolist(), ms.value
+
+    def free(self):
+        if self.h and self.ctx.h:
+            self.ctx.lib.mi_batch_free(self.ctx.h, self.h)
         self.h = None
 
     def __del__(self):

@@ -67,9 +67,13 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
 }
 
 // RoPE on the packed (pair-adjacent) q and k rows of every token, fp16 K / V into the cache
-__global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, const int* pos0_dev, float* qkv, int stride) {
+// (pos_arr / slot_arr, when given: token m sits at position pos_arr[m] of the sequence whose cache is slab slot_arr[m] -
+// independent sequences sharing one weight pass; otherwise consecutive positions pos0 + m of one sequence)
+__global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, const int* pos0_dev, float* qkv, int stride,
+                                                  const int* pos_arr, const int* slot_arr, long long slab_stride) {
     pdl_launch_dependents(); pdl_wait_prior();
-    const int m = blockIdx.x, pos = __ldg(pos0_dev) + m, HD = P.HD, nq = P.NH * HD;
+    const int m = blockIdx.x, pos = pos_arr ? __ldg(pos_arr + m) : __ldg(pos0_dev) + m, HD = P.HD, nq = P.NH * HD;
+    const size_t slab = slot_arr ? (size_t)__ldg(slot_arr + m) * (size_t)slab_stride : 0;
     float* v = qkv + (size_t)m * stride;
     for (int pr = threadIdx.x; pr < (nq + P.KVD) / 2; pr += blockDim.x) {
         const int p = 2 * pr, within = (p < nq ? p : p - nq) % HD, i = within >> 1;
@@ -82,14 +86,15 @@ __global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, c
     __syncthreads();
     for (int e = threadIdx.x; e < P.KVD; e += blockDim.x) {
         const int kvh = e / HD, d = e % HD, pk = d < HD / 2 ? 2 * d : 2 * (d - HD / 2) + 1;
-        P.kc[((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + kvh * HD + pk]);
-        P.vc[((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + P.KVD + e]);
+        P.kc[slab + ((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + kvh * HD + pk]);
+        P.vc[slab + ((size_t)l * P.max_seq + pos) * P.KVD + e] = __float2half_rn(v[nq + P.KVD + e]);
     }
 }
 
 // attention of M queries: blockIdx.y = query; every query runs the decode kernel's attention over its own causal range
 template <int HD, int G, bool QNAT>
-__global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, const int* pos0_dev, int pos0_val, long long q_stride) {
+__global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ DecodeParams P, int l, const int* pos0_dev, int pos0_val, long long q_stride,
+                                                       const int* pos_arr, const int* slot_arr, long long slab_stride) {
     extern __shared__ __align__(128) uint8_t smem[];
     pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.y, nq = P.NH * HD;
@@ -99,7 +104,8 @@ __global__ void __launch_bounds__(DNT, 1) vf_attention(const __grid_constant__ D
     Q.attn_part = P.attn_part + (size_t)m * P.NH * P.max_chunks * (HD + 2);
     Q.attn_cnt = P.attn_cnt + (size_t)m * P.NH;
     Q.prof = nullptr;
-    const int pos = (pos0_dev ? __ldg(pos0_dev) : pos0_val) + m;
+    const int pos = pos_arr ? __ldg(pos_arr + m) : (pos0_dev ? __ldg(pos0_dev) : pos0_val) + m;
+    if (slot_arr) { const size_t slab = (size_t)__ldg(slot_arr + m) * (size_t)slab_stride; Q.kc = P.kc + slab; Q.vc = P.vc + slab; }
     if (pos + 1 <= kShortAttnMax) attention_short<HD, G, false, QNAT>(Q, l, pos, smem);
     else if (pos + 1 <= kPerHeadAttnMax) attention_phase<HD, 1, G, false, QNAT>(Q, l, pos, smem);
     else attention_phase<HD, G, G, false, QNAT>(Q, l, pos, smem);
@@ -178,15 +184,16 @@ size_t attn_smem_bytes(int HD, int G) {
 }
 
 template <bool QNAT>
-int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid, int M, int l, const int* pos0_dev, int pos0, long long q_stride) {
-    void (*kern)(DecodeParams, int, const int*, int, long long) = nullptr;
+int launch_attention(mi_ctx* ctx, const DecodeParams& P, int HD, int G, int grid, int M, int l, const int* pos0_dev, int pos0, long long q_stride,
+                     const int* pos_arr = nullptr, const int* slot_arr = nullptr, long long slab_stride = 0) {
+    void (*kern)(DecodeParams, int, const int*, int, long long, const int*, const int*, long long) = nullptr;
     #define MI_PICK(hd, g) if (HD == hd && G == g) kern = vf_attention<hd, g, QNAT>;
     MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
     #undef MI_PICK
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "attention: head_dim %d with %d query heads per kv head is not instantiated", HD, G);
     const size_t smem = attn_smem_bytes(HD, G);
     MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MI_CUDA(ctx, launch_k(ctx->pdl, kern, dim3(grid, M), dim3(DNT), smem, ctx->stream, P, l, pos0_dev, pos0, q_stride));
+    MI_CUDA(ctx, launch_k(ctx->pdl, kern, dim3(grid, M), dim3(DNT), smem, ctx->stream, P, l, pos0_dev, pos0, q_stride, pos_arr, slot_arr, slab_stride));
     return MI_OK;
 }
 
@@ -222,10 +229,16 @@ namespace {
 // regime: how many CTAs per query the attention launch needs - 0: every query sees <= 256 positions (one CTA per head),
 // 1: <= 1024 (up to four chunks per head), 2: beyond (the whole grid).  Launching the full grid for eight queries of a
 // short context means eight waves of CTAs that exit at once; the chunking of a query does not depend on the regime.
-int enqueue_pass(mi_ctx* ctx, mi_model* m, int M, int regime) {
+// (bv: the tokens are one step each of independent sequences - positions, cache slabs and the cache itself come from it)
+struct BatchView { const int* pos; const int* slot; __half* kc; __half* vc; int max_seq; long long slab_stride; };
+
+int enqueue_pass(mi_ctx* ctx, mi_model* m, int M, int regime, const BatchView* bv = nullptr) {
     VerifyBufs& b = m->vb;
     const int E = m->E, FF = m->FF, L = m->L, V = m->V;
     DecodeParams P = m->P;
+    if (bv) { P.kc = bv->kc; P.vc = bv->vc; P.max_seq = bv->max_seq; }
+    const int* pos_arr = bv ? bv->pos : nullptr; const int* slot_arr = bv ? bv->slot : nullptr;
+    const long long slab_stride = bv ? bv->slab_stride : 0;
     P.qkv_out = b.qkv; P.att = b.att; P.att_q = b.att_q; P.att_d = b.att_d; P.attn_part = b.attn_part; P.attn_cnt = b.attn_cnt;
     P.prof = nullptr;
     const std::vector<LayerPtrs>& lp = m->layer_ptrs;
@@ -245,8 +258,9 @@ int enqueue_pass(mi_ctx* ctx, mi_model* m, int M, int regime) {
                               (const float*)(l == 0 ? nullptr : b.Y), E, lp[l].attn_norm, b.xq, b.xd));
         // the GEMM packs its output at the matrix's own row count: y[m * rows + r]
         if ((st = mi_gemm_q4_q8(ctx, wqkv, b.xq, reinterpret_cast<const uint16_t*>(b.xd), M, lp[l].bqkv, b.qkv))) return st;
-        MI_CUDA(ctx, launch_k(pdl, vf_rope_kv, dim3(M), dim3(DNT), 0, ctx->stream, P, l, (const int*)b.pos0, b.qkv, (int)wqkv->rows));
-        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, attn_grid, M, l, b.pos0, 0, wqkv->rows))) return st;
+        MI_CUDA(ctx, launch_k(pdl, vf_rope_kv, dim3(M), dim3(DNT), 0, ctx->stream, P, l, (const int*)b.pos0, b.qkv, (int)wqkv->rows, pos_arr, slot_arr,
+                              slab_stride));
+        if ((st = launch_attention<false>(ctx, P, m->HD, m->G, attn_grid, M, l, b.pos0, 0, wqkv->rows, pos_arr, slot_arr, slab_stride))) return st;
         if ((st = mi_gemm_q4_q8(ctx, wo, b.att_q, reinterpret_cast<const uint16_t*>(b.att_d), M, nullptr, b.Y))) return st;
         MI_CUDA(ctx, launch_k(pdl, vf_norm_quant, dim3(M), dim3(DNT), nsm, ctx->stream, P, (const int*)b.tokens, false, b.X, (const float*)b.Y, E,
                               lp[l].ffn_norm, b.xq, b.xd));
@@ -367,4 +381,88 @@ extern "C" int mi_attn_splitkv(mi_ctx* ctx, const float* q_dev, const uint16_t* 
     const int lp_max = pos0 + M;
     const int agrid = lp_max <= 256 ? std::min(grid, n_head) : lp_max <= kPerHeadAttnMax ? std::min(grid, n_head * (kPerHeadAttnMax / 256)) : grid;
     return launch_attention<true>(ctx, P, head_dim, G, agrid, M, 0, nullptr, pos0, NQ);
+}
+
+
+// ---- batched decode of independent sequences -------------------------------------------------------------
+// One step of up to B sequences per call: the current token of each goes through ONE pass over the weights as a column
+// of the M-token step (sixteen columns per pass; larger batches run several passes), with its own position and its
+// own slab of a KV cache that belongs to the batch object.  Every column is processed exactly as if it were alone, so
+// a sequence's ids and logits are the bits of its batch-1 run, whatever else shares the pass.  The reference serves one
+// sequence at a time (README.md:54); the closest code is gemv_dp4a_batch<T> (src/cuda_infer.cu:183-222).
+struct mi_batch {
+    mi_model* model = nullptr;
+    int n_slots = 0, max_seq = 0;
+    __half* kc = nullptr; __half* vc = nullptr;       // [slot][layer][max_seq][KVD]
+    int* d_meta = nullptr;                              // [3][16]: tokens, positions, slots of the running pass
+    long long slab_stride = 0;
+};
+
+extern "C" int mi_batch_create(mi_ctx* ctx, mi_model* m, int n_slots, int max_seq, mi_batch** out) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!m || !out || n_slots < 1 || max_seq < 1) return set_error(ctx, MI_ERR_INVALID, "batch_create: bad argument");
+    if (m->tp_world != 1) return set_error(ctx, MI_ERR_UNSUPPORTED, "batch_create: the M-token step runs on an unsharded model");
+    *out = nullptr;
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    mi_batch* b = new (std::nothrow) mi_batch();
+    if (!b) return set_error(ctx, MI_ERR_NOMEM, "batch_create: host allocation failed");
+    b->model = m; b->n_slots = n_slots; b->max_seq = max_seq;
+    b->slab_stride = (long long)m->L * max_seq * m->KVD;
+    const size_t bytes = (size_t)n_slots * (size_t)b->slab_stride * sizeof(__half);
+    if (cudaMalloc(&b->kc, bytes) != cudaSuccess || cudaMalloc(&b->vc, bytes) != cudaSuccess || cudaMalloc(&b->d_meta, 3 * 16 * sizeof(int)) != cudaSuccess) {
+        cudaFree(b->kc); cudaFree(b->vc); cudaFree(b->d_meta); delete b;
+        return set_error(ctx, MI_ERR_NOMEM, "batch_create: %d KV slabs of %zu bytes do not fit", n_slots, bytes / n_slots);
+    }
+    *out = b;
+    return MI_OK;
+}
+
+extern "C" int mi_batch_free(mi_ctx* ctx, mi_batch* b) {
+    if (!b) return MI_OK;
+    if (ctx) { cudaSetDevice(ctx->device); cudaStreamSynchronize(ctx->stream); }
+    cudaFree(b->kc); cudaFree(b->vc); cudaFree(b->d_meta);
+    delete b;
+    return MI_OK;
+}
+
+extern "C" int mi_batch_step(mi_ctx* ctx, mi_batch* b, int n, const int32_t* tokens_host, const int32_t* slots_host, const int32_t* positions_host,
+                             int32_t* out_tokens_host, float* logits_dev, float* elapsed_ms) {
+    if (!ctx) return MI_ERR_INVALID;
+    if (!b || !tokens_host || !slots_host || !positions_host || n < 1) return set_error(ctx, MI_ERR_INVALID, "batch_step: bad argument");
+    mi_model* m = b->model;
+    for (int i = 0; i < n; i++) {
+        if (tokens_host[i] < 0 || tokens_host[i] >= m->V) return set_error(ctx, MI_ERR_INVALID, "batch_step: token id %d out of range", tokens_host[i]);
+        if (slots_host[i] < 0 || slots_host[i] >= b->n_slots) return set_error(ctx, MI_ERR_INVALID, "batch_step: slot %d of %d", slots_host[i], b->n_slots);
+        if (positions_host[i] < 0 || positions_host[i] >= b->max_seq)
+            return set_error(ctx, MI_ERR_LIMIT, "batch_step: position %d outside the KV slab of %d", positions_host[i], b->max_seq);
+        for (int j = 0; j < i; j++)
+            if (slots_host[j] == slots_host[i]) return set_error(ctx, MI_ERR_INVALID, "batch_step: slot %d appears twice in one step", slots_host[i]);
+    }
+    MI_CUDA(ctx, cudaSetDevice(ctx->device));
+    int st;
+    if ((st = ensure_bufs(ctx, m))) return st;
+    VerifyBufs& vb = m->vb;
+    MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
+    for (int i0 = 0; i0 < n; i0 += VMAX) {
+        const int M = std::min(VMAX, n - i0);
+        int32_t meta[3 * 16] = {};
+        int lp_max = 0;
+        for (int i = 0; i < M; i++) {
+            meta[i] = tokens_host[i0 + i]; meta[16 + i] = positions_host[i0 + i]; meta[32 + i] = slots_host[i0 + i];
+            lp_max = std::max(lp_max, positions_host[i0 + i] + 1);
+        }
+        MI_CUDA(ctx, cudaMemcpyAsync(b->d_meta, meta, sizeof meta, cudaMemcpyHostToDevice, ctx->stream));
+        MI_CUDA(ctx, cudaMemcpyAsync(vb.tokens, b->d_meta, (size_t)M * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        const BatchView bv{b->d_meta + 16, b->d_meta + 32, b->kc, b->vc, b->max_seq, b->slab_stride};
+        const int regime = lp_max <= 256 ? 0 : lp_max <= kPerHeadAttnMax ? 1 : 2;
+        if ((st = enqueue_pass(ctx, m, M, regime, &bv))) return st;
+        if (logits_dev) MI_CUDA(ctx, cudaMemcpyAsync(logits_dev + (size_t)i0 * m->V, vb.logits, (size_t)M * m->V * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        if (out_tokens_host) MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host + i0, vb.out, (size_t)M * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (i0 + VMAX < n) MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));       // the pageable meta block is reused by the next pass
+    }
+    MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
+    st = mi_ctx_sync(ctx);
+    if (st != MI_OK) return st;
+    if (elapsed_ms) MI_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, m->ev0, m->ev1));
+    return MI_OK;
 }
