@@ -528,6 +528,91 @@ def run_ours(args, rank, world, local_rank):
         }))
         return
 
+    if args.workload == "batch":
+        # batched decode of independent sequences (the batched configuration: 3B shape, batch 1 / 16 / 64, 128-token seeded
+        # prompts, context <= 4096): every sequence advances one token per step; up to 16 share a weight pass
+        global MODEL_PRESET
+        MODEL_PRESET = "3b"
+        if rank == 0:
+            ensure_model()
+        barrier()
+        model = pkg.Model(ctx, ensure_model(), 16)
+        cfg = model.config
+        K = max(4, min(args.steps, 64))
+        n_prompt = 128
+        res = {}
+        for B in (1, 16, 64):
+            rng = np.random.default_rng(100 + B)
+            prompts = rng.integers(0, cfg.n_vocab, (B, n_prompt)).tolist()
+            bt = pkg.Batch(model, B, n_prompt + warmup + K + 1)
+            slots = list(range(B))
+            cur = [p[0] for p in prompts]
+            for pos in range(n_prompt + warmup):                   # untimed: the prompts, one token per step and sequence, then W steps
+                out, _ = bt.step(cur, slots, [pos] * B)
+                cur = [prompts[i][pos + 1] if pos + 1 < n_prompt else out[i] for i in range(B)]
+            torch.cuda.synchronize()
+            tot = 0.0
+            first = None
+            for s_ in range(K):
+                out, ms = bt.step(cur, slots, [n_prompt + warmup + s_] * B)
+                cur = out; tot += ms
+                first = first or out[:4]
+            res[B] = (tot / K, first)
+            bt.free()
+        if rank != 0:
+            return
+        kvb = cfg.kv_bytes_per_position
+        ms64 = res[64][0]
+        byt = cfg.q4_weight_bytes_per_token + kvb * 64 * (n_prompt + warmup + K // 2)
+        print(json.dumps({
+            "metric": "batched greedy decode tok/s (all sequences), Qwen2.5-3B shape, batch 64, all-q4_0 weights, fp16 KV", "value": round(64 / (ms64 * 1e-3), 1),
+            "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": warmup, "ms_per_step": round(ms64, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "uint4 x int8 -> int32 on tcgen05 (kind::i8); fp64-carried sums stored fp32; fp16 KV", "data": "synthetic",
+            "config": {"workload": f"batch(config 4): Qwen2.5-3B shape, batch 1 / 16 / 64 independent sequences, {n_prompt}-token seeded prompts, "
+                                   f"positions {n_prompt + warmup}..{n_prompt + warmup + K - 1}; 16 sequences per weight pass (batch 64 = 4 passes per step)",
+                       "l2": "1.74 GB of weights per pass, larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": round(byt / (ms64 * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(byt / (ms64 * 1e-3) / 1e9 / peak, 4), "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "traffic": None,
+                         "kernel": "whole step (gemm_q4_q8_tc_kernel + vf_attention + glue)", "algorithmic_bytes_per_launch": byt,
+                         "note": "algorithmic bytes count the weights once per step; batch 64 streams them four times"},
+            "step_ms_by_batch": {str(B): round(v[0], 3) for B, v in res.items()},
+            "tok_s_by_batch": {str(B): round(B / (v[0] * 1e-3), 1) for B, v in res.items()},
+            "gpu_launches": K * (9 * cfg.n_layer + 4) * (1 + 1 + 4),
+        }))
+        return
+
+    if args.workload == "spec":
+        # lossless n-gram speculation on a prompt with repeats: tokens/s with and without drafting, same ids
+        if rank == 0:
+            ensure_model()
+        barrier()
+        model = pkg.Model(ctx, ensure_model(), 1024)
+        cfg = model.config
+        base = prompt_ids(cfg.n_vocab)[:16]
+        prompt = base * 4
+        n_gen = max(32, min(args.steps, 256))
+        res = {}
+        for name, dk in (("plain", 0), ("spec", 8)):
+            model.generate_spec(prompt, 8, 3, dk)               # untimed
+            t0 = time.perf_counter()
+            ids_, st = model.generate_spec(prompt, n_gen, 3, dk)
+            dt = time.perf_counter() - t0
+            res[name] = (ids_, st, dt)
+        if rank != 0:
+            return
+        same = res["plain"][0] == res["spec"][0]
+        st = res["spec"][1]
+        print(json.dumps({
+            "metric": "greedy generation tok/s with lossless n-gram speculation (prompt included in the time), Qwen2.5-1.5B shape", "value": round(n_gen / res["spec"][2], 1),
+            "unit": "tok/s", "n_gpus": world, "steps": n_gen, "warmup": 1, "ms_per_step": round(res["spec"][2] * 1e3 / n_gen, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "as the decode and verify steps", "data": "synthetic",
+            "config": {"workload": "spec: 64-token prompt made of a 16-token seeded block repeated four times, NGMAX=3, DRAFTK=8; "
+                                   "random-init weights do not continue the repetition, so acceptance here is the floor, not a typical value"},
+            "plain_tok_s": round(n_gen / res["plain"][2], 1), "identical_ids": same,
+            "spec_stats": {k: v for k, v in st.items() if k != "margins"}, "gpu_launches": st["steps"],
+        }))
+        return
+
     if args.workload == "verify":
         # M-token step on the 1.5B-shape model at cached contexts 512 / 8192 / 32768 (KV filled with N(0,1) fp16):
         # one pass over the weights scores M drafted tokens; logits of a token must not depend on M
@@ -759,12 +844,12 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "verify", "attn", "setup", "roofline"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "gemv", "gemm", "verify", "attn", "setup", "roofline", "batch", "spec"])
     ap.add_argument("--stack-mb", type=int, default=512, help="distinct weight bytes per GEMV shape per GPU (MiB); small values are for profiler captures")
     ap.add_argument("--shapes", default="", help="comma list like 8960x1536 to restrict the GEMV sweep (profiler captures)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 512 if args.workload == "decode" else 200 if args.workload == "gemv" else 10 if args.workload in ("attn", "setup", "verify", "roofline") else 50
+        args.steps = 512 if args.workload == "decode" else 200 if args.workload == "gemv" else 10 if args.workload in ("attn", "setup", "verify", "roofline") else 32 if args.workload == "batch" else 128 if args.workload == "spec" else 50
     # torch.distributed.run pins OMP_NUM_THREADS to 1; the CPU baseline on rank 0 is meant to use every host thread
     if os.environ.get("OMP_NUM_THREADS") == "1" and "LOCAL_RANK" in os.environ:
         os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)

@@ -96,6 +96,69 @@ ORC_API void orc_dequant_row_q4_0(const uint8_t* row, int64_t nb, float* out) {
     }
 }
 
+/* One row of a Q4_1 / Q8_0 / Q6_K matrix to fp32 (src/gguf.h:103-140); ggml type ids 3, 8, 14.
+ * Q4_1: 20-byte blocks {fp16 d, fp16 m, 16 bytes}: value = nibble * d + m.
+ * Q8_0: 34-byte blocks {fp16 d, 32 int8}: value = q * d.
+ * Q6_K: 210-byte super-blocks of 256 {ql[128], qh[64], int8 sc[16], fp16 d}: value = d * sc * (6-bit q - 32),
+ *       multiplied left to right in fp32 as the reference writes it. */
+ORC_API int orc_dequant_row_t(int type, const uint8_t* p, int64_t cols, float* out) {
+    if (type == 3) {
+        for (int64_t b = 0; b < cols / 32; b++, p += 20) {
+            uint16_t dh, mh; memcpy(&dh, p, 2); memcpy(&mh, p + 2, 2);
+            const float d = orc_fp16_to_fp32(dh), m = orc_fp16_to_fp32(mh);
+            const uint8_t* qs = p + 4; float* y = out + b * 32;
+            for (int j = 0; j < 16; j++) { y[j] = (float)(qs[j] & 0x0F) * d + m; y[j + 16] = (float)(qs[j] >> 4) * d + m; }
+        }
+        return 0;
+    }
+    if (type == 8) {
+        for (int64_t b = 0; b < cols / 32; b++, p += 34) {
+            uint16_t dh; memcpy(&dh, p, 2);
+            const float d = orc_fp16_to_fp32(dh);
+            const int8_t* qs = (const int8_t*)(p + 2); float* y = out + b * 32;
+            for (int j = 0; j < 32; j++) y[j] = (float)qs[j] * d;
+        }
+        return 0;
+    }
+    if (type == 14) {
+        for (int64_t b = 0; b < cols / 256; b++, p += 210) {
+            const uint8_t* ql = p; const uint8_t* qh = p + 128; const int8_t* sc = (const int8_t*)(p + 192);
+            uint16_t dh; memcpy(&dh, p + 208, 2);
+            const float d = orc_fp16_to_fp32(dh);
+            float* y = out + b * 256;
+            for (int n = 0; n < 256; n += 128) {
+                for (int l = 0; l < 32; l++) {
+                    const int is = l / 16;
+                    const int8_t q1 = (int8_t)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;
+                    const int8_t q2 = (int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32;
+                    const int8_t q3 = (int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+                    const int8_t q4 = (int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+                    y[l] = d * sc[is + 0] * q1; y[l + 32] = d * sc[is + 2] * q2; y[l + 64] = d * sc[is + 4] * q3; y[l + 96] = d * sc[is + 6] * q4;
+                }
+                ql += 64; qh += 32; sc += 8; y += 128;
+            }
+        }
+        return 0;
+    }
+    return 1;
+}
+
+/* The reference's own q4_0 re-quantizer for tensors stored in another type (src/mega.cu:924-936, the same arithmetic
+ * as src/cuda_infer.cu:816-835): symmetric, d = amax / 7, q = clamp(lrintf(y / d) + 8, 0, 15), scale stored as fp16. */
+ORC_API void orc_requant_row_q4_0(const float* y, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / 32; b++, y += 32, out += 18) {
+        float amax = 0.f;
+        for (int j = 0; j < 32; j++) amax = fmaxf(amax, fabsf(y[j]));
+        const float d = amax / 7.f, inv = (d > 0.f) ? 1.f / d : 0.f;
+        const uint16_t dh = orc_fp32_to_fp16(d); memcpy(out, &dh, 2);
+        for (int j = 0; j < 16; j++) {
+            int q0 = (int)lrintf(y[j] * inv) + 8;      q0 = q0 < 0 ? 0 : (q0 > 15 ? 15 : q0);
+            int q1 = (int)lrintf(y[j + 16] * inv) + 8; q1 = q1 < 0 ? 0 : (q1 > 15 ? 15 : q1);
+            out[2 + j] = (uint8_t)(q0 | (q1 << 4));
+        }
+    }
+}
+
 /* ggml's q4_0 quantizer, as the benchmark configuration states it: d = (signed
  * value of largest magnitude) / -8, q = min(15, trunc(x/d + 8.5)).  The scale is
  * stored as fp16; the division uses the fp32 d.  Not in the reference tree (the

@@ -33,6 +33,13 @@ void ref_dequant_row_q4_0(const uint8_t* raw, int64_t rows, int64_t cols, int64_
     GGUF::dequant_row(W, r, out);
 }
 
+// src/gguf.h:85-140, any tensor type the reference reads (ggml type id)
+__attribute__((visibility("default")))
+void ref_dequant_row(uint32_t type, const uint8_t* raw, int64_t rows, int64_t cols, int64_t r, float* out) {
+    Tensor W = make_tensor(type, cols, rows, raw);
+    GGUF::dequant_row(W, r, out);
+}
+
 // src/cpu_infer.cpp:40-46
 __attribute__((visibility("default")))
 void ref_rmsnorm(const float* x, const float* w, int n, float eps, float* out) {

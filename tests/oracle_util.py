@@ -33,6 +33,8 @@ def lib():
         L.orc_fp32_to_fp16.restype, L.orc_fp32_to_fp16.argtypes = C.c_uint16, [_f32]
         L.orc_dequant_row_q4_0.argtypes = [_vp, _i64, _vp]
         L.orc_quantize_row_q4_0.argtypes = [_vp, _i64, _vp]
+        L.orc_dequant_row_t.restype, L.orc_dequant_row_t.argtypes = _i32, [_i32, _vp, _i64, _vp]
+        L.orc_requant_row_q4_0.argtypes = [_vp, _i64, _vp]
         L.orc_quant_q8.argtypes = [_vp, _i64, _vp, _vp]
         L.orc_block_isums.argtypes = [_vp, _i64, _i64, _vp, _vp]
         L.orc_gemv_q4_q8.argtypes = [_vp, _i64, _i64, _vp, _vp, _vp, _vp]
@@ -65,6 +67,7 @@ def ref():
         R.ref_rope.argtypes = [_vp, _i32, _i32, _i32, _f32]
         R.ref_add_bias.argtypes = [_vp, _vp, _i32]
         R.ref_fp16_to_fp32.restype, R.ref_fp16_to_fp32.argtypes = _f32, [C.c_uint16]
+        R.ref_dequant_row.argtypes = [C.c_uint32, _vp, _i64, _i64, _i64, _vp]
         _ref = R
     return _ref
 
@@ -242,3 +245,43 @@ def run_ref_cpu_infer(gguf_path, n_gen, prompt, threads=None, timeout=3600):
     if r.returncode != 0:
         raise RuntimeError("cpu_infer failed: " + r.stderr)
     return [int(t) for t in r.stdout.split()], dt
+
+
+# ---- other block formats (real model files): bytes per block, elements per block, ggml type id
+BLOCK_FORMATS = {"q4_1": (3, 20, 32), "q8_0": (8, 34, 32), "q6_k": (14, 210, 256)}
+
+
+def random_blocks(fmt, rows, cols, rng):
+    """Random but well-formed raw blocks of a format: random quant bytes, small positive fp16 scales (and small mins)."""
+    tid, bpb, epb = BLOCK_FORMATS[fmt]
+    nblk = rows * (cols // epb)
+    raw = rng.integers(0, 256, size=(nblk, bpb), dtype=np.uint8)
+    sc = np.float16(rng.uniform(0.001, 0.02, nblk)).view(np.uint16)
+    if fmt == "q4_1":
+        raw[:, 0:2] = sc.view(np.uint8).reshape(-1, 2)
+        raw[:, 2:4] = np.float16(rng.uniform(-0.1, 0.0, nblk)).view(np.uint8).reshape(-1, 2)
+    elif fmt == "q8_0":
+        raw[:, 0:2] = sc.view(np.uint8).reshape(-1, 2)
+    else:
+        raw[:, 208:210] = np.float16(rng.uniform(1e-4, 1e-3, nblk)).view(np.uint8).reshape(-1, 2)
+    return np.ascontiguousarray(raw.reshape(-1))
+
+
+def dequant_rows(fmt, raw, rows, cols):
+    """The oracle's dequantization of every row (float32 [rows][cols])."""
+    tid, bpb, epb = BLOCK_FORMATS[fmt]
+    out = np.empty((rows, cols), np.float32)
+    rb = cols // epb * bpb
+    for r in range(rows):
+        assert lib().orc_dequant_row_t(tid, raw[r * rb:].ctypes.data, cols, out[r].ctypes.data) == 0
+    return out
+
+
+def requant_q4_0(y):
+    """The reference's q4_0 re-quantizer (amax/7, lrintf + 8) as restated by the oracle: float32 [rows][cols] -> raw q4_0 bytes."""
+    y = np.ascontiguousarray(y, np.float32)
+    rows, cols = y.shape
+    out = np.empty(rows * (cols // 32) * 18, np.uint8)
+    for r in range(rows):
+        lib().orc_requant_row_q4_0(y[r].ctypes.data, cols, out[r * (cols // 32) * 18:].ctypes.data)
+    return out
