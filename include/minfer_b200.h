@@ -120,6 +120,13 @@ MI_API int mi_weight_repack_q4_0_dev(mi_ctx* ctx, const void* raw_dev, int64_t r
  * (count*rows*(cols/32)*18 bytes).  For round-trip checks. Synchronous. */
 MI_API int mi_weight_download_q4_0(mi_ctx* ctx, const mi_weight* w, void* raw_host);
 MI_API int mi_weight_free(mi_ctx* ctx, mi_weight* w);
+/* Re-quantize a matrix stored as ggml Q4_1 (type 3), Q8_0 (8) or Q6_K (14) blocks into row-major q4_0 blocks, both in
+ * device memory: src is rows x cols in its stored block format (rows contiguous), dst receives rows*(cols/32)*18 bytes
+ * that mi_weight_repack_q4_0_dev accepts.  Dequantization per src/gguf.h:103-140, then the reference loader's symmetric
+ * rule d = amax/7, q = clamp(lrintf(y/d) + 8, 0, 15), fp16 d (src/mega.cu:924-936; the same as src/cuda_infer.cu:814-842).
+ * Replaces the host loop q4_rows (src/mega.cu:986-993), bit for bit.  cols must be a multiple of the block (32; 256 for
+ * Q6_K).  Asynchronous on the context's stream. */
+MI_API int mi_requant_q4_0(mi_ctx* ctx, int ggml_type, const void* src_dev, int64_t rows, int64_t cols, void* dst_dev);
 /* Shape queries: rows, cols, count, bytes held on the device. */
 MI_API int mi_weight_info(const mi_weight* w, int64_t* rows, int64_t* cols, int64_t* count, int64_t* device_bytes);
 
@@ -219,15 +226,18 @@ enum { MI_STATE_H = 0, MI_STATE_Q = 1, MI_STATE_ATT = 2, MI_STATE_KCACHE = 3, MI
                                  * kind k (0 QKV, 1 attention, 2 O, 3 gate-up, 4 down, 5 lm_head), 12 = grid barrier,
                                  * 13 = per-step prologue.  The reference's PROFILE=1 (src/mega.cu:111-119). */
 
-/* Load an all-q4_0 Qwen2-architecture GGUF file (metadata keys and tensor names
+/* Load a Qwen2-architecture GGUF file (metadata keys and tensor names
  * exactly as the reference drivers read them: src/cpu_infer.cpp:71-98), repack
  * every matrix on the device (q/k/v fused, rows of q and k made pair-adjacent for
  * RoPE; gate and up interleaved by 32-row group), allocate an fp16 KV cache for
  * max_seq positions and plan the per-phase work split.  output.weight may be
  * absent or byte-identical to token_embd.weight (tied lm_head, stored once).
  * Replaces the load / upload / buffer set-up of src/cuda_infer.cu:846-955 and
- * src/mega.cu:1067-1139.  Tensor types other than Q4_0 (matrices) and F32 (norms,
- * biases) give MI_ERR_UNSUPPORTED. */
+ * src/mega.cu:1067-1139.  Matrices stored as Q4_1, Q8_0 or Q6_K are re-quantized
+ * to q4_0 on the device first (mi_requant_q4_0), as the reference's loader does on
+ * the host (src/mega.cu:986-993, 1109); a Q8_0 token embedding is kept and read as
+ * stored (src/mega.cu:639-646, 1110-1111).  Other matrix types, and norms or biases
+ * that are not F32, give MI_ERR_UNSUPPORTED. */
 MI_API int mi_model_load_gguf(mi_ctx* ctx, const char* path, int max_seq, mi_model** out);
 MI_API int mi_model_free(mi_ctx* ctx, mi_model* model);
 MI_API int mi_model_info(const mi_model* model, mi_model_config* out);

@@ -52,6 +52,7 @@ SIGNATURES = {
     "mi_weight_upload_q4_0": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
     "mi_weight_repack_q4_0_dev": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
     "mi_weight_download_q4_0": (_i32, [_vp, _vp, _vp]),
+    "mi_requant_q4_0": (_i32, [_vp, _i32, _vp, _i64, _i64, _vp]),
     "mi_weight_free": (_i32, [_vp, _vp]),
     "mi_weight_info": (_i32, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "mi_quant_q8": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
@@ -207,6 +208,10 @@ class Context:
         h = _vp()
         self.check(self.lib.mi_weight_repack_q4_0_dev(self.h, _ptr(raw_dev), rows, cols, count, C.byref(h)), "mi_weight_repack_q4_0_dev")
         return Weight(self, h)
+
+    def requant_q4_0(self, ggml_type, src_dev, rows, cols, dst_dev):
+        """Q4_1 (3), Q8_0 (8) or Q6_K (14) blocks on the device -> row-major q4_0 blocks on the device (uint8 tensors)."""
+        self.check(self.lib.mi_requant_q4_0(self.h, ggml_type, _ptr(src_dev), rows, cols, _ptr(dst_dev)), "mi_requant_q4_0")
 
     # ---- kernels (device pointers: torch CUDA tensors)
     def quant_q8(self, x, xq, xd, n=None, M=1):

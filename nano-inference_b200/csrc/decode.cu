@@ -20,9 +20,17 @@ int reset_after_error(mi_ctx* ctx, mi_model* m);
 
 namespace {
 
-struct Staging {       // one reusable device buffer for raw GGUF bytes
+struct Staging {       // one reusable device buffer for raw GGUF bytes, one for re-quantized q4_0 rows
     void* d = nullptr; size_t cap = 0;
-    ~Staging() { if (d) cudaFree(d); }
+    void* q = nullptr; size_t qcap = 0;
+    ~Staging() { if (d) cudaFree(d); if (q) cudaFree(q); }
+    int room_q(mi_ctx* ctx, size_t n) {                   // call after put(): the stream has drained, nothing reads q any more
+        if (n <= qcap) return MI_OK;
+        if (q) { cudaFree(q); q = nullptr; qcap = 0; }
+        if (cudaMalloc(&q, n) != cudaSuccess) return set_error(ctx, MI_ERR_NOMEM, "model: staging cudaMalloc(%zu) failed", n);
+        qcap = n;
+        return MI_OK;
+    }
     int put(mi_ctx* ctx, const void* src, size_t n) {
         if (n > cap) {
             if (d) { cudaStreamSynchronize(ctx->stream); cudaFree(d); d = nullptr; cap = 0; }
@@ -38,13 +46,16 @@ struct Staging {       // one reusable device buffer for raw GGUF bytes
     }
 };
 
+// A weight matrix asked for as GGML_Q4_0 may also be stored as Q4_1, Q8_0 or Q6_K: the loader re-quantizes those to q4_0.
 const mib200::GgufTensor* need(mi_ctx* ctx, const mib200::GgufFile& g, const std::string& name, uint32_t type,
                                int64_t cols, int64_t rows, int* st) {
     const mib200::GgufTensor* t = g.find(name);
     if (!t) { *st = set_error(ctx, MI_ERR_FORMAT, "model: tensor not found: %s", name.c_str()); return nullptr; }
-    if (t->type != type) {
+    const bool requant = type == mib200::GGML_Q4_0 && (t->type == mib200::GGML_Q4_1 || t->type == mib200::GGML_Q8_0 ||
+                                                       (t->type == mib200::GGML_Q6_K && cols % 256 == 0));
+    if (t->type != type && !requant) {
         *st = set_error(ctx, MI_ERR_UNSUPPORTED, "model: tensor %s has ggml type %u, this path takes %s only", name.c_str(), t->type,
-                        type == mib200::GGML_Q4_0 ? "Q4_0" : "F32");
+                        type == mib200::GGML_Q4_0 ? "Q4_0, Q4_1, Q8_0 or Q6_K" : "F32");
         return nullptr;
     }
     if (t->cols() != cols || t->rows() != rows) {
@@ -207,7 +218,13 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     auto repack = [&](const mib200::GgufTensor* t, uint8_t* dst, const int* map, int offset) -> int {
         int s = stg.put(ctx, t->data, t->nbytes());
         if (s) return s;
-        return launch_repack_map(ctx, stg.d, t->rows(), (int)(t->cols() / 32), choose_kb((int)(t->cols() / 32)), dst, map, offset);
+        const void* rows_q4 = stg.d;
+        if (t->type != mib200::GGML_Q4_0) {            // stored in another block format: q4_0 rows first (requant.cu)
+            if ((s = stg.room_q(ctx, (size_t)t->rows() * (t->cols() / 32) * 18))) return s;
+            if ((s = launch_requant_q4_0(ctx, (int)t->type, stg.d, t->rows(), t->cols(), stg.q))) return s;
+            rows_q4 = stg.q; m->requantized++;
+        }
+        return launch_repack_map(ctx, rows_q4, t->rows(), (int)(t->cols() / 32), choose_kb((int)(t->cols() / 32)), dst, map, offset);
     };
 
     // ---- embedding / lm_head
@@ -215,11 +232,21 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     const mib200::GgufTensor* tl = g.find("output.weight");            // optional: tied to the embedding when absent
     m->tied = !tl || (tl->type == te->type && tl->nbytes() == te->nbytes() && memcmp(tl->data, te->data, te->nbytes()) == 0);
     if (tl && !m->tied) { tl = need(ctx, g, "output.weight", mib200::GGML_Q4_0, E, V, &st); if (!tl) return st; }
+    // The lm_head is always a tiled q4_0 matrix.  The embedding shares it when the file ties them, except that a Q8_0
+    // embedding is kept as stored and read row by row (the reference's persistent engine does the same, src/mega.cu:1110-1111).
     uint8_t *d_emb = nullptr, *d_lm = nullptr; int ekb, ent;
-    if ((st = alloc_tiled(ctx, m, V, E, &d_emb, &ekb, &ent))) return st;
-    if ((st = repack(te, d_emb, nullptr, 0))) return st;
-    d_lm = d_emb;
-    if (!m->tied) { if ((st = alloc_tiled(ctx, m, V, E, &d_lm, &ekb, &ent))) return st; if ((st = repack(tl, d_lm, nullptr, 0))) return st; }
+    if ((st = alloc_tiled(ctx, m, V, E, &d_lm, &ekb, &ent))) return st;
+    if ((st = repack(m->tied ? te : tl, d_lm, nullptr, 0))) return st;
+    d_emb = d_lm;
+    if (te->type == mib200::GGML_Q8_0) {
+        uint8_t* d_e8;
+        if ((st = dev_alloc(ctx, m, &d_e8, te->nbytes()))) return st;
+        MI_CUDA(ctx, cudaMemcpy(d_e8, te->data, te->nbytes(), cudaMemcpyHostToDevice));
+        P.emb_q8 = d_e8;
+    } else if (!m->tied) {
+        if ((st = alloc_tiled(ctx, m, V, E, &d_emb, &ekb, &ent))) return st;
+        if ((st = repack(te, d_emb, nullptr, 0))) return st;
+    }
     P.emb_base = d_emb; P.emb_kb = ekb; P.emb_nt = ent;
     const mib200::GgufTensor* tn = need(ctx, g, "output_norm.weight", mib200::GGML_F32, E, 1, &st); if (!tn) return st;
     float* d_outnorm; if ((st = upload_f32(tn, &d_outnorm, E))) return st;

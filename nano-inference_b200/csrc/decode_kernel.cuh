@@ -156,6 +156,7 @@ struct DecodeParams {
     const float* rope_freq;          // [HD/2]: base^(-2i/HD), computed on the host with powf
     const uint8_t* emb_base;         // tiled token embedding (may alias the lm_head)
     int emb_nt, emb_kb;
+    const uint8_t* emb_q8;           // or, when set: the embedding as stored Q8_0 rows (34-byte blocks), read instead of emb_base
     // residual stream as committed by CTA 0: read by a launch that starts in the middle of a step, and by tests
     float* h_in;                     // at the input of the current layer
     float* h_mid;                    // after the attention block
@@ -602,6 +603,11 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
         #pragma unroll
         for (int k = 0; k < NB; k++) {
             const int b = min(warp + k * DNW, nb - 1);
+            if (P.emb_q8) {                                      // a Q8_0 row as stored: int8 * d (src/gguf.h:112-118; src/mega.cu:639-642)
+                const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + b) * 34;
+                x[k] = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
+                continue;
+            }
             const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
             const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
             const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));

@@ -54,6 +54,7 @@ int ensure_scratch(mi_ctx* ctx, size_t part_count, size_t n_counters);
 int ensure_staging(mi_ctx* ctx, size_t host_bytes, size_t dev_bytes);
 int launch_repack_map(mi_ctx* ctx, const void* raw_dev, long long src_rows, int nb, int kb, uint8_t* tiled,
                       const int* dst_row_dev, int row_offset);
+int launch_requant_q4_0(mi_ctx* ctx, int type, const void* src_dev, long long rows, long long cols, void* dst_dev);
 
 // Kernel launch, optionally with programmatic stream serialization: the kernel may become resident while its
 // predecessor in the stream still runs; it must execute griddepcontrol.wait (pdl_wait_prior) before it reads what the

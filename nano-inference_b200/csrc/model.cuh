@@ -33,6 +33,7 @@ struct mi_model {
     int max_seq = 0, grid = 0, max_chunks = 0, attn_ctas = 0;
     int tp_rank = 0, tp_world = 1;
     bool tied = false;
+    int requantized = 0;                  // matrices that were stored in another block format and re-quantized at load
     int64_t weight_bytes_q4 = 0;          // algorithmic q4_0 bytes streamed per token (18 bytes / 32 weights)
     std::vector<void*> allocs;            // everything cudaMalloc'ed for this model
     std::vector<mi::Job> jobs;

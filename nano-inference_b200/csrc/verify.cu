@@ -36,7 +36,10 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
     for (int b = warp; b < nb; b += DNW) {
         const int e = b * 32 + lane;
         float x;
-        if (embed) {                                                // value (nibble - 8) * d (src/gguf.h:94-102)
+        if (embed && P.emb_q8) {                                    // a Q8_0 row as stored: int8 * d (src/gguf.h:112-118)
+            const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + b) * 34;
+            x = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
+        } else if (embed) {                                         // value (nibble - 8) * d (src/gguf.h:94-102)
             const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
             const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
             const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));

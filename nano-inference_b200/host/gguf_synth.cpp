@@ -1,4 +1,4 @@
-// gguf_synth: writes a seeded, random-init, all-q4_0 Qwen2-architecture GGUF file
+// gguf_synth: writes a seeded, random-init Qwen2-architecture GGUF file (all q4_0 unless told otherwise)
 // that the reference programs (cpu_infer / cuda_infer / mega) and this engine
 // all accept.  It stands in for a published model file: there is no network for
 // checkpoints, and the benchmark configurations ask for seeded normal weights.
@@ -6,6 +6,11 @@
 //   gguf_synth <out.gguf> --preset {tiny|0.5b|1.5b|3b} [--seed S] [--std 0.02]
 //              [--bias-std 0.02] [--norm-std 0] [--layers L --embd E --ff F
 //              --heads H --kv-heads K --vocab V]
+//              [--emb-type T] [--head-type T] [--down-type T] [--untied]
+//
+// The last four make files shaped like published ones, which store the token embedding, the lm_head and ffn_down in
+// other block formats (T = 2 Q4_0, 3 Q4_1, 8 Q8_0, 14 Q6_K).  --untied (implied when the head and embedding types
+// differ) draws output.weight from its own random stream instead of repeating the embedding's bytes.
 //
 // File layout: the GGUF v3 subset the reference reader parses (reference
 // src/gguf.h:183-222).  Metadata keys and tensor names are the ones the
@@ -95,6 +100,75 @@ void quantize_row_q4_0(const float* x, int64_t n, uint8_t* out) {
     }
 }
 
+// ---- the other block formats.  Layouts as the reference reader decodes them (reference src/gguf.h:103-140); the
+// quantization rules are plain nearest-value ones, stated here in full (any well-formed blocks serve the tests).
+
+// Q8_0: fp16 d = amax / 127, 32 x int8 q = round(x / d)
+void quantize_row_q8_0(const float* x, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / 32; b++, out += 34) {
+        const float* xb = x + b * 32;
+        float amax = 0.f;
+        for (int j = 0; j < 32; j++) amax = std::fmax(amax, std::fabs(xb[j]));
+        const float d = amax / 127.f, id = d != 0.f ? 1.f / d : 0.f;
+        const uint16_t dh = f32_to_f16(d); memcpy(out, &dh, 2);
+        for (int j = 0; j < 32; j++) out[2 + j] = (uint8_t)(int8_t)std::lrintf(xb[j] * id);
+    }
+}
+// Q4_1: fp16 d = (max - min) / 15, fp16 m = min, nibbles q = min(15, trunc((x - min) / d + 0.5)); elements 0..15 low, 16..31 high
+void quantize_row_q4_1(const float* x, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / 32; b++, out += 20) {
+        const float* xb = x + b * 32;
+        float mn = xb[0], mx = xb[0];
+        for (int j = 1; j < 32; j++) { mn = std::fmin(mn, xb[j]); mx = std::fmax(mx, xb[j]); }
+        const float d = (mx - mn) / 15.f, id = d != 0.f ? 1.f / d : 0.f;
+        const uint16_t dh = f32_to_f16(d), mh = f32_to_f16(mn); memcpy(out, &dh, 2); memcpy(out + 2, &mh, 2);
+        for (int j = 0; j < 16; j++) {
+            int q0 = (int)((xb[j] - mn) * id + 0.5f), q1 = (int)((xb[j + 16] - mn) * id + 0.5f);
+            q0 = q0 > 15 ? 15 : q0; q1 = q1 > 15 ? 15 : q1;
+            out[4 + j] = (uint8_t)(q0 | (q1 << 4));
+        }
+    }
+}
+// Q6_K: 256 elements = ql[128] | qh[64] | int8 scale[16] | fp16 d.  Each run of 16 elements j has scale[j];
+// value = d * scale * (q - 32) with 6-bit q.  Rule: s_j = amax_j / 31, d = max_j s_j / 127, scale_j = round(s_j / d),
+// q = clamp(round(x / (d * scale_j)), -32, 31) + 32.
+void quantize_row_q6_k(const float* x, int64_t n, uint8_t* out) {
+    for (int64_t b = 0; b < n / 256; b++, out += 210) {
+        const float* xb = x + b * 256;
+        float sj[16], smax = 0.f;
+        for (int j = 0; j < 16; j++) {
+            float a = 0.f;
+            for (int i = 0; i < 16; i++) a = std::fmax(a, std::fabs(xb[j * 16 + i]));
+            sj[j] = a / 31.f; smax = std::fmax(smax, sj[j]);
+        }
+        const float d = smax / 127.f;
+        const uint16_t dh = f32_to_f16(d);
+        memset(out, 0, 210); memcpy(out + 208, &dh, 2);
+        for (int j = 0; j < 16; j++) {
+            const int sc = d > 0.f ? (int)std::lrintf(sj[j] / d) : 0;
+            out[192 + j] = (uint8_t)(int8_t)(sc > 127 ? 127 : sc);
+            const float step = d * (float)(int8_t)out[192 + j], is = step > 0.f ? 1.f / step : 0.f;
+            for (int i = 0; i < 16; i++) {
+                const int e = j * 16 + i, nh = e >> 7, qd = (e >> 5) & 3, l = e & 31;
+                int q = (int)std::lrintf(xb[e] * is); q = (q < -32 ? -32 : q > 31 ? 31 : q) + 32;
+                out[64 * nh + l + 32 * (qd & 1)] |= (uint8_t)((q & 0x0F) << (qd < 2 ? 0 : 4));
+                out[128 + 32 * nh + l] |= (uint8_t)((q >> 4) << (2 * qd));
+            }
+        }
+    }
+}
+
+inline size_t type_row_bytes(uint32_t type, int64_t cols) {
+    switch (type) {
+        case 0: return (size_t)cols * 4;
+        case 2: return (size_t)cols / 32 * 18;
+        case 3: return (size_t)cols / 32 * 20;
+        case 8: return (size_t)cols / 32 * 34;
+        case 14: return (size_t)cols / 256 * 210;
+    }
+    return 0;
+}
+
 struct TensorSpec {
     std::string name; uint32_t type; int64_t cols, rows; uint64_t key; float std_; float mean;
     int alias = -1;            // index of the tensor whose bytes this one repeats
@@ -120,12 +194,16 @@ void gen_tensor(const TensorSpec& t, std::vector<uint8_t>& buf, unsigned nthread
         if (t.mean != 0.f) for (int64_t i = 0; i < t.cols * t.rows; i++) o[i] += t.mean;
         return;
     }
-    const int64_t row_bytes = t.cols / 32 * 18;
+    const int64_t row_bytes = (int64_t)type_row_bytes(t.type, t.cols);
     auto work = [&](int64_t r0, int64_t r1) {
         std::vector<float> row((size_t)t.cols);
         for (int64_t r = r0; r < r1; r++) {
             fill_normal(row.data(), t.cols, t.key, r * t.cols, t.std_);
-            quantize_row_q4_0(row.data(), t.cols, buf.data() + r * row_bytes);
+            uint8_t* o = buf.data() + r * row_bytes;
+            if (t.type == 3) quantize_row_q4_1(row.data(), t.cols, o);
+            else if (t.type == 8) quantize_row_q8_0(row.data(), t.cols, o);
+            else if (t.type == 14) quantize_row_q6_k(row.data(), t.cols, o);
+            else quantize_row_q4_0(row.data(), t.cols, o);
         }
     };
     if (nthreads <= 1 || t.rows < 64) { work(0, t.rows); return; }
@@ -145,6 +223,12 @@ int main(int argc, char** argv) {
     }
     Shape sh{2, 128, 256, 4, 2, 512};
     uint64_t seed = 1234; float wstd = 0.02f, bstd = 0.02f, nstd = 0.f;
+    uint32_t emb_type = 2, head_type = 2, down_type = 2; bool untied = false;
+    auto block_type = [&](const char* v) -> uint32_t {
+        const int t = atoi(v);
+        if (t != 2 && t != 3 && t != 8 && t != 14) { fprintf(stderr, "gguf_synth: block type %d is not one of 2, 3, 8, 14\n", t); exit(1); }
+        return (uint32_t)t;
+    };
     for (int i = 2; i < argc; i++) {
         std::string a = argv[i];
         auto next = [&]() -> const char* { if (i + 1 >= argc) { fprintf(stderr, "missing value for %s\n", a.c_str()); exit(1); } return argv[++i]; };
@@ -166,6 +250,10 @@ int main(int argc, char** argv) {
         else if (a == "--heads") sh.heads = atoi(next());
         else if (a == "--kv-heads") sh.kv_heads = atoi(next());
         else if (a == "--vocab") sh.vocab = atoi(next());
+        else if (a == "--emb-type") emb_type = block_type(next());
+        else if (a == "--head-type") head_type = block_type(next());
+        else if (a == "--down-type") down_type = block_type(next());
+        else if (a == "--untied") untied = true;
         else { fprintf(stderr, "unknown option %s\n", a.c_str()); return 1; }
     }
     if (sh.embd % 32 || sh.ff % 32 || sh.embd % sh.heads || sh.heads % sh.kv_heads) {
@@ -173,17 +261,22 @@ int main(int argc, char** argv) {
         return 1;
     }
     const int hd = sh.embd / sh.heads, kvd = hd * sh.kv_heads;
+    if (((emb_type == 14 || head_type == 14) && sh.embd % 256) || (down_type == 14 && sh.ff % 256)) {
+        fprintf(stderr, "gguf_synth: a Q6_K tensor needs a row length that is a multiple of 256\n");
+        return 1;
+    }
+    if (head_type != emb_type) untied = true;
 
     std::vector<TensorSpec> ts;
     uint64_t tid = 0;
     auto add = [&](const std::string& n, uint32_t type, int64_t cols, int64_t rows, float sd, float mean) {
         TensorSpec t; t.name = n; t.type = type; t.cols = cols; t.rows = rows; t.std_ = sd; t.mean = mean;
         t.key = splitmix64(seed ^ splitmix64(++tid * 0xD1B54A32D192ED03ull));
-        t.nbytes = type == 0 ? (size_t)cols * rows * 4 : (size_t)rows * (cols / 32) * 18;
+        t.nbytes = (size_t)rows * type_row_bytes(type, cols);
         ts.push_back(t);
     };
-    add("token_embd.weight", 2, sh.embd, sh.vocab, wstd, 0.f);
-    add("output.weight", 2, sh.embd, sh.vocab, wstd, 0.f); ts.back().alias = 0;
+    add("token_embd.weight", emb_type, sh.embd, sh.vocab, wstd, 0.f);
+    add("output.weight", head_type, sh.embd, sh.vocab, wstd, 0.f); if (!untied) ts.back().alias = 0;
     add("output_norm.weight", 0, sh.embd, 1, nstd, 1.f);
     for (int l = 0; l < sh.layers; l++) {
         std::string p = "blk." + std::to_string(l) + ".";
@@ -198,7 +291,7 @@ int main(int argc, char** argv) {
         add(p + "ffn_norm.weight", 0, sh.embd, 1, nstd, 1.f);
         add(p + "ffn_gate.weight", 2, sh.embd, sh.ff, wstd, 0.f);
         add(p + "ffn_up.weight", 2, sh.embd, sh.ff, wstd, 0.f);
-        add(p + "ffn_down.weight", 2, sh.ff, sh.embd, wstd, 0.f);
+        add(p + "ffn_down.weight", down_type, sh.ff, sh.embd, wstd, 0.f);
     }
     uint64_t off = 0;
     for (auto& t : ts) { t.offset = off; off += (t.nbytes + 31) / 32 * 32; }

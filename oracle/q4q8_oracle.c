@@ -362,6 +362,8 @@ typedef struct {
     const uint8_t* const* wq; const uint8_t* const* wk; const uint8_t* const* wv; const uint8_t* const* wo;
     const float* const*   bq; const float* const* bk; const float* const* bv;
     const uint8_t* const* wg; const uint8_t* const* wu; const uint8_t* const* wd;
+    int32_t tok_emb_type;        /* 0 or 2: q4_0 rows; 8: Q8_0 rows (34-byte blocks), which the reference's persistent
+                                    engine reads without re-quantizing (src/mega.cu:639-646, 1110-1111) */
 } orc_model;
 
 typedef struct {
@@ -420,7 +422,8 @@ ORC_API int orc_forward(const orc_model* m, orc_state* s, int token, int pos, fl
     const int E = m->n_embd, HD = m->head_dim, NH = m->n_head, NKV = m->n_head_kv;
     const int kv_dim = NKV * HD, FF = m->n_ff, V = m->n_vocab;
     const int64_t nbE = E / 32;
-    orc_dequant_row_q4_0(m->tok_emb + (int64_t)token * nbE * 18, nbE, s->h);
+    if (m->tok_emb_type == 8) orc_dequant_row_t(8, m->tok_emb + (int64_t)token * nbE * 34, E, s->h);
+    else orc_dequant_row_q4_0(m->tok_emb + (int64_t)token * nbE * 18, nbE, s->h);
     for (int l = 0; l < m->n_layer; l++) {
         orc_rmsnorm(s->h, m->attn_norm[l], E, m->rms_eps, s->xb);
         mv(s, m->wq[l], NH * HD, E, s->xb, m->bq[l], s->q, 1);

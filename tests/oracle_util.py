@@ -154,12 +154,14 @@ def f16_bits_to_f32(bits):
 class _OrcModel(C.Structure):
     _fields_ = [(n, _i32) for n in ("n_layer", "n_embd", "n_ff", "n_head", "n_head_kv", "head_dim", "n_vocab")] + \
                [("rope_base", _f32), ("rms_eps", _f32), ("tok_emb", _vp), ("out_w", _vp), ("out_norm", _vp)] + \
-               [(n, _vp) for n in ("attn_norm", "ffn_norm", "wq", "wk", "wv", "wo", "bq", "bk", "bv", "wg", "wu", "wd")]
+               [(n, _vp) for n in ("attn_norm", "ffn_norm", "wq", "wk", "wv", "wo", "bq", "bk", "bv", "wg", "wu", "wd")] + \
+               [("tok_emb_type", _i32)]
 
 
 class OracleModel:
     """Runs the restated forward pass on the tensors of a parsed GGUF file
-    (tests/gguf_util.GgufReader)."""
+    (tests/gguf_util.GgufReader).  Matrices stored as Q4_1, Q8_0 or Q6_K are re-quantized to q4_0 the way the reference's
+    loader does (src/mega.cu:986-993); a Q8_0 token embedding is read as it is (src/mega.cu:1110-1111)."""
 
     def __init__(self, g, act_q8, kv_f16, max_seq):
         self.g = g
@@ -168,8 +170,12 @@ class OracleModel:
         L = cfg["n_layer"]
         self._keep = []
 
-        def arr(name):
+        def arr(name, keep_q8=False):
             a = g.tensor_bytes(name)
+            typ, rows, cols = g.shape(name)
+            if typ not in (0, 2) and not (keep_q8 and typ == 8):
+                fmt = {t: f for f, (t, _, _) in BLOCK_FORMATS.items()}[typ]
+                a = requant_q4_0(dequant_rows(fmt, a, rows, cols))
             self._keep.append(a)
             return a.ctypes.data
 
@@ -182,7 +188,8 @@ class OracleModel:
         for k in ("n_layer", "n_embd", "n_ff", "n_head", "n_head_kv", "head_dim", "n_vocab"):
             setattr(m, k, cfg[k])
         m.rope_base, m.rms_eps = cfg["rope_base"], cfg["rms_eps"]
-        m.tok_emb, m.out_w, m.out_norm = arr("token_embd.weight"), arr("output.weight"), arr("output_norm.weight")
+        m.tok_emb, m.out_w, m.out_norm = arr("token_embd.weight", True), arr("output.weight"), arr("output_norm.weight")
+        m.tok_emb_type = g.shape("token_embd.weight")[0]
         m.attn_norm, m.ffn_norm = parr("blk.{}.attn_norm.weight"), parr("blk.{}.ffn_norm.weight")
         m.wq, m.wk, m.wv, m.wo = (parr(f"blk.{{}}.attn_{n}.weight") for n in ("q", "k", "v", "output"))
         m.bq, m.bk, m.bv = (parr(f"blk.{{}}.attn_{n}.bias") for n in ("q", "k", "v"))
