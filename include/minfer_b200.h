@@ -102,6 +102,13 @@ MI_API int mi_probe_read_bw(mi_ctx* ctx, size_t bytes, int variant, int repeats,
  * (bench/roofline.cu:125-149). */
 MI_API int mi_probe_hop_ns(mi_ctx* ctx, int iters, float* ns_out);
 
+/* ---- detokenizer (host only) ------------------------------------------------ */
+/* Decode one vocabulary piece of a byte-level BPE tokenizer (the strings of tokenizer.ggml.tokens in a Qwen2 file) into
+ * the text bytes it stands for: every code point of the piece maps back to one byte through the inverse of GPT-2's
+ * byte-to-unicode table.  Replaces build_byte_decoder / detok_piece (src/detok.h:13-41).  Writes at most cap bytes to out
+ * and returns the number of bytes of the decoded piece (never more than n); -1 on a null argument.  Needs no GPU. */
+MI_API int64_t mi_detok_piece(const char* piece, int64_t n, char* out, int64_t cap);
+
 /* ---- weights: GGUF q4_0 -> tiled device layout --------------------------- */
 
 /* Upload `count` consecutive row-major q4_0 matrices of rows x cols (18-byte
@@ -254,6 +261,16 @@ MI_API int mi_model_state_ptr(const mi_model* model, int which, void** ptr, int6
  * src/cuda_infer.cu:1031-1201 and the mega kernel of src/mega.cu:597-903. */
 MI_API int mi_decode(mi_ctx* ctx, mi_model* model, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
                      int32_t* out_tokens_host, float* logits_dev, int mode, float* elapsed_ms);
+
+/* Stop rule of text generation.  Once set (token >= 0), a run of whole steps ends after the first step whose prediction
+ * is consumed as the next input (not a forced position) and equals `token`: the persistent kernel leaves its loop on
+ * every CTA (src/mega.cu:868-874, done = stop_eos && cur == eos), the kernel-sequence engine looks at each token before
+ * it launches the next step (src/cuda_infer.cu:1186-1193), mi_generate_spec stops emitting (src/cuda_infer.cu:1254-1275).
+ * The stop token itself is the last token produced.  mi_model_last_count: how many tokens the last mi_decode or
+ * mi_generate_spec call produced (a run through mi_decode_run reports through its ring's count).  -1 switches the rule
+ * off (the default: the id-printing form of the drivers never stops early, src/mega.cu:1017). */
+MI_API int mi_model_set_stop_token(mi_model* model, int token);
+MI_API int mi_model_last_count(const mi_model* model);
 /* Top-1 minus top-2 logit of each of the first n steps of the last mi_decode call on this model
  * (host memory out).  The reference's engine reports this margin per token (src/mega.cu:385-392,
  * 523-550, printed at :1189, 1196, 1241); its A/B harness reads it (tools/ab.sh:41,49). */

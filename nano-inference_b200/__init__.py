@@ -53,6 +53,9 @@ SIGNATURES = {
     "mi_weight_repack_q4_0_dev": (_i32, [_vp, _vp, _i64, _i64, _i64, C.POINTER(_vp)]),
     "mi_weight_download_q4_0": (_i32, [_vp, _vp, _vp]),
     "mi_requant_q4_0": (_i32, [_vp, _i32, _vp, _i64, _i64, _vp]),
+    "mi_detok_piece": (_i64, [C.c_char_p, _i64, C.c_char_p, _i64]),
+    "mi_model_set_stop_token": (_i32, [_vp, _i32]),
+    "mi_model_last_count": (_i32, [_vp]),
     "mi_weight_free": (_i32, [_vp, _vp]),
     "mi_weight_info": (_i32, [_vp, C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64), C.POINTER(_i64)]),
     "mi_quant_q8": (_i32, [_vp, _vp, _i64, _i32, _vp, _vp]),
@@ -124,6 +127,16 @@ def load_library(path=None):
     if path is None:
         _lib = lib
     return lib
+
+
+def detok_piece(piece):
+    """Text bytes of one vocabulary piece of a byte-level BPE tokenizer (bytes or str in, bytes out).  Host only."""
+    raw = piece.encode("utf-8") if isinstance(piece, str) else bytes(piece)
+    buf = C.create_string_buffer(max(len(raw), 1))
+    n = load_library().mi_detok_piece(raw, len(raw), buf, len(raw))
+    if n < 0:
+        raise ValueError("mi_detok_piece: bad argument")
+    return buf.raw[:n]
 
 
 def _ptr(t):
@@ -351,6 +364,14 @@ class Model:
         self.ctx.check(self.ctx.lib.mi_decode(self.ctx.h, self.h, _ptr(toks) if toks.size else None, toks.size, n_steps, pos0,
                                               _ptr(out), _ptr(logits), mode, C.byref(ms)), "mi_decode")
         return out[:n_steps].tolist(), ms.value
+
+    def set_stop_token(self, token):
+        """End runs of whole steps after the step that picks `token` as the next input (-1: never)."""
+        self.ctx.check(self.ctx.lib.mi_model_set_stop_token(self.h, token), "mi_model_set_stop_token")
+
+    def last_count(self):
+        """Tokens the last decode / generate_spec call produced (fewer than asked after a stop)."""
+        return int(self.ctx.lib.mi_model_last_count(self.h))
 
     def margins(self, n):
         """Top-1 minus top-2 logit of the first n steps of the last decode call (numpy float32)."""

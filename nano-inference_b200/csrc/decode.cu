@@ -393,6 +393,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     float* d_freq; if ((st = dev_alloc(ctx, m, &d_freq, freq.size()))) return st;
     MI_CUDA(ctx, cudaMemcpy(d_freq, freq.data(), freq.size() * 4, cudaMemcpyHostToDevice));
     P.rope_freq = d_freq;
+    P.stop_token = -1;
 
     // ---- state
     // the exchange block: every vector one CTA hands to another, as tagged 8-byte words (layout: XwLayout)
@@ -407,6 +408,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         x.down = take((E + 31) / 32 * 32);
         x.dpart = take((E + 31) / 32 * (kMaxKSplit - 1) * 64);
         x.cand = take(kMaxWorldTP * m->grid * 4);
+        x.tokw = take(2);
         x.total = off;
     }
     if ((st = dev_alloc(ctx, m, &P.h_in, E)) || (st = dev_alloc(ctx, m, &P.h_mid, E)) || (st = dev_alloc(ctx, m, &P.att, NQ)) ||
@@ -558,7 +560,7 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
         if ((st = dev_alloc(ctx, m, &m->d_out_tokens, (size_t)n_steps * 2)) || (st = dev_alloc(ctx, m, &m->d_margins, (size_t)n_steps * 2))) return st;
         m->out_capacity = n_steps * 2;
     }
-    m->last_steps = n_steps;
+    m->last_steps = n_steps; m->last_count = n_steps;
     if (ring && ring->used + n_steps > ring->capacity)
         return set_error(ctx, MI_ERR_LIMIT, "decode: the token ring holds %d entries, %d are used and %d more are asked for", ring->capacity, ring->used, n_steps);
     if (n_forced) MI_CUDA(ctx, cudaMemcpyAsync(m->d_in_tokens, in_tokens_host, (size_t)n_forced * 4, cudaMemcpyHostToDevice, ctx->stream));
@@ -573,6 +575,9 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
         for (int r = 0; r < m->tp_world; r++) T.xw_peer[r] = reinterpret_cast<unsigned long long*>(m->tp_peer[r][0]);
     }
     P.wait_ns = ctx->wait_ns;
+    // the stop rule applies to runs over whole steps that feed their own predictions back
+    const int stop = (ph0 == 0 && ph1 == 5 * m->L + 1 && n_steps > n_forced - 1) ? m->stop_token : -1;
+    P.stop_token = stop;
     if ((st = mi::reset_after_error(ctx, m))) return st;
     P.in_tokens = m->d_in_tokens; P.n_forced = n_forced; P.out_tokens = m->d_out_tokens; P.pos0 = pos0;
     P.out_margins = m->d_margins;
@@ -592,16 +597,29 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
             if (Ps.logits) Ps.logits += (long long)s * Ps.logits_stride;    // the kernel indexes logits from its first step
             for (int ph = ph0; ph < ph1; ph++)
                 if ((st = dispatch_launch(ctx, m, Ps, s, s + 1, ph, ph + 1, false))) return st;
+            if (stop >= 0 && s + 1 >= n_forced && s + 1 < n_steps) {
+                // under the stop rule this engine looks at every token before it launches the next step, as the reference's
+                // kernel-sequence driver does (src/cuda_infer.cu:1186-1193)
+                int32_t tok = -1;
+                MI_CUDA(ctx, cudaMemcpyAsync(&tok, m->d_out_tokens + s, 4, cudaMemcpyDeviceToHost, ctx->stream));
+                if ((st = mi_ctx_sync(ctx))) return st;
+                if (tok == stop) { m->last_count = s + 1; break; }
+            }
         }
     } else {
         return set_error(ctx, MI_ERR_INVALID, "decode: unknown mode %d", mode);
     }
     MI_CUDA(ctx, cudaEventRecord(m->ev1, ctx->stream));
     if (async) return MI_OK;                          // the caller follows the ring and synchronizes itself
+    std::vector<int32_t> scan;
+    if (stop >= 0 && !out_tokens_host) { scan.resize((size_t)n_steps); out_tokens_host = scan.data(); }
     if (out_tokens_host)
         MI_CUDA(ctx, cudaMemcpyAsync(out_tokens_host, m->d_out_tokens, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     st = mi_ctx_sync(ctx);
     if (st != MI_OK) return st;
+    if (stop >= 0 && mode == MI_DECODE_PERSISTENT)    // the kernel ended the run after the first consumed prediction equal to the stop token
+        for (int s = std::max(n_forced - 1, 0); s < n_steps; s++)
+            if (out_tokens_host[s] == stop) { m->last_count = s + 1; break; }
     if (elapsed_ms) MI_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, m->ev0, m->ev1));
     return MI_OK;
 }
@@ -617,6 +635,14 @@ extern "C" int mi_decode_run(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_
     if (!ring) return set_error(ctx, MI_ERR_INVALID, "decode_run: null ring");
     return decode_impl(ctx, m, in_tokens_host, n_forced, n_steps, pos0, nullptr, nullptr, MI_DECODE_PERSISTENT, 0, m ? 5 * m->L + 1 : 0, nullptr, ring, true);
 }
+
+extern "C" int mi_model_set_stop_token(mi_model* m, int token) {
+    if (!m || token >= m->V) return MI_ERR_INVALID;
+    m->stop_token = token < 0 ? -1 : token;
+    return MI_OK;
+}
+
+extern "C" int mi_model_last_count(const mi_model* m) { return m ? m->last_count : 0; }
 
 extern "C" int mi_decode_margins(mi_ctx* ctx, mi_model* m, int n, float* margins_host) {
     if (!ctx) return MI_ERR_INVALID;

@@ -137,6 +137,7 @@ struct XwLayout {
     int down;       // [E] fp32 bits: down projection                                    (pushed)
     int dpart;      // [E/32][kMaxKSplit-1][32][2]: double partial sums (lo, hi) of the down K-splits 1..
     int cand;       // [kMaxWorldTP][grid][4]: argmax candidates {best value}, {its row}, {second-best value}, -   (pushed)
+    int tokw;       // [2]: the token picked by the step that just ended, for the attention CTAs (written only under a stop rule)
     int total;
 };
 
@@ -179,6 +180,8 @@ struct DecodeParams {
     TokenRing ring;                  // optional: host-mapped ring the first GEMV CTA publishes every step's token into
     float* best_val;                 // value of the best logit (tensor parallelism with host-side exchange: this GPU's rows only)
     const int* in_tokens; int n_forced; int* out_tokens; int* cur_token;
+    int stop_token;                  // >= 0: a run over whole steps ends after the step that picks this token as the next input
+                                     // (text generation's end-of-sequence rule, src/mega.cu:868-874); -1: off
     float* logits; long long logits_stride;    // optional [n_steps][stride]
     int pos0;
     const int* pos_dev;              // optional: first position read from device memory instead (a captured launch sequence stays position-free)
@@ -1542,6 +1545,13 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
         const int pos = pos_base + step;
         if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;
+        if (P.stop_token >= 0 && step > step0 && step >= P.n_forced && ph0 == 0 && ph1 == nph) {
+            // the stop rule: learn the token the previous step picked (its lm_head phase carries tag tag0 - 1)
+            unsigned tw[1];
+            const bool got = tw_poll(P, tag0 - 1u, 1u, [&](int) { return P.xw + P.xo.tokw; }, tw);
+            ok = __syncthreads_and(got ? 1 : 0) != 0;
+            if (!ok || (int)tw[0] == P.stop_token) break;
+        }
         for (int l = max(0, (ph0 + 3) / 5); 5 * l + 1 < ph1 && l < P.L && ok; l++) {
             const int ph = 5 * l + 1;
             Pub pub;
@@ -1640,6 +1650,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     int8_t* xq_s = reinterpret_cast<int8_t*>(sm.stage);
     float2* xs_s = reinterpret_cast<float2*>(sm.stage + maxin);
     bool ok = true, h_valid = false;                   // h_valid: this CTA's shared-memory copy of the residual stream is current
+    bool stopped = false;                              // the run ended early on the stop token: tiles of later steps are in flight
     int err_code = MI_ERR_TIMEOUT;
     const unsigned epoch = __ldcg(P.epoch_dev);
     const int pos_base = P.pos_dev ? __ldcg(P.pos_dev) : P.pos0;
@@ -1802,6 +1813,8 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                     s_tok = tok;
                     if (ws.gcta == 0 && ok) {
                         const float margin = __fsub_rn(t.best, t.second);
+                        const bool stopping = P.stop_token >= 0 && tok == P.stop_token && step + 1 >= P.n_forced && ph0 == 0;
+                        if (P.stop_token >= 0 && P.attn_ctas > 0) pub.local(P.xo.tokw, (unsigned)tok);
                         __stcg(P.cur_token, tok); __stcg(P.best_val, t.best); P.out_tokens[step] = tok;
                         if (P.out_margins) P.out_margins[step] = margin;
                         if (P.ring.count) {
@@ -1810,7 +1823,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                             const int slot = P.ring.base + (step - step0);
                             if (slot < P.ring.capacity) {
                                 P.ring.tokens[slot] = tok; P.ring.margins[slot] = margin; P.ring.ns[slot] = gtime_ns();
-                                if (((step - step0) & 3) == 3 || step == step1 - 1) { __threadfence_system(); *reinterpret_cast<volatile int*>(P.ring.count) = slot + 1; }
+                                if (((step - step0) & 3) == 3 || step == step1 - 1 || stopping) { __threadfence_system(); *reinterpret_cast<volatile int*>(P.ring.count) = slot + 1; }
                             }
                         }
                     }
@@ -1818,6 +1831,11 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             }
             ok = __syncthreads_and(ok ? 1 : 0) != 0;          // a wait that gave up in one warp stops the whole CTA
             prof_mark(P, 2 * k + 1);
+        }
+        // the stop rule (every CTA has made the same pick): the step that produced the stop token was the last
+        if (P.stop_token >= 0 && ok && ph0 == 0 && ph1 == nph && s_tok == P.stop_token && step + 1 >= P.n_forced && step + 1 < step1) {
+            stopped = true;
+            break;
         }
     }
 #if MI_PROF
@@ -1833,6 +1851,8 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
         *P.epoch_dev = epoch + (unsigned)(step1 - step0) * (unsigned)nph + (ok ? 0u : (unsigned)nph);
     if (!ok) {
         if (lane == 0) atomicMax(P.err, err_code);
+        ws.drain();
+    } else if (stopped) {
         ws.drain();
     }
 }

@@ -40,6 +40,8 @@ struct mi_model {
     mi::DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
     int* d_in_tokens = nullptr; int in_capacity = 0;
     int* d_out_tokens = nullptr; int out_capacity = 0;
+    int stop_token = -1;                  // see mi_model_set_stop_token
+    int last_count = 0;                   // steps (tokens) the last decode / generate call produced: fewer than asked after a stop
     float* d_margins = nullptr; int last_steps = 0;   // top-1 minus top-2 logit of every step of the last decode call
     size_t smem = 0;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;

@@ -70,7 +70,9 @@ extern "C" int mi_generate_spec(mi_ctx* ctx, mi_model* m, const int32_t* prompt_
     // every 32nd step with a single drafted token (src/cuda_infer.cu:1233-1243)
     float ewma = 0.6f; const float gate = 0.55f; long probe = 0;
     int32_t draft[kMaxPass], hb[kMaxPass], r[kMaxPass];
-    while (n_emit < n_gen) {
+    const int stop = m->stop_token;                                   // generation ends with this token (src/cuda_infer.cu:1254,1272-1275)
+    auto stopped = [&]() { return stop >= 0 && n_emit > 0 && out_tokens_host[n_emit - 1] == stop; };
+    while (n_emit < n_gen && !stopped()) {
         bool allow = ewma >= gate, probing = false;
         if (!allow && (probe++ % 32) == 0) { allow = true; probing = true; }
         int K = (allow && draftk > 0) ? ngram_draft(seq, ngmax, draftk, draft) : 0;
@@ -99,12 +101,13 @@ extern "C" int mi_generate_spec(mi_ctx* ctx, mi_model* m, const int32_t* prompt_
             cur_margin = mg[a];
         }
         out_tokens_host[n_emit++] = cur;
-        for (int k = 0; k < a && n_emit < n_gen; k++) out_tokens_host[n_emit++] = draft[k];
+        for (int k = 0; k < a && n_emit < n_gen && !stopped(); k++) out_tokens_host[n_emit++] = draft[k];
         for (int k = 0; k < a; k++) seq.push_back(draft[k]);
         cur = r[a]; pos += a + 1; seq.push_back(cur);                  // the model's own token at the first mismatch
         ewma = 0.7f * ewma + 0.3f * ((float)a / (float)K);
         n_steps++; n_specruns++; n_drafted += K; n_accepted += a;
     }
+    m->last_count = n_emit;
     if (stats) { stats[0] = n_steps; stats[1] = n_drafted; stats[2] = n_accepted; stats[3] = n_specruns; }
     return MI_OK;
 }

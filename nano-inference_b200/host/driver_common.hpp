@@ -5,10 +5,12 @@
 // path only through the C ABI of minfer_b200.h.  Like the reference's CK()/REQUIRE()
 // they print and exit on any error; the library itself never exits.
 //
-// stdout: the n_gen greedy ids separated by a space, then a newline (the first id
-// is the prediction after the last prompt token: src/cpu_infer.cpp:161-167).
-// Token ids are always printed (the reference's RAWIDS=1 form): detokenized text
-// needs a real vocabulary and is outside this path.
+// stdout with RAWIDS=1: the n_gen greedy ids separated by a space, then a newline
+// (the first id is the prediction after the last prompt token:
+// src/cpu_infer.cpp:161-167).  Without RAWIDS: the text of the generated tokens,
+// streamed piece by piece through the byte-level detokenizer (mi_detok_piece), and
+// generation ends at the file's tokenizer.ggml.eos_token_id, whose piece is not
+// printed (src/cuda_infer.cu:861-873, 1192; src/mega.cu:1017, 1173).
 //
 // Environment: TEACHER=k (ids are a reference sequence whose first k are the
 // prompt; report top-1 agreement at every later position, with this engine's logit
@@ -35,6 +37,7 @@
 #include <thread>
 #include <vector>
 
+#include "gguf_file.hpp"
 #include "minfer_b200.h"
 
 namespace mib200 {
@@ -56,7 +59,26 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
     int tchunk = env_int("TCHUNK", 16);
     tchunk = tchunk < 1 ? 1 : tchunk > 16 ? 16 : tchunk;
     if (env_int("PROFILE", 0)) setenv("MINFER_PROFILE", "1", 1);
-    if (!env_int("RAWIDS", 0)) fprintf(stderr, "minfer-%s: text output is outside this path; printing token ids (RAWIDS=1 form)\n", tag);
+    const bool raw_ids = env_int("RAWIDS", 0) != 0;
+    // text mode: the vocabulary pieces and the end-of-sequence id come from the model file
+    GgufFile vocab_file;
+    int eos_id = -1;
+    if (!raw_ids) {
+        vocab_file.keep_token_strings(true);
+        const std::string err = vocab_file.open(argv[1]);
+        if (!err.empty()) { fprintf(stderr, "minfer-%s: %s\n", tag, err.c_str()); return 1; }
+        eos_id = (int)vocab_file.num("tokenizer.ggml.eos_token_id", 151645);
+    }
+    const std::vector<std::string>& vocab = vocab_file.tokens();
+    auto emit = [&](int id) {
+        if (raw_ids) { printf("%d ", id); return; }
+        if (id == eos_id || id < 0 || id >= (int)vocab.size()) return;
+        const std::string& piece = vocab[(size_t)id];
+        std::string text(piece.size(), '\0');
+        const int64_t n = mi_detok_piece(piece.data(), (int64_t)piece.size(), &text[0], (int64_t)text.size());
+        if (n > 0) fwrite(text.data(), 1, (size_t)n, stdout);
+        fflush(stdout);
+    };
 
     mi_ctx* ctx = nullptr;
     int st = mi_ctx_create(env_int("GPU", 0), &ctx);
@@ -71,6 +93,7 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
             tag, c.n_layer, c.n_embd, c.n_ff, c.n_head, c.n_head_kv, c.head_dim, c.n_vocab, c.max_seq,
             c.q4_weight_bytes_per_token / 1e6, (long long)c.kv_bytes_per_position, c.grid_ctas);
 
+    const bool stop_eos = !raw_ids && !teacher && eos_id >= 0 && eos_id < c.n_vocab;
     for (int w = env_int("WARMUP", 2); w > 0; w--) {             // untimed: clocks, instruction cache, first-touch
         int32_t tok = ids[0], out;
         if ((st = mi_decode(ctx, model, &tok, 1, 1, 0, &out, nullptr, mode, nullptr))) die(ctx, "mi_decode (warm-up)", st);
@@ -124,6 +147,8 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
     std::vector<unsigned long long> stamp;    // GPU time of each (ring path)
     double dms = 0, ttft = -1;
     long long n_steps = 0, n_drafted = 0, n_accepted = 0;
+    if (stop_eos && (st = mi_model_set_stop_token(model, eos_id))) die(ctx, "mi_model_set_stop_token", st);
+    int n_out = n_gen;                        // tokens actually generated: fewer when the end-of-sequence token came up
     const auto t0 = std::chrono::steady_clock::now();
     auto since = [&]() { return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count(); };
     if (spec && n_gen > 0) {
@@ -131,14 +156,15 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         gen.resize(n_gen); margin.resize(n_gen);
         int64_t stats[4] = {0, 0, 0, 0};
         if ((st = mi_generate_spec(ctx, model, ids.data(), P, n_gen, ngmax, draftk, gen.data(), margin.data(), stats))) die(ctx, "mi_generate_spec", st);
-        dms = since(); ttft = dms / (n_gen > 0 ? n_gen : 1);
+        n_out = mi_model_last_count(model);
+        dms = since(); ttft = dms / (n_out > 0 ? n_out : 1);
         n_steps = stats[0]; n_drafted = stats[1]; n_accepted = stats[2];
-        for (int i = 0; i < n_gen; i++) printf("%d ", gen[i]);
+        for (int i = 0; i < n_out; i++) emit(gen[i]);
         printf("\n");
         float minm = 1e30f; int mi = 0;
-        for (int i = 0; i < n_gen; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
+        for (int i = 0; i < n_out; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
         fprintf(stderr, "minfer-%s decode: %d tok in %.1f ms = %.2f tok/s | first token after %.1f ms (prompt %d) | min logit margin %.4f at #%d | prompt included in the time; NGMAX=%d DRAFTK=%d\n",
-                tag, n_gen, dms, dms > 0 ? n_gen * 1e3 / dms : 0.0, ttft, P, minm, mi, ngmax, draftk);
+                tag, n_out, dms, dms > 0 ? n_out * 1e3 / dms : 0.0, ttft, P, minm, mi, ngmax, draftk);
     } else if (n_gen > 0) {
         // prompt: all but its last token, tchunk per weight pass (or one step per token); the last prompt token is the
         // first step of the generation itself, so that every generated id comes with its margin
@@ -172,44 +198,46 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
                 for (; seen < cnt; seen++) {
                     if (ttft < 0) ttft = since();
                     gen[seen] = rt[seen]; margin[seen] = rm[seen]; stamp[seen] = rn[seen];
-                    printf("%d ", gen[seen]); fflush(stdout);
+                    emit(gen[seen]); fflush(stdout);
                 }
-                if (seen >= n_gen) break;
+                if (seen >= n_gen || (stop_eos && seen > 0 && gen[seen - 1] == eos_id)) break;
                 if (since() > 600e3) { fprintf(stderr, "minfer-%s: no token for ten minutes\n", tag); break; }
                 std::this_thread::sleep_for(std::chrono::microseconds(100));
             }
             if ((st = mi_ctx_sync(ctx))) die(ctx, "mi_decode_run", st);
             mi_ring_destroy(ctx, ring);
             printf("\n");
-            if (seen < n_gen) return 1;
-            dms = n_gen > 1 ? (double)(stamp[n_gen - 1] - stamp[0]) / 1e6 : 0.0;          // first to last token, on the GPU's clock
+            if (seen < n_gen && !(stop_eos && seen > 0 && gen[seen - 1] == eos_id)) return 1;
+            n_out = seen;
+            dms = n_out > 1 ? (double)(stamp[n_out - 1] - stamp[0]) / 1e6 : 0.0;          // first to last token, on the GPU's clock
         } else {
             float ms = 0;
             if ((st = mi_decode(ctx, model, &ids[P - 1], 1, n_gen, P - 1, gen.data(), nullptr, mode, &ms))) die(ctx, "mi_decode", st);
-            if ((st = mi_decode_margins(ctx, model, n_gen, margin.data()))) die(ctx, "mi_decode_margins", st);
+            n_out = mi_model_last_count(model);
+            if ((st = mi_decode_margins(ctx, model, n_out, margin.data()))) die(ctx, "mi_decode_margins", st);
             ttft = since();
-            dms = n_gen > 1 ? ms * (n_gen - 1) / n_gen : 0.0;
-            for (int i = 0; i < n_gen; i++) printf("%d ", gen[i]);
+            dms = n_out > 1 ? ms * (n_out - 1) / n_out : 0.0;
+            for (int i = 0; i < n_out; i++) emit(gen[i]);
             printf("\n");
         }
-        n_steps = n_gen;
+        n_steps = n_out;
         float minm = 1e30f; int mi = 0;
-        for (int i = 0; i < n_gen; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
-        const int timed = n_gen - 1;
+        for (int i = 0; i < n_out; i++) if (margin[i] < minm) { minm = margin[i]; mi = i; }
+        const int timed = n_out - 1;
         fprintf(stderr, "minfer-%s decode: %d tok in %.1f ms = %.2f tok/s | first token after %.1f ms (prompt %d) | min logit margin %.4f at #%d\n", tag, timed,
                 dms, dms > 0 ? timed * 1e3 / dms : 0.0, ttft, P, minm, mi);
         if (timed > 0 && dms > 0) {
-            const double bytes = (double)c.q4_weight_bytes_per_token + (double)c.kv_bytes_per_position * (P + n_gen / 2.0);
+            const double bytes = (double)c.q4_weight_bytes_per_token + (double)c.kv_bytes_per_position * (P + n_out / 2.0);
             fprintf(stderr, "minfer-%s: %.1f us/token, %.0f GB/s of weight + KV bytes (%.1f MB/token)\n", tag, dms * 1e3 / timed,
                     bytes * timed / (dms * 1e-3) / 1e9, bytes / 1e6);
         }
     }
     if (n_steps > 0)
         fprintf(stderr, "minfer-%s: %lld generation steps, %.2f tokens/step | drafted %lld, accepted %lld (%.0f%%)%s\n", tag, n_steps,
-                (double)n_gen / n_steps, n_drafted, n_accepted, n_drafted ? 100.0 * n_accepted / n_drafted : 0.0, spec ? "" : " [SPEC=0]");
+                (double)n_out / n_steps, n_drafted, n_accepted, n_drafted ? 100.0 * n_accepted / n_drafted : 0.0, spec ? "" : " [SPEC=0]");
     if (getenv("SEGMENTS") && !stamp.empty()) {                      // tok/s over consecutive windows: the slope with depth
         const int w = atoi(getenv("SEGMENTS"));
-        for (int i = 0; w > 0 && i + w < n_gen; i += w)
+        for (int i = 0; w > 0 && i + w < n_out; i += w)
             fprintf(stderr, "  tokens %4d-%4d (pos %4d): %.1f tok/s\n", i, i + w, P + i, w * 1e9 / (double)(stamp[i + w] - stamp[i]));
     }
     if (env_int("PROFILE", 0)) {
@@ -236,7 +264,7 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         }
     }
     if (getenv("MARGINS") && !margin.empty())
-        for (int i = 0; i < n_gen; i++) fprintf(stderr, "%d:%d:%.4f%c", i, gen[i], margin[i], i + 1 < n_gen ? ' ' : '\n');
+        for (int i = 0; i < n_out; i++) fprintf(stderr, "%d:%d:%.4f%c", i, gen[i], margin[i], i + 1 < n_out ? ' ' : '\n');
     mi_model_free(ctx, model);
     mi_ctx_destroy(ctx);
     return 0;

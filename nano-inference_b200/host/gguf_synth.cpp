@@ -6,7 +6,7 @@
 //   gguf_synth <out.gguf> --preset {tiny|0.5b|1.5b|3b} [--seed S] [--std 0.02]
 //              [--bias-std 0.02] [--norm-std 0] [--layers L --embd E --ff F
 //              --heads H --kv-heads K --vocab V]
-//              [--emb-type T] [--head-type T] [--down-type T] [--untied]
+//              [--emb-type T] [--head-type T] [--down-type T] [--untied] [--eos ID]
 //
 // The last four make files shaped like published ones, which store the token embedding, the lm_head and ffn_down in
 // other block formats (T = 2 Q4_0, 3 Q4_1, 8 Q8_0, 14 Q6_K).  --untied (implied when the head and embedding types
@@ -16,7 +16,10 @@
 // src/gguf.h:183-222).  Metadata keys and tensor names are the ones the
 // reference drivers look up (src/cpu_infer.cpp:71-98).  The vocabulary size is
 // the length of tokenizer.ggml.tokens (src/cpu_infer.cpp:79), so V placeholder
-// strings are written.  The lm_head is tied: the same q4_0 bytes are stored as
+// strings are written: token b < 256 is the byte-level BPE spelling of byte b (so that
+// a detokenizer has every byte to decode), token i >= 256 is "t<i>" preceded by the
+// spelling of a space.  tokenizer.ggml.eos_token_id is V-1 unless --eos says
+// otherwise.  The lm_head is tied: the same q4_0 bytes are stored as
 // token_embd.weight and as output.weight, which cpu_infer requires to exist
 // (src/cpu_infer.cpp:85).
 //
@@ -223,7 +226,7 @@ int main(int argc, char** argv) {
     }
     Shape sh{2, 128, 256, 4, 2, 512};
     uint64_t seed = 1234; float wstd = 0.02f, bstd = 0.02f, nstd = 0.f;
-    uint32_t emb_type = 2, head_type = 2, down_type = 2; bool untied = false;
+    uint32_t emb_type = 2, head_type = 2, down_type = 2; bool untied = false; int eos = -1;
     auto block_type = [&](const char* v) -> uint32_t {
         const int t = atoi(v);
         if (t != 2 && t != 3 && t != 8 && t != 14) { fprintf(stderr, "gguf_synth: block type %d is not one of 2, 3, 8, 14\n", t); exit(1); }
@@ -254,6 +257,7 @@ int main(int argc, char** argv) {
         else if (a == "--head-type") head_type = block_type(next());
         else if (a == "--down-type") down_type = block_type(next());
         else if (a == "--untied") untied = true;
+        else if (a == "--eos") eos = atoi(next());
         else { fprintf(stderr, "unknown option %s\n", a.c_str()); return 1; }
     }
     if (sh.embd % 32 || sh.ff % 32 || sh.embd % sh.heads || sh.heads % sh.kv_heads) {
@@ -312,9 +316,21 @@ int main(int argc, char** argv) {
     w.kv_u32("qwen2.attention.head_count_kv", (uint32_t)sh.kv_heads);
     w.kv_f32("qwen2.rope.freq_base", 1e6f);
     w.kv_f32("qwen2.attention.layer_norm_rms_epsilon", 1e-6f);
-    w.kv_u32("tokenizer.ggml.eos_token_id", (uint32_t)(sh.vocab - 1));
+    w.kv_u32("tokenizer.ggml.eos_token_id", (uint32_t)(eos >= 0 && eos < sh.vocab ? eos : sh.vocab - 1));
     w.s("tokenizer.ggml.tokens"); w.v<uint32_t>(9); w.v<uint32_t>(8); w.v<uint64_t>((uint64_t)sh.vocab);
-    for (int i = 0; i < sh.vocab; i++) w.s("t" + std::to_string(i));
+    // byte-level BPE alphabet: printable non-space Latin-1 bytes spell themselves, the other 68 bytes take code points 256..
+    auto spell = [](int byte) {
+        int cp = byte, next = 256;
+        for (int b = 0; b <= byte; b++) {
+            const bool self = (b >= 0x21 && b <= 0x7E) || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
+            if (!self) { if (b == byte) cp = next; next++; }
+        }
+        std::string u;
+        if (cp < 0x80) u.push_back((char)cp);
+        else { u.push_back((char)(0xC0 | (cp >> 6))); u.push_back((char)(0x80 | (cp & 0x3F))); }
+        return u;
+    };
+    for (int i = 0; i < sh.vocab; i++) w.s(i < 256 ? spell(i) : spell(' ') + "t" + std::to_string(i));
     for (auto& t : ts) {
         w.s(t.name);
         if (t.rows == 1) { w.v<uint32_t>(1); w.v<uint64_t>((uint64_t)t.cols); }

@@ -24,6 +24,7 @@ class GgufReader:
         self.pos = 0
         self.meta = {}
         self.n_tokens = 0
+        self.tokens = []
         self.tensors = {}
         self._parse()
 
@@ -49,11 +50,15 @@ class GgufReader:
                 self.meta[key] = v
         elif vt == 9:
             et, n = self._rd("<I"), self._rd("<Q")
-            if key == "tokenizer.ggml.tokens" and et == 8:
+            keep = key == "tokenizer.ggml.tokens" and et == 8
+            if keep:
                 self.n_tokens = n
+                self.tokens = []
             for _ in range(n):
                 if et == 8:
                     ln = self._rd("<Q")
+                    if keep and n <= 65536:          # the pieces of small test vocabularies (bytes; large ones are only counted)
+                        self.tokens.append(bytes(self.mv[self.pos:self.pos + ln]))
                     self.pos += ln
                 else:
                     self._value(et, "")

@@ -158,3 +158,75 @@ def test_ring_delivers_the_tokens_of_a_plain_decode_while_the_kernel_runs(ctx, p
     with pytest.raises(pkg.MinferError):
         m2.decode_run([1], 64, n + 8, ring)
     ring.free(); m.free(); m2.free()
+
+
+# ---- text mode: detokenized output and the end-of-sequence stop -------------------------------------------------------
+
+def _stream(path, prompt, n_gen):
+    g = gu.GgufReader(path)
+    return g, ou.OracleModel(g, act_q8=True, kv_f16=True, max_seq=len(prompt) + n_gen + 1).generate(prompt, n_gen)
+
+
+def test_stop_token_ends_every_engine_at_the_same_token(ctx, pkg, tmp_path):
+    """mi_model_set_stop_token: the run ends after the step that picks the token; forced positions never stop it."""
+    path = gu.make_synthetic(tmp_path / "s.gguf", "tiny", seed=21, std=0.1, extra=["--bias-std", 0.05])
+    prompt, n_gen = [3, 7, 100, 41], 24
+    g, want = _stream(path, prompt, n_gen)
+    k = 9                                               # stop at the 10th generated token's first occurrence
+    stop = want[k]
+    first = want.index(stop)
+    m = pkg.Model(ctx, path, max_seq=len(prompt) + n_gen + 1)
+    n_steps = len(prompt) + n_gen - 1
+    for mode in (pkg.DECODE_PERSISTENT, pkg.DECODE_PER_PHASE):
+        m.set_stop_token(stop)
+        out, _ = m.decode(prompt, n_steps, 0, None, mode)
+        assert m.last_count() == len(prompt) + first, "the step that produced the stop token is the last"
+        assert out[len(prompt) - 1:m.last_count()] == want[:first + 1]
+        # the cache and the position bookkeeping stay usable: the same call without the rule gives the whole stream
+        m.set_stop_token(-1)
+        out, _ = m.decode(prompt, n_steps, 0, None, mode)
+        assert m.last_count() == n_steps and out[len(prompt) - 1:] == want
+    # a forced position whose prediction equals the stop token does not end the run: force the whole stream
+    m.set_stop_token(stop)
+    seq = prompt + want[:-1]
+    out, _ = m.decode(seq, len(seq), 0, None, pkg.DECODE_PERSISTENT)
+    assert m.last_count() == len(seq) and out[len(prompt) - 1:] == want
+    # the speculative loop stops at the same token
+    got, st = m.generate_spec(prompt, n_gen)
+    assert m.last_count() == first + 1 and got[:first + 1] == want[:first + 1]
+    # a run that reports through the ring: its count is that of the stopped run
+    ring = pkg.TokenRing(ctx, n_steps)
+    m.decode_run(prompt, n_steps, 0, ring)
+    ctx.sync()
+    k, toks, _, _ = ring.peek()
+    assert k == len(prompt) + first and toks[len(prompt) - 1:] == want[:first + 1]
+    ring.free()
+    m.set_stop_token(-1)
+
+
+@pytest.mark.parametrize("exe", ["cuda_infer", "mega"])
+@pytest.mark.parametrize("spec", [0, 1])
+def test_text_mode_prints_pieces_and_stops_at_eos(tmp_path, pkg, exe, spec):
+    prompt, n_gen = [3, 7, 100, 41], 24
+    base = gu.make_synthetic(tmp_path / "a.gguf", "tiny", seed=21, std=0.1, extra=["--bias-std", 0.05])
+    g, want = _stream(base, prompt, n_gen)
+    eos = want[9]
+    first = want.index(eos)
+    path = gu.make_synthetic(tmp_path / "b.gguf", "tiny", seed=21, std=0.1, extra=["--bias-std", 0.05, "--eos", eos])
+    toks = gu.GgufReader(path).tokens
+    text = b"".join(pkg.detok_piece(toks[t]) for t in want[:first])          # the end-of-sequence piece is not printed
+
+    def run(**env):
+        e = dict(os.environ, WARMUP="1", SPEC=str(spec), **{k: str(v) for k, v in env.items()})
+        e.pop("RAWIDS", None)
+        r = subprocess.run([str(BIN / exe), str(path), str(n_gen), *[str(i) for i in prompt]], capture_output=True, env=e, timeout=300)
+        assert r.returncode == 0, r.stderr.decode()
+        return r.stdout, r.stderr.decode()
+
+    out, err = run()
+    assert out == text + b"\n"
+    m = re.search(r"(\d+) generation steps", err)
+    assert m and int(m.group(1)) <= first + 1
+    # with ids asked for, nothing stops early (src/mega.cu:1017: stop_eos = !raw_ids && !teacher)
+    out, _ = run(RAWIDS=1)
+    assert [int(t) for t in out.split()] == want
