@@ -621,11 +621,12 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     bool ok = true;
     if (addw) {
         unsigned aw[NB];
-        prof_mark(P, 23);
+        prof_mark(P, 27);
         ok = tw_poll(P, tag, valid, [&](int k) { return addw + (size_t)(warp + k * DNW) * 32 + lane; }, aw);
         prof_mark(P, kProfWait);
         #pragma unroll
         for (int k = 0; k < NB; k++) if (valid >> k & 1u) x[k] = __fadd_rn(x[k], __uint_as_float(aw[k]));
+        prof_mark(P, 28);
     }
     double ss = 0.0;
     #pragma unroll

@@ -217,8 +217,9 @@ def test_text_mode_prints_pieces_and_stops_at_eos(tmp_path, pkg, exe, spec):
     text = b"".join(pkg.detok_piece(toks[t]) for t in want[:first])          # the end-of-sequence piece is not printed
 
     def run(**env):
-        e = dict(os.environ, WARMUP="1", SPEC=str(spec), **{k: str(v) for k, v in env.items()})
+        e = dict(os.environ, WARMUP="1", SPEC=str(spec))
         e.pop("RAWIDS", None)
+        e.update({k: str(v) for k, v in env.items()})
         r = subprocess.run([str(BIN / exe), str(path), str(n_gen), *[str(i) for i in prompt]], capture_output=True, env=e, timeout=300)
         assert r.returncode == 0, r.stderr.decode()
         return r.stdout, r.stderr.decode()
