@@ -7,6 +7,8 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -14,7 +16,7 @@
 using namespace mi;
 
 namespace mi {
-const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G);
+const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); const void* decode_kernel_lean(int HD, int G);
 int reset_after_error(mi_ctx* ctx, mi_model* m);
 }
 
@@ -92,6 +94,11 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
         kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_tp(m->HD, m->G)));
     } else if (P.prof) {                            // the instrumented build (decode_prof.cu)
         kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_prof(m->HD, m->G)));
+    } else if (m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && lean_shape_ok(m->E, m->FF, m->NH * m->HD) &&
+               !getenv("MINFER_NO_LEAN")) {
+        // every step of this launch ends within the range the dedicated attention CTAs handle: the build without the other
+        // attention variants (decode_lean.cu)
+        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_lean(m->HD, m->G)));
     } else {
         #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
         MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
@@ -99,11 +106,15 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
     }
     if (!kern) return set_error(ctx, MI_ERR_UNSUPPORTED, "decode: head_dim %d with %d query heads per kv head is not instantiated", m->HD, m->G);
     // the opt-in shared-memory size is a property of (device, kernel): raise it whenever this model needs more than any before
-    static const void* attr_kern[16] = {nullptr};
-    static size_t attr_smem[16] = {0};
-    if (attr_kern[ctx->device & 15] != (const void*)kern || attr_smem[ctx->device & 15] < m->smem) {
-        MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem));
-        attr_kern[ctx->device & 15] = (const void*)kern; attr_smem[ctx->device & 15] = m->smem;
+    {
+        static std::mutex mu;
+        static std::map<std::pair<int, const void*>, size_t> raised;
+        std::lock_guard<std::mutex> lock(mu);
+        size_t& have = raised[{ctx->device, (const void*)kern}];
+        if (have < m->smem) {
+            MI_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->smem));
+            have = m->smem;
+        }
     }
     // Always a cooperative launch: CTAs wait for one another's tagged words inside every phase range (the K-split fold
     // of the down projection, the greedy pick over all CTAs' candidates), so all of them must be resident together.

@@ -65,25 +65,39 @@
 #ifndef MI_ATT_FN
 #define MI_ATT_FN static __device__ __noinline__
 #endif
+// functions that sit out of line to keep the loop body small; the short-context build inlines them instead, because every
+// call site inside the step loop, executed or not, makes the compiler keep the loop's values where a call preserves them
+#if defined(MI_LEAN) && MI_LEAN
+#define MI_COLD_FN static __device__ __forceinline__
+#else
+#define MI_COLD_FN static __device__ __noinline__
+#endif
 #ifndef MI_PIECE
 #define MI_PIECE __forceinline__
 #endif
 
-// The kernel exists in three builds.  The default one carries no profiling code and no peer stores.  A translation unit
+// The kernel exists in four builds.  The default one carries no profiling code and no peer stores.  A translation unit
 // that defines MI_PROF 1 before including this file gets the instrumented build (timer marks between the hot instructions
 // cost a few percent when merely compiled in); MI_TP 1 gives the tensor-parallel build, whose publishing stores also go to
-// the other GPUs.  The three live in different inline namespaces, so all can be linked into one library and picked at
-// launch time.
+// the other GPUs; MI_LEAN 1 gives the short-context build, which holds no attention code but that of the dedicated
+// attention CTAs (launched only for step ranges that end within kShortAttnMax positions on a model with such CTAs: without
+// the other attention variants in the same function the GEMV CTAs' loop keeps its values in registers).  They live in
+// different inline namespaces, so all can be linked into one library and picked at launch time.
 #ifndef MI_PROF
 #define MI_PROF 0
 #endif
 #ifndef MI_TP
 #define MI_TP 0
 #endif
+#ifndef MI_LEAN
+#define MI_LEAN 0
+#endif
 #if MI_PROF
 #define MI_KVARIANT prof
 #elif MI_TP
 #define MI_KVARIANT tpx
+#elif MI_LEAN
+#define MI_KVARIANT lean
 #else
 #define MI_KVARIANT fast
 #endif
@@ -294,7 +308,7 @@ struct Pub {
 
 // Poll one word until it carries `tag`.  Gives up (false) when the time budget has run out or another CTA has reported
 // an error; the caller then leaves the kernel through its error path.
-static __device__ __noinline__ bool tw_spin(const unsigned long long* p, unsigned tag, unsigned long long budget_ns, const int* err) {
+MI_COLD_FN bool tw_spin(const unsigned long long* p, unsigned tag, unsigned long long budget_ns, const int* err) {
     unsigned long long t0 = 0;
     for (unsigned it = 1;; it++) {
         if (tw_is(tw_ld(p), tag)) return true;
@@ -419,7 +433,7 @@ struct WarpStream {
 // 15 % faster once the four GEMV phases shared one copy of their code.  So the double-precision exponential has one
 // out-of-line copy, and the variants a given model never takes (other tile depths, other norm widths) sit out of line
 // instead of between the hot instructions.
-static __device__ __noinline__ double exp_shared(double x) { return exp(x); }
+MI_COLD_FN double exp_shared(double x) { return exp(x); }
 static __device__ __noinline__ double tile_dot_row_rare(int kb, const uint8_t* tile, int lane, int t, const int8_t* xq_s, const float2* xs_s, double acc) {
     switch (kb) {
         case 4: return tile_dot_row<4, false>(tile, lane, t * 4, xq_s, xs_s, acc, nullptr);
@@ -437,8 +451,12 @@ __device__ __forceinline__ double tile_consume(WarpStream& ws, int lane, int kb,
     if (!mbar_wait_bounded(&ws.bars[slot], (ws.consumed / DS) & 1)) { ok = false; return acc; }
     if (PP) prof_mark(*PP, 20);
     const uint8_t* tile = ws.ring + (size_t)slot * DSLOT;
+#if MI_LEAN
+    acc = tile_dot_row<8, false>(tile, lane, t * 8, xq_s, xs_s, acc, nullptr);          // lean_shape_ok(): every tile is 8 blocks deep
+#else
     if (kb == 8) acc = tile_dot_row<8, false>(tile, lane, t * 8, xq_s, xs_s, acc, nullptr);
     else acc = tile_dot_row_rare(kb, tile, lane, t, xq_s, xs_s, acc);
+#endif
     ws.consumed++;
     __syncwarp();
     if (PP) prof_mark(*PP, 21);
@@ -700,8 +718,12 @@ static __device__ __noinline__ bool stage_norm_q8_rare(MI_NORM_ARGS) {
     return stage_norm_q8_t<32, 8>(MI_NORM_PASS);
 }
 __device__ __forceinline__ bool stage_norm_q8u(MI_NORM_ARGS) {
+#if MI_LEAN
+    return stage_norm_q8_t<8, 8>(MI_NORM_PASS);                                         // lean_shape_ok(): 1024 < E <= 2048
+#else
     if (E > 1024 && E <= 2048) return stage_norm_q8_t<8, 8>(MI_NORM_PASS);
     return stage_norm_q8_rare(MI_NORM_PASS);
+#endif
 }
 
 // A q8_0 vector published as tagged words by other CTAs -> shared memory: int8 values, and per block {fp32 of the fp16
@@ -765,7 +787,18 @@ __device__ __forceinline__ bool stage_poll_q8(const DecodeParams& P, const unsig
     const int np = (q8_words(n) / 2 + DNT - 1) / DNT;
     if (np <= 1) return stage_poll_q8_t<1>(P, vw, n, tag, xq_s, xs_s);
     if (np <= 5) return stage_poll_q8_t<5>(P, vw, n, tag, xq_s, xs_s);
+#if MI_LEAN
+    return stage_poll_q8_t<8>(P, vw, n, tag, xq_s, xs_s);                               // lean_shape_ok(): at most 8 word pairs per thread
+#else
     return stage_poll_q8_rare(P, vw, n, tag, xq_s, xs_s);
+#endif
+}
+
+// Shapes the short-context build takes: it holds one variant of each prologue and of the tile loop and no call to the others.
+inline bool lean_shape_ok(int E, int FF, int NQ) {
+    auto kb8 = [](int n) { return (n / 32) % 8 == 0; };
+    auto np = [](int n) { return (q8_words(n) / 2 + DNT - 1) / DNT; };
+    return E > 1024 && E <= 2048 && kb8(E) && kb8(FF) && kb8(NQ) && np(FF) <= 8 && np(NQ) <= 8;
 }
 
 // ---- attention --------------------------------------------------------------------
@@ -1544,7 +1577,7 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
 #endif
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = pos_base + step;
-        if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }
+        if (pos < 0 || pos >= P.max_seq || (MI_LEAN && (pos + 1 > kShortAttnMax || P.attn_ctas == 0))) { ok = false; err_code = MI_ERR_LIMIT; break; }
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;
         if (P.stop_token >= 0 && step > step0 && step >= P.n_forced && ph0 == 0 && ph1 == nph) {
             // the stop rule: learn the token the previous step picked (its lm_head phase carries tag tag0 - 1)
@@ -1567,11 +1600,14 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
                 else if (step + 1 < step1 && ph0 <= 1) { nl = 0; np_ = pos + 1; }
                 apf = attention_dedicated<HD, G, attn_heads_per_cta<G>()>(P, l, pos, smem, apf, pub.tag - 1u, pub, nl, np_);
                 ok = apf.ok;
-            } else {
+            }
+#if !MI_LEAN
+            else {
                 if (apf.pending) { (void)mbar_wait_bounded(apf.bar, apf.parity); apf.parity ^= 1u; apf.pending = false; apf.layer = -1; }
                 if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
                 else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
             }
+#endif
             ok = __syncthreads_and(ok ? 1 : 0) != 0;
             prof_mark(P, 3);
         }
@@ -1674,7 +1710,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     __syncthreads();
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = pos_base + step;
-        if (pos < 0 || pos >= P.max_seq) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
+        if (pos < 0 || pos >= P.max_seq || (MI_LEAN && (pos + 1 > kShortAttnMax || P.attn_ctas == 0))) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;        // tag of (step, phase 0)
         if (step > step0 && ph1 != nph) { rope_table(pos); __syncthreads(); }     // (otherwise the previous step's lm_head phase has made the table)
         prof_mark(P, kProfStep);
@@ -1722,9 +1758,12 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
             if (k == 1) {
                 if (pos + 1 <= kShortAttnMax && P.attn_ctas > 0) {
                     // the attention CTAs' business
-                } else if (pos + 1 <= kShortAttnMax) ok = attention_short<HD, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+                }
+#if !MI_LEAN
+                else if (pos + 1 <= kShortAttnMax) ok = attention_short<HD, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
                 else if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
                 else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+#endif
             } else if (k != 5) {
                 const int jn = 4 * l + (k == 0 ? 0 : k == 2 ? 1 : k == 3 ? 2 : 3);
                 const float* bias = sm.lp[l].bqkv;
