@@ -17,6 +17,7 @@ using namespace mi;
 
 namespace mi {
 const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); const void* decode_kernel_lean(int HD, int G);
+const void* decode_kernel_prof_lean(int HD, int G);
 int reset_after_error(mi_ctx* ctx, mi_model* m);
 }
 
@@ -88,17 +89,29 @@ int plan_ks(int kind, int groups, int nt, int grid) {
     return std::max(1, std::min(std::min(ks, nt), kMaxKSplit));
 }
 
+// cos and sin of the rotary angles of every position: angle = fp32(pos * freq) as src/cpu_infer.cpp:54, then the double
+// cosine / sine rounded to fp32 once (the products of the rotation are formed in double by the QKV epilogue)
+__global__ void rope_cs_kernel(const float* __restrict__ freq, float* __restrict__ cs, int HD, int max_seq) {
+    const int pos = blockIdx.x, i = threadIdx.x;
+    if (pos >= max_seq || i >= HD / 2) return;
+    const double th = (double)__fmul_rn((float)pos, freq[i]);
+    cs[(size_t)pos * HD + i] = __double2float_rn(cos(th));
+    cs[(size_t)pos * HD + HD / 2 + i] = __double2float_rn(sin(th));
+}
+
 int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
     void (*kern)(DecodeParams, int, int, int, int) = nullptr;
+    // every step of this launch ends within the range the dedicated attention CTAs handle, on a shape the short-context
+    // build takes: that build has no other attention variant in it (decode_lean.cu)
+    const bool lean = m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && lean_shape_ok(m->E, m->FF, m->NH * m->HD) &&
+                      !getenv("MINFER_NO_LEAN");
+    auto as_kernel = [](const void* p) { return reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(p)); };
     if (P.tp.on) {                                  // the build with the exchange between GPUs inside (decode_tp.cu)
-        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_tp(m->HD, m->G)));
-    } else if (P.prof) {                            // the instrumented build (decode_prof.cu)
-        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_prof(m->HD, m->G)));
-    } else if (m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && lean_shape_ok(m->E, m->FF, m->NH * m->HD) &&
-               !getenv("MINFER_NO_LEAN")) {
-        // every step of this launch ends within the range the dedicated attention CTAs handle: the build without the other
-        // attention variants (decode_lean.cu)
-        kern = reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(decode_kernel_lean(m->HD, m->G)));
+        kern = as_kernel(decode_kernel_tp(m->HD, m->G));
+    } else if (P.prof) {                            // the instrumented builds (decode_prof.cu, decode_prof_lean.cu)
+        kern = as_kernel(lean ? decode_kernel_prof_lean(m->HD, m->G) : decode_kernel_prof(m->HD, m->G));
+    } else if (lean) {
+        kern = as_kernel(decode_kernel_lean(m->HD, m->G));
     } else {
         #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
         MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
@@ -404,6 +417,10 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     float* d_freq; if ((st = dev_alloc(ctx, m, &d_freq, freq.size()))) return st;
     MI_CUDA(ctx, cudaMemcpy(d_freq, freq.data(), freq.size() * 4, cudaMemcpyHostToDevice));
     P.rope_freq = d_freq;
+    float* d_cs; if ((st = dev_alloc(ctx, m, &d_cs, (size_t)max_seq * HD, false))) return st;
+    rope_cs_kernel<<<max_seq, HD / 2, 0, ctx->stream>>>(d_freq, d_cs, HD, max_seq);
+    MI_CUDA(ctx, cudaGetLastError());
+    P.rope_cs = d_cs;
     P.stop_token = -1;
 
     // ---- state

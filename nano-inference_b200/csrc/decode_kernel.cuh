@@ -92,7 +92,9 @@
 #ifndef MI_LEAN
 #define MI_LEAN 0
 #endif
-#if MI_PROF
+#if MI_PROF && MI_LEAN
+#define MI_KVARIANT proflean
+#elif MI_PROF
 #define MI_KVARIANT prof
 #elif MI_TP
 #define MI_KVARIANT tpx
@@ -169,6 +171,7 @@ struct DecodeParams {
     const LayerPtrs* layers;         // [L]
     const float* out_norm;
     const float* rope_freq;          // [HD/2]: base^(-2i/HD), computed on the host with powf
+    const float* rope_cs;            // [max_seq][HD]: cos then sin of every position's HD/2 angles, made once at load (rope_cs_kernel)
     const uint8_t* emb_base;         // tiled token embedding (may alias the lm_head)
     int emb_nt, emb_kb;
     const uint8_t* emb_q8;           // or, when set: the embedding as stored Q8_0 rows (34-byte blocks), read instead of emb_base
@@ -1695,11 +1698,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     const int cand_world = P.tp.on ? P.tp.world : 1, n_cand = cand_world * ws.ggrid;
     const int my_cand = P.xo.cand + ((P.tp.on ? P.tp.rank : 0) * ws.ggrid + ws.gcta) * 4;
 
-    auto rope_table = [&](int pos) {                   // cos / sin of this position's angles, fp32 angle as src/cpu_infer.cpp:54
-        if (tid < HD / 2) {
-            const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + tid));
-            sm.cs[tid] = __double2float_rn(cos(th)); sm.cs[HD / 2 + tid] = __double2float_rn(sin(th));
-        }
+    // cos / sin of a position's angles come from the table made at load: the double-precision cosine and sine and their
+    // argument reduction stay out of this function (as code, and as calls inside the step loop)
+    auto rope_table = [&](int pos) {
+        if (tid < HD) sm.cs[tid] = __ldg(P.rope_cs + (size_t)min(max(pos, 0), P.max_seq - 1) * HD + tid);
     };
 
 #if MI_PROF
