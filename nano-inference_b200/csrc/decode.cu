@@ -18,6 +18,7 @@ using namespace mi;
 namespace mi {
 const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); const void* decode_kernel_lean(int HD, int G);
 const void* decode_kernel_prof_lean(int HD, int G);
+const void* decode_kernel_tp_lean(int HD, int G);
 int reset_after_error(mi_ctx* ctx, mi_model* m);
 }
 
@@ -107,7 +108,7 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
                       !getenv("MINFER_NO_LEAN");
     auto as_kernel = [](const void* p) { return reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(p)); };
     if (P.tp.on) {                                  // the build with the exchange between GPUs inside (decode_tp.cu)
-        kern = as_kernel(decode_kernel_tp(m->HD, m->G));
+        kern = as_kernel(lean ? decode_kernel_tp_lean(m->HD, m->G) : decode_kernel_tp(m->HD, m->G));
     } else if (P.prof) {                            // the instrumented builds (decode_prof.cu, decode_prof_lean.cu)
         kern = as_kernel(lean ? decode_kernel_prof_lean(m->HD, m->G) : decode_kernel_prof(m->HD, m->G));
     } else if (lean) {
@@ -299,6 +300,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
         if (force) jb.ks = std::max(1, std::min(std::min(atoi(force), jb.nt), kMaxKSplit));
         if (jb.ks >= GG) jb.ks = std::max(1, GG - 1);       // the CTAs of a row group's splits must be distinct
         jb.n_units = jb.groups * jb.ks;
+        jb.ks_inv = (unsigned)(((1ull << 32) + (unsigned)jb.ks - 1) / (unsigned)jb.ks);    // ks == 1: 2^32 wraps to 0, and that path does not divide
         if (kind == JOB_LM) { jb.rot = 0; jb.wrot = 0; }
         else {
             // successive jobs start where the previous one stopped, over CTAs and over the warps of a CTA

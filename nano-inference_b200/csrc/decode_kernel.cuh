@@ -96,6 +96,8 @@
 #define MI_KVARIANT proflean
 #elif MI_PROF
 #define MI_KVARIANT prof
+#elif MI_TP && MI_LEAN
+#define MI_KVARIANT tpxlean
 #elif MI_TP
 #define MI_KVARIANT tpx
 #elif MI_LEAN
@@ -128,7 +130,7 @@ struct Job {
     int n_units;           // groups * ks
     int rot;               // CTA (per-layer jobs) or warp slot (lm_head) that gets unit 0
     int wrot;              // warp that gets tile 0 of a CTA unit
-    int pad0_;
+    unsigned ks_inv;       // ceil(2^32 / ks): x / ks == __umulhi(x, ks_inv) for the unit and tile counts that occur (set by the host)
     int layer;
     int g_off;             // first unit group this GPU owns (tensor parallelism; base points at it, groups counts the owned ones)
     int pad_;
@@ -370,9 +372,10 @@ __device__ __forceinline__ UnitShape unit_shape(const Job& jb, int u, int uidx) 
     UnitShape s;
     if (jb.ks == 1) { s.g = u; s.sp = 0; s.t0 = 0; s.ntu = jb.nt; }
     else {
-        s.g = u / jb.ks; s.sp = u - s.g * jb.ks;
-        s.t0 = s.sp * jb.nt / jb.ks;                      // all operands are small: 32-bit is exact
-        s.ntu = (s.sp + 1) * jb.nt / jb.ks - s.t0;
+        // divisions by the K-split count through the host's reciprocal: exact for operands below 2^20 with ks <= kMaxKSplit
+        s.g = (int)__umulhi((unsigned)u, jb.ks_inv); s.sp = u - s.g * jb.ks;
+        s.t0 = (int)__umulhi((unsigned)(s.sp * jb.nt), jb.ks_inv);
+        s.ntu = (int)__umulhi((unsigned)((s.sp + 1) * jb.nt), jb.ks_inv) - s.t0;
     }
     s.n = jb.nacc * s.ntu;
     s.wrot = (jb.wrot + uidx * 3) & (DNW - 1);      // uidx: how many units this CTA had before u in the job
@@ -424,7 +427,7 @@ struct WarpStream {
         for (int k = consumed; k < issued; k++) (void)mbar_wait_bounded(&bars[k % DS], (k / DS) & 1);
     }
     __device__ __forceinline__ int first_cta_unit(const Job& jb) const {
-        const int G = ggrid, r = jb.rot % G, b = gcta;
+        const int G = ggrid, r = jb.rot, b = gcta;         // the host keeps rot below the number of GEMV CTAs
         return b >= r ? b - r : b + G - r;
     }
     __device__ __forceinline__ int first_warp_unit(const Job& jb) const {
@@ -603,8 +606,10 @@ __device__ __forceinline__ int quant_block_warp(float v, int lane, float2* xs_ou
 // block sum fold over 32/EPL lanes with log2(32/EPL) shuffles.  (One element per thread and warp-wide REDUX reductions,
 // twelve per warp at the 1.5B shape, measured 1500 cycles for the quantizer alone: the reduction unit, not the
 // arithmetic, set the time.)  Sum of squares in double (every x*x is exact there).
+// h_s must hold the residual stream already (residual_init below puts the embedding row, or the copy committed to global
+// memory, there with this same thread mapping, so no barrier is needed in between).
 template <int NB, int EPL>
-__device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token,
+__device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_s,
                                                 const unsigned long long* addw, unsigned tag, float* commit, const float* __restrict__ w,
                                                 int E, float eps, double* red, int8_t* xq_s, float2* xs_s) {
     constexpr int LPB = 32 / EPL;                        // lanes per block while quantizing
@@ -621,23 +626,7 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     for (int k = 0; k < NB; k++) {
         const int b = min(warp + k * DNW, nb - 1), e = b * 32 + lane;      // clamped: every address is valid
         if (warp + k * DNW < nb) valid |= 1u << k;
-        x[k] = embed ? 0.f : (gsrc ? __ldcg(gsrc + e) : h_s[e]);
-    }
-    if (embed) {                                                 // layer 0: the embedding row, value (nibble - 8) * d (src/gguf.h:94-102)
-        #pragma unroll
-        for (int k = 0; k < NB; k++) {
-            const int b = min(warp + k * DNW, nb - 1);
-            if (P.emb_q8) {                                      // a Q8_0 row as stored: int8 * d (src/gguf.h:112-118; src/mega.cu:639-642)
-                const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + b) * 34;
-                x[k] = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
-                continue;
-            }
-            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
-            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
-            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
-            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
-            x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
-        }
+        x[k] = h_s[e];
     }
     bool ok = true;
     if (addw) {
@@ -708,9 +697,33 @@ __device__ __forceinline__ bool stage_norm_q8_t(const DecodeParams& P, float* h_
     return true;
 }
 
-#define MI_NORM_ARGS const DecodeParams& P, float* h_s, const float* gsrc, bool embed, int token, const unsigned long long* addw, unsigned tag, \
+// The residual stream into this CTA's shared memory, where a step or a launch begins: the embedding row of `token`
+// (value (nibble - 8) * d, src/gguf.h:94-102; or a Q8_0 row as stored, int8 * d, src/gguf.h:112-118 and src/mega.cu:639-642),
+// or the copy the first GEMV CTA committed to global memory (a launch that starts in mid-step).  Thread mapping of the norm
+// prologue's gathering pass: each thread later reads only what it wrote here.
+__device__ __forceinline__ void residual_init(const DecodeParams& P, float* h_s, const float* gsrc, int token, int E) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nb = E / 32;
+    for (int b = warp; b < nb; b += DNW) {
+        const int e = b * 32 + lane;
+        float x;
+        if (gsrc) x = __ldcg(gsrc + e);
+        else if (P.emb_q8) {
+            const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + b) * 34;
+            x = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
+        } else {
+            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
+            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
+            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
+            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
+            x = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
+        }
+        h_s[e] = x;
+    }
+}
+
+#define MI_NORM_ARGS const DecodeParams& P, float* h_s, const unsigned long long* addw, unsigned tag, \
                      float* commit, const float* __restrict__ w, int E, float eps, double* red, int8_t* xq_s, float2* xs_s
-#define MI_NORM_PASS P, h_s, gsrc, embed, token, addw, tag, commit, w, E, eps, red, xq_s, xs_s
+#define MI_NORM_PASS P, h_s, addw, tag, commit, w, E, eps, red, xq_s, xs_s
 // blocks per warp while gathering (NB) and elements per thread while quantizing (EPL: the largest of 8, 4, 2, 1 with
 // which 256 threads cover the vector, 8 in several rounds beyond 2048 elements)
 static __device__ __noinline__ bool stage_norm_q8_rare(MI_NORM_ARGS) {
@@ -1417,53 +1430,38 @@ __device__ __forceinline__ AttnPrefetch attention_dedicated(const DecodeParams& 
     prof_mark(P, 27);
     const float inv = __fdiv_rn(1.f, __fsqrt_rn((float)HD));
     const int a0 = (int)((long long)Lp * warp / DNW), a1 = (int)((long long)Lp * (warp + 1) / DNW), np = a1 - a0;
-    // pass 1: four positions per sweep, eight lanes per position; one conversion of the K row serves all heads.  The lane's
-    // slice of every head's q sits in registers for all sweeps: read from shared memory per sweep, the 16-byte broadcast
-    // loads (512 bytes written back per warp instruction) were the larger half of this pass.
-    {
-        const int sub = lane >> 3, li = lane & 7;
-        double qr[HPC][DPL];
+    // pass 1: thread = position (the range is at most 256 rows).  A thread walks its K row front to back, one fp16 ->
+    // double conversion of an element serving all heads, and adds the products in dimension order with one accumulator
+    // per head: the oracle's own order of this sum.  q comes as 16-byte broadcast loads (every lane reads the same address);
+    // rows are 16 bytes longer than their data, so the eight lanes of a quarter warp cover all banks.  (Eight lanes per
+    // position with a shuffle tree per sweep measured 1.8 us per layer at a hundred positions: the conversions and the
+    // tree of every sweep were serial.)
+    if (warp * 32 < Lp) {
+        const uint4* kr = reinterpret_cast<const uint4*>(Kb + (size_t)min(tid, Lp - 1) * RSB);
+        double acc[HPC];
         #pragma unroll
-        for (int j = 0; j < HPC; j++) {
-            const double* qj = qs + (j * LPP + li) * QSTR;
+        for (int j = 0; j < HPC; j++) acc[j] = 0.0;
+        #pragma unroll 2
+        for (int c = 0; c < HD / 8; c++) {
+            const uint4 kk = kr[c];
+            const __half2* hh = reinterpret_cast<const __half2*>(&kk);
+            double kd[8];
             #pragma unroll
-            for (int e = 0; e < DPL; e += 2) { const double2 qq = *reinterpret_cast<const double2*>(qj + e); qr[j][e] = qq.x; qr[j][e + 1] = qq.y; }
-        }
-        #pragma unroll 1
-        for (int s0 = 0; s0 * 4 < np; s0++) {
-            const int pi = s0 * 4 + sub;
-            const uint4* kr = reinterpret_cast<const uint4*>(Kb + (size_t)(a0 + min(pi, np - 1)) * RSB + li * DPL * 2);
-            double kd[DPL];
-            if constexpr (DPL >= 8) {
-                #pragma unroll
-                for (int c = 0; c < KV4; c++) {
-                    const uint4 kk = kr[c];
-                    const __half2* hh = reinterpret_cast<const __half2*>(&kk);
-                    #pragma unroll
-                    for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hh[e]); kd[c * 8 + 2 * e] = (double)f.x; kd[c * 8 + 2 * e + 1] = (double)f.y; }
-                }
-            } else {
-                const uint2 kk = *reinterpret_cast<const uint2*>(kr);
-                const __half2* hh = reinterpret_cast<const __half2*>(&kk);
-                #pragma unroll
-                for (int e = 0; e < DPL / 2; e++) { const float2 f = __half22float2(hh[e]); kd[2 * e] = (double)f.x; kd[2 * e + 1] = (double)f.y; }
-            }
-            double acc[HPC];
+            for (int e = 0; e < 4; e++) { const float2 f = __half22float2(hh[e]); kd[2 * e] = (double)f.x; kd[2 * e + 1] = (double)f.y; }
             #pragma unroll
             for (int j = 0; j < HPC; j++) {
-                double a = 0.0;
                 #pragma unroll
-                for (int e = 0; e < DPL; e++) a = __fma_rn(qr[j][e], kd[e], a);
-                acc[j] = a;
+                for (int e = 0; e < 8; e += 2) {
+                    const int d = c * 8 + e;
+                    const double2 qq = *reinterpret_cast<const double2*>(qs + (j * LPP + d / DPL) * QSTR + d % DPL);
+                    acc[j] = __fma_rn(qq.x, kd[e], acc[j]);
+                    acc[j] = __fma_rn(qq.y, kd[e + 1], acc[j]);
+                }
             }
+        }
+        if (tid < Lp) {
             #pragma unroll
-            for (int sft = 1; sft <= 4; sft <<= 1)
-                #pragma unroll
-                for (int j = 0; j < HPC; j++) acc[j] = __dadd_rn(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], sft));
-            if (li == 0 && pi < np) {
-                #pragma unroll
-                for (int j = 0; j < HPC; j++) sc[j * kAttnRows + a0 + pi] = __fmul_rn(__double2float_rn(acc[j]), inv);
-            }
+            for (int j = 0; j < HPC; j++) sc[j * kAttnRows + tid] = __fmul_rn(__double2float_rn(acc[j]), inv);
         }
     }
     __syncthreads();
@@ -1731,11 +1729,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 // GU  : h = h + O projection                                                 (committed as h_mid)
                 // LM  : final norm over h + last down projection
                 const float* gsrc = nullptr; const unsigned long long* addw = nullptr; float* commit = nullptr; const float* nw = nullptr;
-                int tok = 0; bool embed = false;
                 if (k == 0 && l == 0) {
-                    embed = true;
-                    tok = step < P.n_forced ? __ldg(P.in_tokens + step) : (step == step0 ? __ldcg(P.cur_token) : s_tok);
+                    int tok = step < P.n_forced ? __ldg(P.in_tokens + step) : (step == step0 ? __ldcg(P.cur_token) : s_tok);
                     tok = min(max(tok, 0), P.V - 1);
+                    residual_init(P, sm.h, nullptr, tok, P.E);
                     commit = P.h_in; nw = sm.lp[0].attn_norm;
                 } else if (k == 0) {
                     gsrc = h_valid ? nullptr : P.h_mid; addw = P.xw + P.xo.down; commit = P.h_in; nw = sm.lp[l].attn_norm;
@@ -1744,7 +1741,10 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 } else {
                     gsrc = h_valid ? nullptr : P.h_mid; addw = P.xw + P.xo.down; nw = P.out_norm;
                 }
-                ok = stage_norm_q8u(P, sm.h, gsrc, embed, tok, addw, pub.tag - 1u, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s);
+                if (gsrc) residual_init(P, sm.h, gsrc, 0, P.E);                 // a launch that starts in mid-step
+                // the committed copy serves launches that start in mid-step (and state read-back); a launch over whole steps has no reader for it
+                if (MI_LEAN && ph0 == 0 && ph1 == nph) commit = nullptr;
+                ok = stage_norm_q8u(P, sm.h, addw, pub.tag - 1u, commit, nw, P.E, P.eps, sm.red, xq_s, xs_s);
                 h_valid = true;
                 prof_mark(P, 2 * k);
             } else if (k == 2 || k == 4) {

@@ -1,0 +1,15 @@
+// The tensor-parallel form of the short-context build (see decode_lean.cu and decode_tp.cu).
+#define MI_TP 1
+#define MI_LEAN 1
+#include "decode_kernel.cuh"
+
+namespace mi {
+
+const void* decode_kernel_tp_lean(int HD, int G) {
+    #define MI_PICK(hd, g) if (HD == hd && G == g) return (const void*)decode_kernel<hd, g>;
+    MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
+    #undef MI_PICK
+    return nullptr;
+}
+
+}  // namespace mi
