@@ -703,7 +703,8 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
         launches = 1
-        engine = "persistent kernel (one cooperative launch for all timed steps; phases chained by tagged words, no grid barrier)"
+        engine = ("persistent kernel (one cooperative launch for all timed steps; phases chained by tagged words, no grid barrier); "
+                  "its short-context build, since every timed position lies within 256")
         parallelism = "single GPU"
     else:
         # tensor parallel: the large GEMV jobs row-sharded over the ranks, NCCL all-reduce of the (zero-padded) phase
