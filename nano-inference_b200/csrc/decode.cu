@@ -19,6 +19,8 @@ namespace mi {
 const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); const void* decode_kernel_lean(int HD, int G);
 const void* decode_kernel_prof_lean(int HD, int G);
 const void* decode_kernel_tp_lean(int HD, int G);
+const void* decode_kernel_lean_mid(int HD, int G);
+const void* decode_kernel_lean_long(int HD, int G);
 int reset_after_error(mi_ctx* ctx, mi_model* m);
 }
 
@@ -104,8 +106,8 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
     void (*kern)(DecodeParams, int, int, int, int) = nullptr;
     // every step of this launch ends within the range the dedicated attention CTAs handle, on a shape the short-context
     // build takes: that build has no other attention variant in it (decode_lean.cu)
-    const bool lean = m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && lean_shape_ok(m->E, m->FF, m->NH * m->HD) &&
-                      !getenv("MINFER_NO_LEAN");
+    const bool shape_ok = lean_shape_ok(m->E, m->FF, m->NH * m->HD) && !getenv("MINFER_NO_LEAN");
+    const bool lean = m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && shape_ok;
     auto as_kernel = [](const void* p) { return reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(p)); };
     if (P.tp.on) {                                  // the build with the exchange between GPUs inside (decode_tp.cu)
         kern = as_kernel(lean ? decode_kernel_tp_lean(m->HD, m->G) : decode_kernel_tp(m->HD, m->G));
@@ -113,6 +115,10 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
         kern = as_kernel(lean ? decode_kernel_prof_lean(m->HD, m->G) : decode_kernel_prof(m->HD, m->G));
     } else if (lean) {
         kern = as_kernel(decode_kernel_lean(m->HD, m->G));
+    } else if (shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kShortAttnMax && (long long)P.pos0 + step1 <= kPerHeadAttnMax) {
+        kern = as_kernel(decode_kernel_lean_mid(m->HD, m->G));       // every step within 257..kPerHeadAttnMax positions
+    } else if (shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax) {
+        kern = as_kernel(decode_kernel_lean_long(m->HD, m->G));      // every step beyond
     } else {
         #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
         MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)

@@ -79,7 +79,8 @@
 // The kernel exists in four builds.  The default one carries no profiling code and no peer stores.  A translation unit
 // that defines MI_PROF 1 before including this file gets the instrumented build (timer marks between the hot instructions
 // cost a few percent when merely compiled in); MI_TP 1 gives the tensor-parallel build, whose publishing stores also go to
-// the other GPUs; MI_LEAN 1 gives the short-context build, which holds no attention code but that of the dedicated
+// the other GPUs; MI_LEAN 2 and 3 are the same idea for 257..kPerHeadAttnMax positions (one query head per CTA and chunk) and
+// beyond (a whole GQA group per CTA and chunk): one attention variant each; MI_LEAN 1 gives the short-context build, which holds no attention code but that of the dedicated
 // attention CTAs (launched only for step ranges that end within kShortAttnMax positions on a model with such CTAs: without
 // the other attention variants in the same function the GEMV CTAs' loop keeps its values in registers).  They live in
 // different inline namespaces, so all can be linked into one library and picked at launch time.
@@ -100,6 +101,10 @@
 #define MI_KVARIANT tpxlean
 #elif MI_TP
 #define MI_KVARIANT tpx
+#elif MI_LEAN == 2
+#define MI_KVARIANT leanmid
+#elif MI_LEAN == 3
+#define MI_KVARIANT leanlong
 #elif MI_LEAN
 #define MI_KVARIANT lean
 #else
@@ -1562,6 +1567,19 @@ __device__ __forceinline__ AttnPrefetch attention_dedicated(const DecodeParams& 
 // at the top of the kernel, out of line: its registers and instructions are its own, and the CTAs that carry the GEMV phases
 // never see any of it (measured: an out-of-line call inside their per-layer loop, or this code inlined into it, costs the
 // GEMV phases 10 - 25 %).
+// whether this build holds the attention variant a position needs (the host picks the build by the launch's positions)
+__device__ __forceinline__ bool lean_regime_ok(int pos, int attn_ctas) {
+#if MI_LEAN == 1
+    return pos + 1 <= kShortAttnMax && attn_ctas > 0;
+#elif MI_LEAN == 2
+    return pos + 1 > kShortAttnMax && pos + 1 <= kPerHeadAttnMax;
+#elif MI_LEAN == 3
+    return pos + 1 > kPerHeadAttnMax;
+#else
+    return true;
+#endif
+}
+
 template <int HD, int G>
 static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int step0, int step1, int ph0, int ph1, uint8_t* smem, uint8_t* stage, uint64_t* bar) {
     const int nph = 5 * P.L + 1;
@@ -1578,7 +1596,7 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
 #endif
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = pos_base + step;
-        if (pos < 0 || pos >= P.max_seq || (MI_LEAN && (pos + 1 > kShortAttnMax || P.attn_ctas == 0))) { ok = false; err_code = MI_ERR_LIMIT; break; }
+        if (pos < 0 || pos >= P.max_seq || !lean_regime_ok(pos, P.attn_ctas)) { ok = false; err_code = MI_ERR_LIMIT; break; }
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;
         if (P.stop_token >= 0 && step > step0 && step >= P.n_forced && ph0 == 0 && ph1 == nph) {
             // the stop rule: learn the token the previous step picked (its lm_head phase carries tag tag0 - 1)
@@ -1594,6 +1612,7 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
 #if MI_TP
             pub.tp = &P.tp;
 #endif
+#if MI_LEAN <= 1
             if (pos + 1 <= kShortAttnMax) {
                 // where this CTA's next attention will be: the next layer of this step, or layer 0 of the next step
                 int nl = -1, np_ = pos;
@@ -1602,12 +1621,17 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
                 apf = attention_dedicated<HD, G, attn_heads_per_cta<G>()>(P, l, pos, smem, apf, pub.tag - 1u, pub, nl, np_);
                 ok = apf.ok;
             }
-#if !MI_LEAN
+#endif
+#if MI_LEAN == 0
             else {
                 if (apf.pending) { (void)mbar_wait_bounded(apf.bar, apf.parity); apf.parity ^= 1u; apf.pending = false; apf.layer = -1; }
                 if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
                 else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
             }
+#elif MI_LEAN == 2
+            ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
+#elif MI_LEAN == 3
+            ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, stage, pub.tag - 1u, pub);
 #endif
             ok = __syncthreads_and(ok ? 1 : 0) != 0;
             prof_mark(P, 3);
@@ -1710,7 +1734,7 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
     __syncthreads();
     for (int step = step0; step < step1 && ok; step++) {
         const int pos = pos_base + step;
-        if (pos < 0 || pos >= P.max_seq || (MI_LEAN && (pos + 1 > kShortAttnMax || P.attn_ctas == 0))) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
+        if (pos < 0 || pos >= P.max_seq || !lean_regime_ok(pos, P.attn_ctas)) { ok = false; err_code = MI_ERR_LIMIT; break; }   // the same on every CTA: nobody waits for anybody
         const unsigned tag0 = epoch + (unsigned)(step - step0) * (unsigned)nph + 1u;        // tag of (step, phase 0)
         if (step > step0 && ph1 != nph) { rope_table(pos); __syncthreads(); }     // (otherwise the previous step's lm_head phase has made the table)
         prof_mark(P, kProfStep);
@@ -1761,9 +1785,13 @@ decode_kernel(const __grid_constant__ DecodeParams P, int step0, int step1, int 
                 if (pos + 1 <= kShortAttnMax && P.attn_ctas > 0) {
                     // the attention CTAs' business
                 }
-#if !MI_LEAN
+#if MI_LEAN == 0
                 else if (pos + 1 <= kShortAttnMax) ok = attention_short<HD, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
                 else if (pos + 1 <= kPerHeadAttnMax) ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+                else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+#elif MI_LEAN == 2
+                else ok = attention_phase<HD, 1, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
+#elif MI_LEAN == 3
                 else ok = attention_phase<HD, G, G, true, false, true>(P, l, pos, sm.stage, pub.tag - 1u, pub);
 #endif
             } else if (k != 5) {

@@ -108,3 +108,37 @@ def test_config2_window_against_the_oracle(ctx, pkg, tmp_path):
             worst = max(worst, rel_err(lg[s].cpu().numpy(), lo))
     assert worst < 1e-3, f"logits deviate {worst:.2e}"
     m.free(); m2.free()
+
+
+@pytest.mark.parametrize("preset", ["1.5b", "3b"])
+def test_context_specific_builds_give_the_bits_of_the_general_build(ctx, pkg, tmp_path, monkeypatch, preset):
+    """The decode kernel is compiled once with every attention variant and once per context range with only that
+    range's variant (short: dedicated attention CTAs; 257..1024 positions; beyond).  Which one a launch gets depends on
+    its positions alone; the results must not: same tokens, same logits bits, also for a launch that straddles two
+    ranges and therefore runs on the general build."""
+    import torch
+    path = gu.make_synthetic(tmp_path / "m.gguf", preset, seed=99)
+    V = gu.GgufReader(path).config()["n_vocab"]
+    rng = np.random.default_rng(5)
+    n = 6
+    for pos0 in (40, 253, 300, 1020, 1100, 2500):
+        res = []
+        for general in (False, True):
+            if general:
+                monkeypatch.setenv("MINFER_NO_LEAN", "1")
+            else:
+                monkeypatch.delenv("MINFER_NO_LEAN", raising=False)
+            m = pkg.Model(ctx, path, 2600)
+            # the same arbitrary cache content for both runs
+            torch.manual_seed(pos0)
+            for name in ("kcache", "vcache"):
+                t = m.state_tensor(name).view(torch.float16)
+                t.copy_((torch.randn(t.numel(), device="cuda") * 0.5).to(torch.float16))
+            logits = torch.zeros((n, V), dtype=torch.float32, device="cuda")
+            toks = [int(t) for t in np.random.default_rng(pos0).integers(0, V, 2)]
+            out, _ = m.decode(toks, n, pos0, logits)
+            res.append((out, logits.cpu().numpy().copy()))
+            m.free()
+        assert res[0][0] == res[1][0], f"tokens differ at position {pos0}"
+        assert np.array_equal(res[0][1].view(np.uint32), res[1][1].view(np.uint32)), f"logits differ at position {pos0}"
+    monkeypatch.delenv("MINFER_NO_LEAN", raising=False)
