@@ -702,9 +702,11 @@ def run_ours(args, rank, world, local_rank):
             tok = out[0]
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-        launches = 1
-        engine = ("persistent kernel (one cooperative launch for all timed steps; phases chained by tagged words, no grid barrier); "
-                  "its short-context build, since every timed position lies within 256")
+        # the library starts a new launch where a run passes 256 or 1024 cached positions (each range has its own build of the kernel)
+        launches = 1 + sum(1 for edge in (256, 1024) if 0 < edge - pos0 < K)
+        engine = ("persistent kernel (one cooperative launch for all timed steps within a context range: up to 256, up to 1024 "
+                  "cached positions, beyond; phases chained by tagged words, no grid barrier); "
+                  + ("the short-context build, since every timed position lies within 256" if pos0 + K <= 256 else f"{launches} launch(es) here"))
         parallelism = "single GPU"
     else:
         # tensor parallel: the large GEMV jobs row-sharded over the ranks, NCCL all-reduce of the (zero-padded) phase

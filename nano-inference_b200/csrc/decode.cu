@@ -626,7 +626,24 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
     const int nph = 5 * m->L + 1;
     MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));
     if (mode == MI_DECODE_PERSISTENT) {
-        if ((st = dispatch_launch(ctx, m, P, 0, n_steps, 0, nph, true))) return st;
+        // One launch, or one per context range the steps pass through (up to kShortAttnMax positions, up to kPerHeadAttnMax,
+        // beyond): each range has a build of the kernel with only its attention variant (dispatch_launch picks by the
+        // launch's positions), a launch that straddles a boundary would fall back to the general build.  Under the stop
+        // rule the host cannot know whether an earlier launch ended the run, so the run stays one launch.
+        int cuts[4] = {0, 0, 0, n_steps}, nc = 1;
+        if (stop < 0 && !P.tp.on && lean_shape_ok(m->E, m->FF, m->NH * m->HD)) {
+            for (int edge : {kShortAttnMax, kPerHeadAttnMax}) {
+                const long long s = (long long)edge - pos0;            // first step whose position count exceeds the edge
+                if (s > cuts[nc - 1] && s < n_steps) cuts[nc++] = (int)s;
+            }
+        }
+        cuts[nc] = n_steps;
+        for (int i = 0; i < nc; i++) {
+            DecodeParams Ps = P;
+            if (Ps.logits) Ps.logits += (long long)cuts[i] * Ps.logits_stride;   // the kernel indexes logits and ring entries from its first step
+            Ps.ring.base += cuts[i];
+            if ((st = dispatch_launch(ctx, m, Ps, cuts[i], cuts[i + 1], 0, nph, true))) return st;
+        }
     } else if (mode == MI_DECODE_PER_PHASE) {
         for (int s = 0; s < n_steps; s++) {
             DecodeParams Ps = P;
