@@ -17,8 +17,8 @@
  *    named *_host are ordinary host memory.  Work is enqueued on the context's
  *    stream and is asynchronous unless stated otherwise.
  *  - There is no CPU fallback: without a usable CUDA device every call fails.
- *  - Device-side waits (bulk-copy barriers, grid barriers, peer flags) are
- *    bounded; when one gives up the kernel records MI_ERR_TIMEOUT in the
+ *  - Device-side waits (bulk-copy barriers, polls for another CTA's or GPU's
+ *    data, peer flags) are bounded; when one gives up the kernel records MI_ERR_TIMEOUT in the
  *    context's device error word, which mi_ctx_sync() reports.
  */
 #ifndef MINFER_B200_H
@@ -221,7 +221,7 @@ typedef struct mi_model_config {
 } mi_model_config;
 
 enum { MI_DECODE_PERSISTENT = 0,   /* one cooperative launch: all phases, layers and steps in one persistent kernel */
-       MI_DECODE_PER_PHASE = 1 };  /* the same kernel launched once per phase (plain stream order, no grid barrier) */
+       MI_DECODE_PER_PHASE = 1 };  /* the same kernel launched once per phase (stream order between the phases) */
 
 /* MI_STATE_H: residual stream at the input of the layer whose QKV phase ran last;
  * MI_STATE_H_MID: residual stream after the attention block of the layer whose gate/up phase ran last. */
@@ -230,7 +230,7 @@ enum { MI_STATE_H = 0, MI_STATE_Q = 1, MI_STATE_ATT = 2, MI_STATE_KCACHE = 3, MI
        MI_STATE_PROFILE = 7,
        MI_STATE_H_MID = 8 };  /* 32 x uint64 nanoseconds per phase part on CTA 0, filled when the model was loaded
                                  * with MINFER_PROFILE set in the environment: slots 2k / 2k+1 = staging / work of phase
-                                 * kind k (0 QKV, 1 attention, 2 O, 3 gate-up, 4 down, 5 lm_head), 12 = grid barrier,
+                                 * kind k (0 QKV, 1 attention, 2 O, 3 gate-up, 4 down, 5 lm_head), 12 = waiting for other CTAs' data,
                                  * 13 = per-step prologue.  The reference's PROFILE=1 (src/mega.cu:111-119). */
 
 /* Load a Qwen2-architecture GGUF file (metadata keys and tensor names
@@ -398,7 +398,7 @@ MI_API int mi_model_tp_region(const mi_model* model, int which, int layer, void*
  * waiting; the input token is the model's device-resident current token.  On a sharded model the
  * buffer a phase writes is zeroed first.  The caller interleaves its all-reduces on the same stream. */
 MI_API int mi_decode_launch(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
-/* The same range as ONE cooperative launch (grid barriers between the phases, as in the persistent loop): for a run of
+/* The same range as ONE cooperative launch (the phases chained inside the kernel, as in the persistent loop): for a run of
  * phases with no exchange between them - on a sharded model QKV, attention, O and gate/up of a layer. */
 MI_API int mi_decode_launch_fused(mi_ctx* ctx, mi_model* model, int pos, int phase_begin, int phase_end);
 /* Exchange through peer memory instead of a collective library: every process calls mi_tp_ipc_handles (192 bytes out:
@@ -409,7 +409,8 @@ MI_API int mi_decode_launch_fused(mi_ctx* ctx, mi_model* model, int pos, int pha
  * overall greedy token current.  Every GPU issues the same sequence of exchanges.  Same bits as the all-reduce path.
  * Once mi_tp_ipc_open has run, mi_decode(..., MI_DECODE_PERSISTENT, ...) works on the sharded model too - called with the
  * same arguments on every GPU, it runs the whole generation as one cooperative launch per GPU and does these exchanges
- * inside the kernel (CTA 0, between two grid barriers, bounded waits). */
+ * inside the kernel (every producing CTA stores its results into the peers' exchange blocks as well; consumers poll,
+ * bounded). */
 MI_API int mi_tp_ipc_handles(mi_ctx* ctx, mi_model* model, void* out_host);
 MI_API int mi_tp_ipc_open(mi_ctx* ctx, mi_model* model, const void* all_host);
 MI_API int mi_tp_exchange(mi_ctx* ctx, mi_model* model, int which, int layer);

@@ -29,8 +29,8 @@
 //
 // The residual stream lives in shared memory: every CTA adds the same projection
 // outputs to its own copy (the arithmetic is deterministic, all copies hold the
-// same bits), so it never travels.  CTA 0 also writes it to global memory for
-// launches that start in the middle of a step, and for inspection.
+// same bits), so it never travels.  The first GEMV CTA also writes it to global memory
+// for launches that start in the middle of a step, and for inspection.
 //
 // Work split.  Every GEMV phase is a "job" over a tiled q4_0 matrix.  For the
 // per-layer matrices a unit is (32-row group [gate/up: a pair of groups], K-split)

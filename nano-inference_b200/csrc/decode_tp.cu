@@ -1,6 +1,7 @@
 // The tensor-parallel build of the decode kernel: the persistent loop with the exchange with the other GPUs inside it
-// (peer memory over NVLink, CTA 0 between two grid barriers).  decode.cu launches these instantiations for a sharded model
-// whose peer buffers are mapped; the single-GPU build carries none of this code.
+// (every producing CTA stores its tagged words into the other GPUs' exchange blocks over NVLink as well as its own).
+// decode.cu launches these instantiations for a sharded model whose peer buffers are mapped; the single-GPU build
+// carries none of this code.
 #define MI_TP 1
 #include "decode_kernel.cuh"
 

@@ -245,8 +245,8 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         if (mi_model_state_ptr(model, MI_STATE_PROFILE, &p, &nb) == MI_OK && p) {
             unsigned long long pr[32];
             mi_memcpy_to_host(ctx, pr, p, sizeof pr);
-            // slots (csrc/decode_kernel.cuh): 2k = prologue of phase kind k, 2k+1 = its tail after the unit loop, 12 = grid
-            // barrier, 13 = step prologue, 14..16 = attention (q staging, scan, fold + merge), 18 / 19 = tile loops and
+            // slots (csrc/decode_kernel.cuh): 2k = prologue of phase kind k, 2k+1 = its tail after the unit loop, 12 = waiting
+            // for other CTAs' data, 13 = step prologue, 14..16 = attention (q staging, scan, fold + merge), 18 / 19 = tile loops and
             // fold + epilogue of the per-layer GEMV phases
             const char* ph[6] = {"P1 QKV", "P2 attention", "P3 Wo", "P4 gate/up", "P5 down", "lm_head"};
             const double steps = (double)(P + n_gen - 1 + env_int("WARMUP", 2));   // (with TCHUNK > 1 the prompt is not in the profile)
