@@ -428,7 +428,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     float* d_cs; if ((st = dev_alloc(ctx, m, &d_cs, (size_t)max_seq * HD, false))) return st;
     rope_cs_kernel<<<max_seq, HD / 2, 0, ctx->stream>>>(d_freq, d_cs, HD, max_seq);
     MI_CUDA(ctx, cudaGetLastError());
-    P.rope_cs = d_cs;
+    P.rope_cs = d_cs; P.rope_rows = max_seq;
     P.stop_token = -1;
 
     // ---- state

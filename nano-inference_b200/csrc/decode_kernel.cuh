@@ -178,7 +178,8 @@ struct DecodeParams {
     const LayerPtrs* layers;         // [L]
     const float* out_norm;
     const float* rope_freq;          // [HD/2]: base^(-2i/HD), computed on the host with powf
-    const float* rope_cs;            // [max_seq][HD]: cos then sin of every position's HD/2 angles, made once at load (rope_cs_kernel)
+    const float* rope_cs;            // [rope_rows][HD]: cos then sin of every position's HD/2 angles, made once at load (rope_cs_kernel)
+    int rope_rows;                   // = the model's max_seq at load
     const uint8_t* emb_base;         // tiled token embedding (may alias the lm_head)
     int emb_nt, emb_kb;
     const uint8_t* emb_q8;           // or, when set: the embedding as stored Q8_0 rows (34-byte blocks), read instead of emb_base

@@ -24,34 +24,49 @@ namespace {
 
 constexpr int VMAX = 16;
 
-// x = (embedding row | X) (+ Y), committed to X; q8_0(rmsnorm(x) * w) (src/cpu_infer.cpp:40-46)
+// x = (embedding row | X) (+ Y), committed to X; q8_0(rmsnorm(x) * w) (src/cpu_infer.cpp:40-46).
+// One CTA per token.  Gathering: warp w owns the blocks w, w+8, ... with lane = element, all loads of a round requested
+// before any is used (X is read and written here, so the compiler may not move a later load above an earlier store).
+// Quantizing: eight consecutive elements per thread, four lanes per q8_0 block, two shuffle folds for the block maximum.
 __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const int* __restrict__ tokens, bool embed, float* X, const float* Y,
                                                       int ystride, const float* __restrict__ w, int8_t* xq, __half* xd) {
-    extern __shared__ float xs[];
+    extern __shared__ __align__(16) float xs[];
     __shared__ double red[DNW];
     pdl_launch_dependents(); pdl_wait_prior();
     const int m = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, E = P.E, nb = E / 32;
     const int token = embed ? __ldg(tokens + m) : 0;
+    constexpr int RB = 8;                                            // blocks per warp and round
     double ss = 0.0;
-    for (int b = warp; b < nb; b += DNW) {
-        const int e = b * 32 + lane;
-        float x;
-        if (embed && P.emb_q8) {                                    // a Q8_0 row as stored: int8 * d (src/gguf.h:112-118)
-            const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + b) * 34;
-            x = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
-        } else if (embed) {                                         // value (nibble - 8) * d (src/gguf.h:94-102)
-            const int g = token >> 5, r = token & 31, kb = P.emb_kb, t = b / kb, kk = b % kb;
-            const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
-            const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
-            const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
-            x = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
-        } else {
-            x = X[(size_t)m * E + e];
+    for (int b0 = warp; b0 < nb; b0 += RB * DNW) {
+        float x[RB], y[RB];
+        #pragma unroll
+        for (int k = 0; k < RB; k++) {
+            const int b = b0 + k * DNW, e = min(b, nb - 1) * 32 + lane;
+            y[k] = Y ? Y[(size_t)m * ystride + e] : 0.f;
+            if (embed && P.emb_q8) {                                // a Q8_0 row as stored: int8 * d (src/gguf.h:112-118)
+                const uint8_t* bp = P.emb_q8 + ((size_t)token * nb + min(b, nb - 1)) * 34;
+                x[k] = __fmul_rn(__int2float_rn((int)(int8_t)__ldg(bp + 2 + lane)), __half2float(__ldg(reinterpret_cast<const __half*>(bp))));
+            } else if (embed) {                                     // value (nibble - 8) * d (src/gguf.h:94-102)
+                const int bb = min(b, nb - 1), g = token >> 5, r = token & 31, kb = P.emb_kb, t = bb / kb, kk = bb % kb;
+                const uint8_t* tile = P.emb_base + ((size_t)g * P.emb_nt + t) * (kb * kTileRowBytes);
+                const uint8_t byte = __ldg(tile + ((size_t)kk * 32 + r) * 16 + (lane & 15));
+                const float d = __half2float(__ldg(reinterpret_cast<const __half*>(tile + (size_t)kb * 512 + ((size_t)r * kb + kk) * 2)));
+                x[k] = __fmul_rn(__int2float_rn((lane < 16 ? (byte & 0x0F) : (byte >> 4)) - 8), d);
+            } else {
+                x[k] = X[(size_t)m * E + e];
+            }
         }
-        if (Y) x = __fadd_rn(x, Y[(size_t)m * ystride + e]);
-        X[(size_t)m * E + e] = x;
-        xs[e] = x;
-        const double xdv = x; ss = __fma_rn(xdv, xdv, ss);
+        #pragma unroll
+        for (int k = 0; k < RB; k++) {
+            const int b = b0 + k * DNW;
+            if (b < nb) {
+                const int e = b * 32 + lane;
+                const float v = Y ? __fadd_rn(x[k], y[k]) : x[k];
+                X[(size_t)m * E + e] = v;
+                xs[e] = v;
+                const double xdv = v; ss = __fma_rn(xdv, xdv, ss);
+            }
+        }
     }
     #pragma unroll
     for (int o = 16; o; o >>= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
@@ -62,10 +77,28 @@ __global__ void __launch_bounds__(DNT) vf_norm_quant(const DecodeParams P, const
     for (int v = 0; v < DNW; v++) tot = __dadd_rn(tot, red[v]);
     const float mean = __double2float_rn(__ddiv_rn(tot, (double)E));
     const float scale = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(mean, P.eps)));
-    for (int b = warp; b < nb; b += DNW) {
-        const int e = b * 32 + lane;
-        const float v = __fmul_rn(__fmul_rn(xs[e], scale), __ldg(w + e));
-        xq[(size_t)m * E + e] = (int8_t)quant_block_warp(v, lane, nullptr, xd + (size_t)m * nb + b);
+    for (int t = tid; (t & ~31) * 8 < E; t += DNT) {                 // warp-uniform trip count: the folds are warp-wide
+        const bool live = t * 8 < E;
+        const int e0 = live ? t * 8 : 0;
+        const float4 h0 = *reinterpret_cast<const float4*>(xs + e0), h1 = *reinterpret_cast<const float4*>(xs + e0 + 4);
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + e0)), w1 = __ldg(reinterpret_cast<const float4*>(w + e0 + 4));
+        const float hv[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w}, wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        float v[8], a = 0.f;
+        #pragma unroll
+        for (int i = 0; i < 8; i++) { v[i] = __fmul_rn(__fmul_rn(hv[i], scale), wv[i]); a = fmaxf(a, fabsf(v[i])); }
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+        const float inv = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+        unsigned lo = 0, hi = 0;
+        #pragma unroll
+        for (int i = 0; i < 4; i++) {
+            lo |= ((unsigned)__float2int_rn(__fmul_rn(v[i], inv)) & 0xffu) << (8 * i);
+            hi |= ((unsigned)__float2int_rn(__fmul_rn(v[4 + i], inv)) & 0xffu) << (8 * i);
+        }
+        if (live) {
+            *reinterpret_cast<uint2*>(xq + (size_t)m * E + e0) = make_uint2(lo, hi);
+            if ((t & 3) == 0) xd[(size_t)m * nb + (e0 >> 5)] = __float2half_rn(__fdiv_rn(a, 127.f));
+        }
     }
 }
 
@@ -80,8 +113,13 @@ __global__ void __launch_bounds__(DNT) vf_rope_kv(const DecodeParams P, int l, c
     float* v = qkv + (size_t)m * stride;
     for (int pr = threadIdx.x; pr < (nq + P.KVD) / 2; pr += blockDim.x) {
         const int p = 2 * pr, within = (p < nq ? p : p - nq) % HD, i = within >> 1;
-        const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + i));      // fp32 angle, as src/cpu_infer.cpp:54
-        const double c = (double)__double2float_rn(cos(th)), s = (double)__double2float_rn(sin(th));
+        double c, s;
+        if (pos < P.rope_rows) {                                      // the table made at load holds these very values
+            c = (double)__ldg(P.rope_cs + (size_t)pos * HD + i); s = (double)__ldg(P.rope_cs + (size_t)pos * HD + HD / 2 + i);
+        } else {
+            const double th = (double)__fmul_rn((float)pos, __ldg(P.rope_freq + i));  // fp32 angle, as src/cpu_infer.cpp:54
+            c = (double)__double2float_rn(cos(th)); s = (double)__double2float_rn(sin(th));
+        }
         const double x0 = v[p], x1 = v[p + 1];
         v[p] = __double2float_rn(__dsub_rn(__dmul_rn(x0, c), __dmul_rn(x1, s)));
         v[p + 1] = __double2float_rn(__dadd_rn(__dmul_rn(x0, s), __dmul_rn(x1, c)));
