@@ -109,17 +109,24 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
     const bool shape_ok = lean_shape_ok(m->E, m->FF, m->NH * m->HD) && !getenv("MINFER_NO_LEAN");
     const bool lean = m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && shape_ok;
     auto as_kernel = [](const void* p) { return reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(p)); };
-    if (P.tp.on) {                                  // the build with the exchange between GPUs inside (decode_tp.cu)
-        kern = as_kernel(lean ? decode_kernel_tp_lean(m->HD, m->G) : decode_kernel_tp(m->HD, m->G));
+    // the context-range builds are instantiated for the head shapes that occur with the embedding widths they take; a
+    // null pointer from their pickers means "not built for this head shape": the general build of the same family runs
+    const bool mid = shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kShortAttnMax && (long long)P.pos0 + step1 <= kPerHeadAttnMax;
+    const bool far = shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax;
+    const void* pick = nullptr;
+    if (P.tp.on) {                                  // the builds with the exchange between GPUs inside (decode_tp.cu, decode_tp_lean.cu)
+        if (lean) pick = decode_kernel_tp_lean(m->HD, m->G);
+        if (!pick) pick = decode_kernel_tp(m->HD, m->G);
     } else if (P.prof) {                            // the instrumented builds (decode_prof.cu, decode_prof_lean.cu)
-        kern = as_kernel(lean ? decode_kernel_prof_lean(m->HD, m->G) : decode_kernel_prof(m->HD, m->G));
-    } else if (lean) {
-        kern = as_kernel(decode_kernel_lean(m->HD, m->G));
-    } else if (shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kShortAttnMax && (long long)P.pos0 + step1 <= kPerHeadAttnMax) {
-        kern = as_kernel(decode_kernel_lean_mid(m->HD, m->G));       // every step within 257..kPerHeadAttnMax positions
-    } else if (shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax) {
-        kern = as_kernel(decode_kernel_lean_long(m->HD, m->G));      // every step beyond
+        if (lean) pick = decode_kernel_prof_lean(m->HD, m->G);
+        if (!pick) pick = decode_kernel_prof(m->HD, m->G);
     } else {
+        if (lean) pick = decode_kernel_lean(m->HD, m->G);
+        else if (mid) pick = decode_kernel_lean_mid(m->HD, m->G);
+        else if (far) pick = decode_kernel_lean_long(m->HD, m->G);
+    }
+    if (pick) kern = as_kernel(pick);
+    else {
         #define MI_PICK(hd, g) if (m->HD == hd && m->G == g) kern = decode_kernel<hd, g>;
         MI_PICK(32, 2) MI_PICK(64, 2) MI_PICK(64, 7) MI_PICK(128, 6) MI_PICK(128, 8)
         #undef MI_PICK

@@ -1438,8 +1438,9 @@ __device__ __forceinline__ AttnPrefetch attention_dedicated(const DecodeParams& 
     const int a0 = (int)((long long)Lp * warp / DNW), a1 = (int)((long long)Lp * (warp + 1) / DNW), np = a1 - a0;
     // pass 1: thread = position (the range is at most 256 rows).  A thread walks its K row front to back, one fp16 ->
     // double conversion of an element serving all heads, and adds the products in dimension order with one accumulator
-    // per head: the oracle's own order of this sum.  q comes as 16-byte broadcast loads (every lane reads the same address);
-    // rows are 16 bytes longer than their data, so the eight lanes of a quarter warp cover all banks.  (Eight lanes per
+    // per head: the order in which the reference's CPU program adds this sum (src/cpu_infer.cpp:127-130).  q comes as
+    // 16-byte broadcast loads (every lane reads the same address); rows are 16 bytes longer than their data, so the
+    // eight lanes of a quarter warp cover all banks.  (Eight lanes per
     // position with a shuffle tree per sweep measured 1.8 us per layer at a hundred positions: the conversions and the
     // tree of every sweep were serial.)
     if (warp * 32 < Lp) {
