@@ -330,7 +330,12 @@ MI_API int mi_verify(mi_ctx* ctx, mi_model* model, const int32_t* tokens_host, i
  * tokens by prompt lookup - the tokens that followed the latest earlier occurrence of the last
  * ngmax .. 1 tokens of the sequence so far - scores the current token and the draft in ONE
  * M-token pass (mi_verify) and keeps the longest prefix of the draft that equals the model's own
- * greedy tokens; without a draft it runs one single-token step (mi_decode).  Because a token's
+ * greedy tokens; without a draft it runs one single-token step (mi_decode).  How many of the drafted
+ * tokens a step submits is decided per step, as in the reference's kernel (src/mega.cu:579-589): the
+ * length that maximizes expected tokens per unit of time for the running acceptance estimate, priced
+ * with the device times the loop has measured for its own two kinds of step - none, where a pass of
+ * that size costs more than it is expected to bring (every 32nd such step still tests one token).
+ * draftk < 0: always submit the whole draft (up to -draftk tokens), whatever it costs.  Because a token's
  * logits are the same bits in both kinds of step, out_tokens_host[0 .. n_gen) is exactly the
  * sequence plain greedy decoding produces (the first id is the prediction after the last prompt
  * token).  margins_host (optional, [n_gen]): the logit margin (top-1 minus top-2) of the step that

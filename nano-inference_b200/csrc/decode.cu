@@ -215,7 +215,7 @@ extern "C" int mi_model_load_gguf_tp(mi_ctx* ctx, const char* path, int max_seq,
     m->max_chunks = std::max(1, m->grid / m->NKV);
     // CTAs set aside for attention (see DecodeParams::attn_ctas): one per query head, where the grid is large enough to spare them
     {
-        const int G = m->G, hpc = (G % 2 == 0 && G > 2) ? G / 2 : (G <= 2 ? 1 : G);      // attn_heads_per_cta<G>()
+        const int hpc = attn_heads_per_cta(m->G);
         m->attn_ctas = (m->NH / hpc * 8 <= m->grid && attn_dedicated_smem(m->HD, hpc) + 1024 <= (size_t)ctx->smem_optin) ? m->NH / hpc : 0;
         if (const char* ac = getenv("MINFER_ATTN_CTAS")) { int v = atoi(ac); if (v == 0) m->attn_ctas = 0; }
     }

@@ -75,6 +75,9 @@
 #ifndef MI_PIECE
 #define MI_PIECE __forceinline__
 #endif
+#ifndef MI_ATTN_HPC_EVEN
+#define MI_ATTN_HPC_EVEN(G) 2
+#endif
 
 // The kernel exists in four builds.  The default one carries no profiling code and no peer stores.  A translation unit
 // that defines MI_PROF 1 before including this file gets the instrumented build (timer marks between the hot instructions
@@ -1364,7 +1367,10 @@ __host__ __device__ inline size_t attn_dedicated_smem(int HD, int HPC) {
     return (size_t)2 * kAttnRows * (2 * HD + 16) + (size_t)HPC * (HD + 16) * 8 + (size_t)HPC * kAttnRows * 8 + (size_t)DNW * HPC * HD * 8 +
            (size_t)DNW * HPC * 8 + (size_t)HPC * kAttnRows * 4 + 64;
 }
-template <int G> __host__ __device__ constexpr int attn_heads_per_cta() { return (G % 2 == 0 && G > 2) ? G / 2 : (G <= 2 ? 1 : G); }
+// query heads per attention CTA: two where the group size is even (1.5B: six CTAs of two heads; three heads per CTA
+// measured 4.5 us per layer on the critical path, see the profile table in the repository's design notes), the whole
+// group where it is odd, one head for groups of one or two
+__host__ __device__ constexpr int attn_heads_per_cta(int G) { return (G % 2 == 0 && G > 2) ? MI_ATTN_HPC_EVEN(G) : (G <= 2 ? 1 : G); }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
@@ -1620,7 +1626,7 @@ static __device__ __noinline__ void attn_cta_main(const DecodeParams& P, int ste
                 int nl = -1, np_ = pos;
                 if (ph + 5 < ph1 && l + 1 < P.L) nl = l + 1;
                 else if (step + 1 < step1 && ph0 <= 1) { nl = 0; np_ = pos + 1; }
-                apf = attention_dedicated<HD, G, attn_heads_per_cta<G>()>(P, l, pos, smem, apf, pub.tag - 1u, pub, nl, np_);
+                apf = attention_dedicated<HD, G, attn_heads_per_cta(G)>(P, l, pos, smem, apf, pub.tag - 1u, pub, nl, np_);
                 ok = apf.ok;
             }
 #endif

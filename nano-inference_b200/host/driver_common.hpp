@@ -19,9 +19,10 @@
 // before the run), PROFILE=1 (per-phase time on one CTA, persistent engine), GPU=i
 // (device index), TCHUNK=m (prompt / teacher-forced tokens per weight pass through
 // the M-token step, 1..16, default 16; 1 = one decode step per token;
-// src/cuda_infer.cu:1130-1144), SPEC=0|1 (lossless n-gram speculation;
+// src/cuda_infer.cu:1130-1144), SPEC=0|1|2 (lossless n-gram speculation;
 // default 1 in mega, 0 in cuda_infer, as in the reference: src/mega.cu:1020,
-// src/cuda_infer.cu:1167), NGMAX / NG (longest n-gram, default 3), DRAFTK (drafted
+// src/cuda_infer.cu:1167; 2 = submit every draft in full instead of the length
+// the loop's cost model picks), NGMAX / NG (longest n-gram, default 3), DRAFTK (drafted
 // tokens per step, default 4), MARGINS=1 (last stderr line "i:tok:margin ..." for
 // every generated token, src/mega.cu:1241), SEGMENTS=w (tok/s over windows of w
 // tokens, src/mega.cu:1236-1240), ATTN (accepted and ignored: attention is always
@@ -155,7 +156,7 @@ inline int driver_main(int argc, char** argv, const char* tag, int mode) {
         // lossless n-gram speculation: the library's loop over single-token steps and M-token verify passes
         gen.resize(n_gen); margin.resize(n_gen);
         int64_t stats[4] = {0, 0, 0, 0};
-        if ((st = mi_generate_spec(ctx, model, ids.data(), P, n_gen, ngmax, draftk, gen.data(), margin.data(), stats))) die(ctx, "mi_generate_spec", st);
+        if ((st = mi_generate_spec(ctx, model, ids.data(), P, n_gen, ngmax, spec >= 2 ? -draftk : draftk, gen.data(), margin.data(), stats))) die(ctx, "mi_generate_spec", st);
         n_out = mi_model_last_count(model);
         dms = since(); ttft = dms / (n_out > 0 ? n_out : 1);
         n_steps = stats[0]; n_drafted = stats[1]; n_accepted = stats[2];

@@ -62,7 +62,9 @@ def test_speculation_is_lossless_and_accepts_drafts_where_the_stream_repeats(cas
     several tokens; the livelier models exercise rejection."""
     for idx, (path, c) in enumerate(cases):
         outs = {}
-        for spec in (0, 1):
+        # SPEC=1 lets the loop's cost model pick the draft length (on these two-layer models a pass costs several single
+        # steps, so it may pick none); SPEC=2 submits every draft in full, which is what exercises acceptance here
+        for spec in (0, 1, 2):
             out, err = run_driver("mega", path, 48, c["prompt"], SPEC=spec, DRAFTK=8, MAXSEQ=128)
             outs[spec] = out
             m = re.search(r"(\d+) generation steps, ([\d.]+) tokens/step \| drafted (\d+), accepted (\d+)", err)      # tools/specbench.sh:35
@@ -72,9 +74,9 @@ def test_speculation_is_lossless_and_accepts_drafts_where_the_stream_repeats(cas
                 assert "[SPEC=0]" in err and steps == 48 and drafted == 0
             else:
                 assert accepted <= drafted and steps <= 48
-                if idx == 0:
+                if idx == 0 and spec == 2:
                     assert accepted > 0 and steps < 48 and tps > 1.5, f"no draft accepted on a constant stream: {m.group(0)}"
-        assert outs[0] == outs[1], f"SPEC=1 changed the generated ids on the std-{c['std']} model"
+        assert outs[0] == outs[1] == outs[2], f"speculation changed the generated ids on the std-{c['std']} model"
 
 
 def test_generate_spec_equals_plain_decode_and_counts_accepted_tokens(ctx, pkg, cases):
@@ -85,7 +87,7 @@ def test_generate_spec_equals_plain_decode_and_counts_accepted_tokens(ctx, pkg, 
     prompt = [int(t) for t in np.random.default_rng(5).integers(0, V, 20)]
     plain, _ = m.generate(prompt, 100)
     plain_margins = None
-    for ngmax, draftk in ((3, 4), (1, 15), (2, 8)):
+    for ngmax, draftk in ((3, 4), (1, 15), (2, 8), (3, -4), (2, -15)):         # negative: every draft submitted in full
         got, st = m.generate_spec(prompt, 100, ngmax=ngmax, draftk=draftk)
         assert got == plain, f"NGMAX={ngmax} DRAFTK={draftk}"
         assert st["accepted"] <= st["drafted"] and st["steps"] <= 100
