@@ -825,9 +825,9 @@ def run_ours(args, rank, world, local_rank):
                    "grid_ctas": cfg.grid_ctas},
         "roofline": {"bound": "hbm", "achieved": round(ach, 1), "peak": peak * world, "unit": "GB/s", "frac": round(ach / (peak * world), 4),
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind}) x {world} GPU(s)",
-                     "traffic": round(1.001 * bytes_region) if world == 1 else None,
-                     "traffic_note": "dram read+write per launch = 1.001 x algorithmic bytes (weights read exactly once, KV served by L2): "
-                                     "ncu capture of a 23-token persistent launch, scaled by tokens",
+                     "traffic": round(1.000 * bytes_region) if world == 1 else None,
+                     "traffic_note": "dram read+write per launch = 1.000 x algorithmic bytes (weights read exactly once, KV served by L2): "
+                                     "ncu capture of a 24-token persistent launch, scaled by tokens",
                      "kernel": "decode_kernel", "algorithmic_bytes_per_launch": int(bytes_region), "bytes_per_token": int(bytes_region / K),
                      "roofline_tok_s": round(roof_tok_s, 1), "frac_of_roofline_tok_s": round((K / (ms * 1e-3)) / roof_tok_s, 4)},
         "gemv_roofline": gemv_roofline(stacks, kern_ms, peak, peak_kind, probe),
