@@ -19,6 +19,7 @@ namespace mi {
 const void* decode_kernel_prof(int HD, int G); const void* decode_kernel_tp(int HD, int G); const void* decode_kernel_lean(int HD, int G);
 const void* decode_kernel_prof_lean(int HD, int G);
 const void* decode_kernel_tp_lean(int HD, int G);
+const void* decode_kernel_tp_prof_lean(int HD, int G);
 const void* decode_kernel_lean_mid(int HD, int G);
 const void* decode_kernel_lean_long(int HD, int G);
 int reset_after_error(mi_ctx* ctx, mi_model* m);
@@ -115,7 +116,8 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
     const bool far = shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax;
     const void* pick = nullptr;
     if (P.tp.on) {                                  // the builds with the exchange between GPUs inside (decode_tp.cu, decode_tp_lean.cu)
-        if (lean) pick = decode_kernel_tp_lean(m->HD, m->G);
+        if (lean && P.prof) pick = decode_kernel_tp_prof_lean(m->HD, m->G);
+        if (lean && !pick) pick = decode_kernel_tp_lean(m->HD, m->G);
         if (!pick) pick = decode_kernel_tp(m->HD, m->G);
     } else if (P.prof) {                            // the instrumented builds (decode_prof.cu, decode_prof_lean.cu)
         if (lean) pick = decode_kernel_prof_lean(m->HD, m->G);

@@ -96,7 +96,9 @@
 #ifndef MI_LEAN
 #define MI_LEAN 0
 #endif
-#if MI_PROF && MI_LEAN
+#if MI_PROF && MI_TP && MI_LEAN
+#define MI_KVARIANT tpxproflean
+#elif MI_PROF && MI_LEAN
 #define MI_KVARIANT proflean
 #elif MI_PROF
 #define MI_KVARIANT prof
