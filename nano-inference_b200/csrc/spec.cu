@@ -75,7 +75,7 @@ extern "C" int mi_generate_spec(mi_ctx* ctx, mi_model* m, const int32_t* prompt_
     int pos = n_prompt, n_emit = 0;
     // What a step costs, as measured by this loop (device milliseconds, running averages): a single-token step, and an
     // M-token pass for every M used so far; an M not yet seen is priced from the nearest seen one along the measured shape
-    // of the pass time (about 0.36 + 0.04 M of the 16-token pass).
+    // of the pass time (about 0.49 + 0.032 M of the 16-token pass).
     float t_dec = 0.f, t_ver[kMaxPass + 1] = {0.f};
     auto learn = [](float& avg, float ms) { if (ms > 0.f) avg = avg > 0.f ? 0.8f * avg + 0.2f * ms : ms; };
     for (int M = 1; M <= kMaxPass; M++) t_ver[M] = prompt_ms[M];     // the prompt's own passes are the first measurements
@@ -83,7 +83,7 @@ extern "C" int mi_generate_spec(mi_ctx* ctx, mi_model* m, const int32_t* prompt_
         if (t_ver[M] > 0.f) return t_ver[M];
         for (int d = 1; d <= kMaxPass; d++)
             for (int q : {M - d, M + d})
-                if (q >= 1 && q <= kMaxPass && t_ver[q] > 0.f) return t_ver[q] * (0.36f + 0.04f * M) / (0.36f + 0.04f * q);
+                if (q >= 1 && q <= kMaxPass && t_ver[q] > 0.f) return t_ver[q] * (0.49f + 0.032f * M) / (0.49f + 0.032f * q);
         return 0.f;
     };
     // acceptance probability of one drafted token (running estimate), and the draft length that pays best for it
