@@ -1399,7 +1399,7 @@ template <int HD, int GQ, int HPC>
 __device__ __forceinline__ AttnPrefetch attention_dedicated(const DecodeParams& P, int l, int pos, uint8_t* smem, AttnPrefetch pf,
                                                                 unsigned tag_in, const Pub pub, int next_layer, int next_pos) {
     constexpr int DPW = HD / 32, RSB = attn_row_bytes<HD>();
-    constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2, KV4 = DPL * 2 / 16 > 0 ? DPL * 2 / 16 : 1;
+    constexpr int LPP = 8, DPL = HD / LPP, QSTR = DPL + 2;
     constexpr int QN = (HPC * HD + DNT - 1) / DNT;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h0 = (int)blockIdx.x * HPC, kvh = h0 / GQ, Lp = pos + 1, nq = P.NH * HD;

@@ -100,11 +100,7 @@ __device__ __forceinline__ double tile_dot_row(const uint8_t* tile, int lane, in
     float dw[KB];
     load_tile_scales<KB>(tile, lane, dw);
     const uint4* wq = reinterpret_cast<const uint4*>(tile) + lane;
-#ifdef MI_TILE_UNROLL
-    #pragma unroll MI_TILE_UNROLL
-#else
-    #pragma unroll
-#endif
+    #pragma unroll                                      // (four at a time instead of all KB: 6 % slower in the decode kernel)
     for (int k = 0; k < KB; k++) {
         const uint4 w = wq[k * 32];
         const int4 xa = *reinterpret_cast<const int4*>(xq_s + (b0 + k) * 32);
