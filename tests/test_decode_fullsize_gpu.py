@@ -151,3 +151,23 @@ def test_context_specific_builds_give_the_bits_of_the_general_build(ctx, pkg, tm
         assert res[0][0] == res[1][0], f"tokens differ at position {pos0}"
         assert np.array_equal(res[0][1].view(np.uint32), res[1][1].view(np.uint32)), f"logits differ at position {pos0}"
     monkeypatch.delenv("MINFER_NO_LEAN", raising=False)
+
+
+def test_a_long_run_through_every_context_range_matches_the_general_build(ctx, pkg, tmp_path, monkeypatch):
+    """1100 generated tokens after an 8-token prompt pass 256 and 1024 cached positions: three launches of three builds
+    on one side, one launch of the general build on the other, the same ids."""
+    path = gu.make_synthetic(tmp_path / "m.gguf", "1.5b", seed=4)
+    V = gu.GgufReader(path).config()["n_vocab"]
+    prompt = [int(t) for t in np.random.default_rng(8).integers(0, V, 8)]
+    outs = []
+    for general in (False, True):
+        if general:
+            monkeypatch.setenv("MINFER_NO_LEAN", "1")
+        else:
+            monkeypatch.delenv("MINFER_NO_LEAN", raising=False)
+        m = pkg.Model(ctx, path, 1200)
+        out, _ = m.decode(prompt, 1108, 0)
+        outs.append(out)
+        m.free()
+    monkeypatch.delenv("MINFER_NO_LEAN", raising=False)
+    assert outs[0] == outs[1]
