@@ -231,7 +231,10 @@ enum { MI_STATE_H = 0, MI_STATE_Q = 1, MI_STATE_ATT = 2, MI_STATE_KCACHE = 3, MI
        MI_STATE_H_MID = 8 };  /* 32 x uint64 nanoseconds per phase part on CTA 0, filled when the model was loaded
                                  * with MINFER_PROFILE set in the environment: slots 2k / 2k+1 = staging / work of phase
                                  * kind k (0 QKV, 1 attention, 2 O, 3 gate-up, 4 down, 5 lm_head), 12 = waiting for other CTAs' data,
-                                 * 13 = per-step prologue.  The reference's PROFILE=1 (src/mega.cu:111-119). */
+                                 * 13 = per-step prologue, 18..22 = tile loops (loop, ring wait, arithmetic, issuing copies; 19 =
+                                 * fold + epilogue), 23..28 = parts of the norm prologue; on an attention CTA (MINFER_PROFILE_CTA)
+                                 * 14..17 and 27..31 = parts of the attention; slots 8 and 9 of the persistent engine hold the
+                                 * launch's SM cycles and nanoseconds.  The reference's PROFILE=1 (src/mega.cu:111-119). */
 
 /* Load a Qwen2-architecture GGUF file (metadata keys and tensor names
  * exactly as the reference drivers read them: src/cpu_infer.cpp:71-98), repack
