@@ -103,17 +103,23 @@ __global__ void rope_cs_kernel(const float* __restrict__ freq, float* __restrict
     cs[(size_t)pos * HD + HD / 2 + i] = __double2float_rn(sin(th));
 }
 
-int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop) {
+// range_hint 1 / 2 / 3: the caller vouches that every position of the launch lies in that context range (up to kShortAttnMax,
+// up to kPerHeadAttnMax, beyond) although the position is device-resident; 0: decided from pos0 and the steps.  (A build
+// launched outside its range ends with MI_ERR_LIMIT on every CTA, it computes nothing wrong.)  only_prepare: pick the
+// kernel and raise its shared-memory limit, launch nothing (what must not happen inside a stream capture).
+int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, int step1, int ph0, int ph1, bool coop, int range_hint = 0,
+                    bool only_prepare = false) {
     void (*kern)(DecodeParams, int, int, int, int) = nullptr;
     // every step of this launch ends within the range the dedicated attention CTAs handle, on a shape the short-context
     // build takes: that build has no other attention variant in it (decode_lean.cu)
     const bool shape_ok = lean_shape_ok(m->E, m->FF, m->NH * m->HD) && !getenv("MINFER_NO_LEAN");
-    const bool lean = m->attn_ctas > 0 && !P.pos_dev && (long long)P.pos0 + step1 <= kShortAttnMax && shape_ok;
+    const bool by_pos = !P.pos_dev && range_hint == 0;
+    const bool lean = m->attn_ctas > 0 && shape_ok && (range_hint == 1 || (by_pos && (long long)P.pos0 + step1 <= kShortAttnMax));
     auto as_kernel = [](const void* p) { return reinterpret_cast<void (*)(DecodeParams, int, int, int, int)>(const_cast<void*>(p)); };
     // the context-range builds are instantiated for the head shapes that occur with the embedding widths they take; a
     // null pointer from their pickers means "not built for this head shape": the general build of the same family runs
-    const bool mid = shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kShortAttnMax && (long long)P.pos0 + step1 <= kPerHeadAttnMax;
-    const bool far = shape_ok && !P.pos_dev && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax;
+    const bool mid = shape_ok && (range_hint == 2 || (by_pos && (long long)P.pos0 + step0 + 1 > kShortAttnMax && (long long)P.pos0 + step1 <= kPerHeadAttnMax));
+    const bool far = shape_ok && (range_hint == 3 || (by_pos && (long long)P.pos0 + step0 + 1 > kPerHeadAttnMax));
     const void* pick = nullptr;
     if (P.tp.on) {                                  // the builds with the exchange between GPUs inside (decode_tp.cu, decode_tp_lean.cu)
         if (lean && P.prof) pick = decode_kernel_tp_prof_lean(m->HD, m->G);
@@ -148,6 +154,7 @@ int dispatch_launch(mi_ctx* ctx, mi_model* m, const DecodeParams& P, int step0, 
     // Always a cooperative launch: CTAs wait for one another's tagged words inside every phase range (the K-split fold
     // of the down projection, the greedy pick over all CTAs' candidates), so all of them must be resident together.
     (void)coop;
+    if (only_prepare) return MI_OK;
     void* args[] = {(void*)&P, &step0, &step1, &ph0, &ph1};
     MI_CUDA(ctx, cudaLaunchCooperativeKernel((const void*)kern, dim3(m->grid), dim3(DNT), args, m->smem, ctx->stream));
     return MI_OK;
@@ -163,6 +170,7 @@ extern "C" int mi_model_free(mi_ctx* ctx, mi_model* m) {
     for (void* p : m->ipc_opened) cudaIpcCloseMemHandle(p);
     for (void* p : m->allocs) cudaFree(p);
     for (void* g : m->vb.graph) if (g) cudaGraphExecDestroy((cudaGraphExec_t)g);
+    for (void* g : m->step_graph) if (g) cudaGraphExecDestroy((cudaGraphExec_t)g);
     if (m->ev0) cudaEventDestroy(m->ev0);
     if (m->ev1) cudaEventDestroy(m->ev1);
     delete m;
@@ -582,6 +590,59 @@ extern "C" int mi_ring_peek(const mi_token_ring* r, int* count, const int32_t** 
     return MI_OK;
 }
 
+// ---- the kernel-sequence engine as a replayed graph -----------------------------------------------------------------
+// One step of the kernel-sequence engine is 5L+1 cooperative launches; issued one by one they cost the host about 10 us
+// each, more than the kernels take.  So the step is captured once per context range - position and token device-resident,
+// which phase a launch runs is its only argument - and replayed per token, as the reference's kernel-sequence driver
+// replays its captured step (src/cuda_infer.cu:1089-1109).  The graph's first node puts a forced token in place, its last
+// nodes file the step's token and margin under the step's index and advance position and index; the arrays they use are
+// named by a control block in device memory that every call refills, so a graph outlives reallocation of those arrays.
+struct SeqCtl { const int* in; int* out; float* mg; int n_forced; int step; };
+__global__ void seq_set_pos_kernel(int* pos, int value) { *pos = value; }
+__global__ void seq_pre_kernel(const SeqCtl* c, int* cur_token) { if (c->step < c->n_forced) *cur_token = c->in[c->step]; }
+__global__ void seq_post_kernel(SeqCtl* c, const int* tok, const float* margin, int* pos) {
+    c->out[c->step] = *tok; c->mg[c->step] = *margin; c->step += 1; *pos += 1;
+}
+
+static int step_graph(mi_ctx* ctx, mi_model* m, int range, cudaGraphExec_t* out) {
+    if (m->step_graph[range] && m->step_graph_wait[range] == ctx->wait_ns) { *out = (cudaGraphExec_t)m->step_graph[range]; return MI_OK; }
+    if (m->step_graph[range]) { cudaGraphExecDestroy((cudaGraphExec_t)m->step_graph[range]); m->step_graph[range] = nullptr; }
+    int st;
+    if (!m->d_seq_ctl) {
+        SeqCtl* c; if ((st = dev_alloc(ctx, m, &c, 1)) || (st = dev_alloc(ctx, m, &m->d_step_out, 2)) || (st = dev_alloc(ctx, m, &m->d_step_margin, 2))) return st;
+        m->d_seq_ctl = c;
+    }
+    const int nph = 5 * m->L + 1;
+    DecodeParams P = m->P;
+    P.in_tokens = nullptr; P.n_forced = 0; P.out_tokens = m->d_step_out; P.out_margins = m->d_step_margin; P.pos0 = 0; P.pos_dev = m->d_pos;
+    P.logits = nullptr; P.logits_stride = m->V; P.wait_ns = ctx->wait_ns; P.stop_token = -1;
+    if ((st = dispatch_launch(ctx, m, P, 0, 1, 0, 1, false, range, true))) return st;      // kernel picked, shared-memory limit raised: not inside the capture
+    // captured on a stream of its own: the context's stream may be the legacy default stream, which cannot capture
+    MI_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaStream_t cs = nullptr, user = ctx->stream;
+    MI_CUDA(ctx, cudaStreamCreateWithFlags(&cs, cudaStreamNonBlocking));
+    cudaError_t eb = cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal);
+    if (eb != cudaSuccess) { cudaStreamDestroy(cs); return set_error(ctx, MI_ERR_CUDA, "decode: the step cannot be captured: %s", cudaGetErrorString(eb)); }
+    ctx->stream = cs;
+    seq_pre_kernel<<<1, 1, 0, cs>>>(static_cast<const SeqCtl*>(m->d_seq_ctl), m->P.cur_token);
+    st = MI_OK;
+    for (int ph = 0; ph < nph && st == MI_OK; ph++) st = dispatch_launch(ctx, m, P, 0, 1, ph, ph + 1, false, range);
+    seq_post_kernel<<<1, 1, 0, cs>>>(static_cast<SeqCtl*>(m->d_seq_ctl), m->d_step_out, m->d_step_margin, m->d_pos);
+    ctx->stream = user;
+    cudaGraph_t g = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(cs, &g);
+    cudaStreamDestroy(cs);
+    if (st != MI_OK) { if (g) cudaGraphDestroy(g); return st; }
+    if (e != cudaSuccess) { if (g) cudaGraphDestroy(g); return set_error(ctx, MI_ERR_CUDA, "decode: capturing the step failed: %s", cudaGetErrorString(e)); }
+    cudaGraphExec_t x = nullptr;
+    const cudaError_t e2 = cudaGraphInstantiate(&x, g, 0);
+    cudaGraphDestroy(g);
+    if (e2 != cudaSuccess) return set_error(ctx, MI_ERR_CUDA, "decode: instantiating the step graph failed: %s", cudaGetErrorString(e2));
+    m->step_graph[range] = x; m->step_graph_wait[range] = ctx->wait_ns;
+    *out = x;
+    return MI_OK;
+}
+
 static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, int n_forced, int n_steps, int pos0,
                        int32_t* out_tokens_host, float* logits_dev, int mode, int ph0, int ph1, float* elapsed_ms,
                        mi_token_ring* ring = nullptr, bool async = false) {
@@ -652,6 +713,23 @@ static int decode_impl(mi_ctx* ctx, mi_model* m, const int32_t* in_tokens_host, 
             if (Ps.logits) Ps.logits += (long long)cuts[i] * Ps.logits_stride;   // the kernel indexes logits and ring entries from its first step
             Ps.ring.base += cuts[i];
             if ((st = dispatch_launch(ctx, m, Ps, cuts[i], cuts[i + 1], 0, nph, true))) return st;
+        }
+    } else if (mode == MI_DECODE_PER_PHASE && !logits_dev && stop < 0 && !ring && ph0 == 0 && ph1 == nph && m->tp_world == 1 && P.drop_phase < 0 && !P.prof &&
+               !getenv("MINFER_SEQ_NO_GRAPH")) {
+        // whole steps, nothing to look at between them: the captured step, replayed per token
+        cudaGraphExec_t gx[4] = {nullptr, nullptr, nullptr, nullptr};
+        for (int s = 0; s < n_steps; s++) {             // every graph this run needs exists before the first replay
+            const int range = pos0 + s + 1 <= kShortAttnMax ? 1 : pos0 + s + 1 <= kPerHeadAttnMax ? 2 : 3;
+            if (!gx[range] && (st = step_graph(ctx, m, range, &gx[range]))) return st;
+        }
+        const SeqCtl ctl{m->d_in_tokens, m->d_out_tokens, m->d_margins, n_forced, 0};
+        MI_CUDA(ctx, cudaMemcpyAsync(m->d_seq_ctl, &ctl, sizeof ctl, cudaMemcpyHostToDevice, ctx->stream));
+        seq_set_pos_kernel<<<1, 1, 0, ctx->stream>>>(m->d_pos, pos0);
+        MI_CUDA(ctx, cudaGetLastError());
+        MI_CUDA(ctx, cudaEventRecord(m->ev0, ctx->stream));         // (the timed region starts after the set-up above)
+        for (int s = 0; s < n_steps; s++) {
+            const int range = pos0 + s + 1 <= kShortAttnMax ? 1 : pos0 + s + 1 <= kPerHeadAttnMax ? 2 : 3;
+            MI_CUDA(ctx, cudaGraphLaunch(gx[range], ctx->stream));
         }
     } else if (mode == MI_DECODE_PER_PHASE) {
         for (int s = 0; s < n_steps; s++) {

@@ -40,6 +40,10 @@ struct mi_model {
     mi::DecodeParams P{};                     // device pointers filled in; per-call fields set at launch
     int* d_in_tokens = nullptr; int in_capacity = 0;
     int* d_out_tokens = nullptr; int out_capacity = 0;
+    // kernel-sequence engine as a replayed CUDA graph (decode.cu, step_graph): one graph per context range, the control
+    // block the graph's first and last node read (device memory, refilled per call), the step's token and margin
+    void* step_graph[4] = {}; unsigned long long step_graph_wait[4] = {};
+    void* d_seq_ctl = nullptr; int* d_step_out = nullptr; float* d_step_margin = nullptr;
     int stop_token = -1;                  // see mi_model_set_stop_token
     int last_count = 0;                   // steps (tokens) the last decode / generate call produced: fewer than asked after a stop
     float* d_margins = nullptr; int last_steps = 0;   // top-1 minus top-2 logit of every step of the last decode call
